@@ -1,0 +1,214 @@
+/* tsb200.h - C ABI of the B200 (sm_100a) compressed-decode kernels.
+ *
+ * This library replaces, for one hot path, what transformer-surgeon executes through
+ * PyTorch library calls: LinearCompressed.forward on quantized low-rank factors, a
+ * quantized paged KV cache (append + decode attention) and the small decoder ops around
+ * them.  The reference project ships no native code and therefore no FFI; each entry
+ * point below names the reference Python function whose arithmetic it takes over
+ * (paths are relative to the reference project root).
+ *
+ * Conventions
+ *   - every function returns 0 (TSB200_OK) or a negative tsb200_status; it never throws,
+ *     never allocates device memory, never synchronises the device; work is enqueued on
+ *     the `stream` argument (a cudaStream_t passed as void*; NULL = legacy default stream);
+ *   - all pointers are DEVICE pointers unless the name ends in `_host`;
+ *   - tensors are dense row-major; "act dtype" is the dtype of activations/bias/outputs;
+ *   - scratch memory is supplied by the caller (`workspace`, sized by the matching
+ *     `*_workspace_bytes` function);
+ *   - the library contains sm_100a code only: on any other device every compute entry
+ *     point returns TSB200_ERR_DEVICE (there is no fallback path).
+ */
+#ifndef TSB200_H
+#define TSB200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum {
+  TSB200_OK = 0,
+  TSB200_ERR_ARG = -1,         /* null pointer, negative size, misaligned pointer        */
+  TSB200_ERR_UNSUPPORTED = -2, /* shape / dtype / format combination not implemented     */
+  TSB200_ERR_CUDA = -3,        /* a CUDA runtime call failed (see tsb200_last_cuda_error)*/
+  TSB200_ERR_WORKSPACE = -4,   /* workspace too small                                    */
+  TSB200_ERR_DEVICE = -5,      /* current device is not compute capability 10.0          */
+  TSB200_ERR_TIMEOUT = -6      /* a bounded device-side wait ran out (status word set)   */
+} tsb200_status;
+
+typedef enum { TSB200_F32 = 0, TSB200_BF16 = 1 } tsb200_dtype;
+
+/* Weight containers: storage bits per code.  32/16 = unquantized fp32/bf16 weights. */
+typedef enum {
+  TSB200_W_BIN1 = 1, TSB200_W_INT2 = 2, TSB200_W_INT4 = 4, TSB200_W_INT8 = 8,
+  TSB200_W_BF16 = 16, TSB200_W_F32 = 32
+} tsb200_wbits;
+
+typedef enum { TSB200_KV_INT8 = 0, TSB200_KV_FP8 = 1, TSB200_KV_NVFP4 = 2 } tsb200_kv_format;
+
+const char* tsb200_strerror(int status);
+int tsb200_version(void);
+/* cudaError_t of the most recent failing runtime call made by this library (0 if none). */
+int tsb200_last_cuda_error(void);
+/* TSB200_OK when the CURRENT device can run this library (compute capability 10.0). */
+int tsb200_check_device(void);
+
+/* ------------------------------------------------------------------------------------
+ * Weight quantization, packing, reconstruction
+ * Replaces: compression/quantization_methods/vanilla.py:10-24 (_quantize_maxabs),
+ *           :27-37 (_quantize_binarize), :5-7 (_dequantize_symmetric) and the write-back
+ *           compression/quantization.py:112,126.
+ * Arithmetic follows the reference bit for bit: all steps in the parameter dtype
+ * (bf16: fp32 op then round-to-nearest-even to bf16 after EVERY op), round-half-even.
+ * ---------------------------------------------------------------------------------- */
+
+/* Bytes of one packed row: ceil(cols/64)*64*bits/8 (bits in 1,2,4,8). 0 on bad args. */
+size_t tsb200_packed_row_bytes(int64_t cols, int bits);
+
+/* w [rows, cols] (dtype) -> codes int8 [rows, cols], scales fp32 [rows] (values exactly
+ * representable in `dtype`; per-tensor mode writes the same scale to every row).
+ * precision: 2..8 fixed point, 0 = binary (sign, mean|w|).  workspace: >= 16 bytes. */
+int tsb200_quantize_weight(const void* w, int dtype, int64_t rows, int64_t cols,
+                           int precision, int per_channel, float eps,
+                           int8_t* codes, float* scales,
+                           void* workspace, size_t workspace_bytes, void* stream);
+
+/* codes int8 [rows, cols] -> packed [rows, tsb200_packed_row_bytes(cols,bits)].
+ * bits=1 requires codes in {-1,+1}; *zero_flag (device int32, may be NULL) is set to 1
+ * when a zero code was met (the caller then repacks with bits=2). */
+int tsb200_pack_codes(const int8_t* codes, int64_t rows, int64_t cols, int bits,
+                      uint8_t* packed, int32_t* zero_flag, void* stream);
+
+/* packed -> codes int8 [rows, cols]. */
+int tsb200_unpack_codes(const uint8_t* packed, int64_t rows, int64_t cols, int bits,
+                        int8_t* codes, void* stream);
+
+/* packed + scales -> w_out [rows, cols] (dtype) = RN_dtype(float(code) * scale[row]):
+ * the fake-quantized weight the reference stores (quantization.py:126). */
+int tsb200_dequantize_weight(const uint8_t* packed, const float* scales, int64_t rows,
+                             int64_t cols, int bits, int dtype, void* w_out, void* stream);
+
+/* ------------------------------------------------------------------------------------
+ * LinearCompressed.forward
+ * Replaces: blocks/linear_compressed.py:81-105
+ *   h = x @ V^T        (only when rank > 0;  V = linear_V.weight [rank, in])
+ *   y = h @ U^T + bias (U = weight [out, rank] or [out, in])
+ * A factor is either unquantized (bits 16/32, pointer to act-dtype matrix, scale NULL)
+ * or packed codes (bits 1/2/4/8) with one fp32 scale per row.
+ * ---------------------------------------------------------------------------------- */
+typedef struct {
+  int64_t in_features;
+  int64_t out_features;
+  int64_t rank;          /* 0 = full rank (no V factor)                                 */
+  int32_t act_dtype;     /* tsb200_dtype of x, y, bias and of the rank-r intermediate   */
+  int32_t u_bits;        /* tsb200_wbits of U                                            */
+  int32_t v_bits;        /* tsb200_wbits of V (ignored when rank == 0)                   */
+  int32_t reserved;      /* must be 0                                                    */
+  const void* u;         /* [out, K] packed or dense, K = rank ? rank : in_features      */
+  const float* u_scale;  /* [out] or NULL for dense                                      */
+  const void* v;         /* [rank, in] packed or dense, or NULL                          */
+  const float* v_scale;  /* [rank] or NULL                                               */
+  const void* bias;      /* [out] act dtype, or NULL                                     */
+} tsb200_linear_desc;
+
+size_t tsb200_linear_workspace_bytes(const tsb200_linear_desc* d, int64_t M);
+/* x [M, in] -> y [M, out].  M == 0 is a no-op. */
+int tsb200_linear(const tsb200_linear_desc* d, const void* x, void* y, int64_t M,
+                  void* workspace, size_t workspace_bytes, void* stream);
+/* Same contract; forces the CUDA-core streaming kernel (any M; used for tiny M and as
+ * the cross-check of the tensor-core kernel). */
+int tsb200_linear_simt(const tsb200_linear_desc* d, const void* x, void* y, int64_t M,
+                       void* workspace, size_t workspace_bytes, void* stream);
+
+/* ------------------------------------------------------------------------------------
+ * Quantized paged KV cache
+ * The reference's cache is a dense fixed-size row store written at clamp(pos_id)
+ * (blocks/mha.py:514-535, :583) or Hugging Face's DynamicLayer.update (torch.cat); the
+ * quantized/paged formats here are new behaviour layered on the same call points.
+ * Page = 16 tokens.  Pools: uint8 [num_pages, hkv, record_bytes]; record layouts:
+ *   K int8  : codes [16][d], then fp32 scale [16]
+ *   K fp8   : codes [16][d]                         (e4m3, one fp32 scale per (seq, head))
+ *   K nvfp4 : codes [16][d/2], then e4m3 block scales [16][d/16]
+ *   V int8  : codes [d][16] (token-minor), then fp32 scale [16]
+ *   V fp8   : codes [d][16]
+ *   V nvfp4 : codes [d/2][16] (byte = elements 2i | 2i+1<<4 of one token), scales [d/16][16]
+ * ---------------------------------------------------------------------------------- */
+size_t tsb200_kv_record_bytes(int format, int head_dim);
+
+typedef struct {
+  int32_t format;        /* tsb200_kv_format                                            */
+  int32_t hkv;           /* number of kv heads                                           */
+  int32_t head_dim;      /* 64 or 128                                                    */
+  int32_t reserved;
+  int64_t num_pages;
+  uint8_t* k_pool;       /* 16-byte aligned                                              */
+  uint8_t* v_pool;
+  const int32_t* block_table; /* [B, bt_stride]: page id of logical page i of sequence b */
+  int64_t bt_stride;
+  const int32_t* seq_lens;    /* [B] tokens currently in the cache                       */
+  const float* k_scale;  /* fp8 only: [B, hkv]                                           */
+  const float* v_scale;
+} tsb200_kv_desc;
+
+/* fp8 per-(sequence, head) scales from a prompt: scale = amax/448 (1.0 when amax == 0)
+ * over k[b, :, h, :] (after the same RoPE the append applies when tables are given; token
+ * j of sequence b is at position pos0[b] + j, pos0 NULL = 0) and over v[b, :, h, :].
+ * k, v [B, T, hkv, d] act dtype.  Outputs fp32 [B, hkv]. */
+int tsb200_kv_fp8_scales(const void* k, const void* v, int dtype, int64_t B, int64_t T,
+                         int hkv, int head_dim, const int32_t* pos0,
+                         const float* rope_cos, const float* rope_sin, int64_t rope_rows,
+                         float* k_scale, float* v_scale, void* stream);
+
+/* Fused (RoPE on k +) quantize-and-append of T new tokens per sequence.
+ * k, v [B, T, hkv, d]; token j of sequence b goes to position seq_lens[b] + j.
+ * new_lens (int32 [B], may be NULL = T): only the first new_lens[b] tokens are appended.
+ * rope_cos/rope_sin: fp32 tables [rope_rows, d/2] indexed by position, or NULL (k is
+ * appended as given).  Rotation is the half-split form of blocks/rope.py:140-173 with
+ * each product and sum rounded to the act dtype.  seq_lens is NOT modified.
+ * Positions beyond the block table (>= bt_stride*16) are skipped. */
+int tsb200_kv_append(const tsb200_kv_desc* kv, const void* k, const void* v, int dtype,
+                     int64_t B, int64_t T, const int32_t* new_lens,
+                     const float* rope_cos, const float* rope_sin, int64_t rope_rows,
+                     void* stream);
+
+/* Split-K paged decode attention: one query token per sequence.
+ * Replaces blocks/mha.py:9-103 (attention(): GQA, softmax(q k^T / sqrt(d)) v) for the
+ * decode step, reading the quantized pages directly.
+ * q, out [B, H, d] act dtype; attends over seq_lens[b] tokens (0 -> zeros).
+ * max_seq_len bounds seq_lens (sizes the split grid; lengths above it are clamped). */
+size_t tsb200_paged_decode_attn_workspace_bytes(int64_t B, int H, int head_dim, int64_t max_seq_len);
+int tsb200_paged_decode_attn(const tsb200_kv_desc* kv, const void* q, void* out, int dtype,
+                             int64_t B, int H, float sm_scale, int64_t max_seq_len,
+                             void* workspace, size_t workspace_bytes, void* stream);
+/* Same contract; CUDA-core kernel (cross-check of the tensor-core kernel). */
+int tsb200_paged_decode_attn_simt(const tsb200_kv_desc* kv, const void* q, void* out, int dtype,
+                                  int64_t B, int H, float sm_scale, int64_t max_seq_len,
+                                  void* workspace, size_t workspace_bytes, void* stream);
+
+/* ------------------------------------------------------------------------------------
+ * Small decoder ops
+ * ---------------------------------------------------------------------------------- */
+/* In-place half-split RoPE (blocks/rope.py:140-173) on x [B, T, heads, d]; position of
+ * token (b, j) is pos0[b] + j (pos0 int32 [B], NULL = 0). */
+int tsb200_rope(void* x, int dtype, int64_t B, int64_t T, int heads, int head_dim,
+                const int32_t* pos0, const float* rope_cos, const float* rope_sin,
+                int64_t rope_rows, void* stream);
+
+/* residual += delta (delta may be NULL), then y = RMSNorm(residual) * w.
+ * variant 0: Hugging Face Qwen2/Llama RMSNorm (fp32 x*rsqrt(mean(x^2)+eps), cast, *w);
+ * variant 1: blocks/norm.py:8-23 (x /= max(1, max|x|), eps fixed 1e-5, in act dtype).
+ * residual, delta, y [M, hidden]; w [hidden]. y may alias delta. */
+int tsb200_add_rmsnorm(void* residual, const void* delta, const void* w, void* y, int dtype,
+                       int64_t M, int64_t hidden, float eps, int variant, void* stream);
+
+/* y = silu(gate) * up (blocks/mlp.py:181-183); gate, up, y [M, n] with row strides in
+ * elements (so gate/up may be the two halves of one [M, 2n] buffer). */
+int tsb200_swiglu(const void* gate, const void* up, void* y, int dtype, int64_t M, int64_t n,
+                  int64_t gate_stride, int64_t up_stride, int64_t y_stride, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TSB200_H */

@@ -17,7 +17,8 @@ import torch
 
 
 def attention(query, key, value, attn_mask=None):
-    """query [T,H,d], key/value [L,Hkv,d] -> [T,H,d]; fp32 math (mha.py:9-103)."""
+    """query [T,H,d], key/value [L,Hkv,d] -> [H,T,d] (the layout mha.py:56,103 returns);
+    fp32 math (mha.py:9-103)."""
     q, k, v = query.float(), key.float(), value.float()
     T, H, dq = q.shape
     L, Hkv, _ = k.shape
@@ -29,20 +30,22 @@ def attention(query, key, value, attn_mask=None):
     if attn_mask is not None:
         scores = scores + attn_mask
     p = torch.softmax(scores, dim=-1)
-    return torch.matmul(p, v).transpose(0, 1)
+    return torch.matmul(p, v)
 
 
 def paged_decode_attention(kv, q):
     """kv: oracle.kv_cache.PagedKV, q: fp32 array [B,H,d] -> fp32 [B,H,d].
     A sequence of length 0 yields zeros."""
+    from .kv_cache import gather_all
     B, H, d = q.shape
     out = np.zeros((B, H, d), dtype=np.float32)
+    Ks, Vs = gather_all(kv)
     for b in range(B):
         if kv.seq_lens[b] == 0:
             continue
-        K, V = kv.gather(b)
+        K, V = Ks[b], Vs[b]
         o = attention(torch.from_numpy(q[b:b + 1]), torch.from_numpy(K), torch.from_numpy(V))
-        out[b] = o[0].numpy()
+        out[b] = o[:, 0].numpy()
     return out
 
 

@@ -208,3 +208,52 @@ def append_vectorized(kv, k, v):
         vr[:, :, :n].reshape(-1, H, d // 2, PAGE)[pg, hh, :, sl] = bv
         vr[:, :, n:].reshape(-1, H, d // 16, PAGE)[pg, hh, :, sl] = sbv
     kv.seq_lens += T
+
+
+def dequant_pools(kv, batch_of_page=None):
+    """Vectorised dequantisation of whole pools -> K, V fp32 [num_pages, Hkv, 16, d].
+    fp8 needs the owning sequence of every page: batch_of_page int [num_pages] (-1 = free)."""
+    P, H, d = kv.k_pool.shape[0], kv.hkv, kv.d
+    if kv.fmt == FMT_INT8:
+        n = PAGE * d
+        K = kv.k_pool[:, :, :n].reshape(P, H, PAGE, d).view(np.int8).astype(np.float32)
+        K *= np.ascontiguousarray(kv.k_pool[:, :, n:]).view(np.float32).reshape(P, H, PAGE, 1)
+        V = kv.v_pool[:, :, :n].reshape(P, H, d, PAGE).view(np.int8).astype(np.float32).transpose(0, 1, 3, 2)
+        V = V * np.ascontiguousarray(kv.v_pool[:, :, n:]).view(np.float32).reshape(P, H, PAGE, 1)
+        return K, V
+    if kv.fmt == FMT_FP8:
+        bop = np.asarray(batch_of_page)
+        ks = np.where(bop[:, None] >= 0, kv.k_scale[np.maximum(bop, 0)], 0).astype(np.float32)   # [P, H]
+        vs = np.where(bop[:, None] >= 0, kv.v_scale[np.maximum(bop, 0)], 0).astype(np.float32)
+        K = e4m3_decode(kv.k_pool.reshape(P, H, PAGE, d)) * ks[:, :, None, None]
+        V = e4m3_decode(kv.v_pool.reshape(P, H, d, PAGE)).transpose(0, 1, 3, 2) * vs[:, :, None, None]
+        return np.nan_to_num(K), np.nan_to_num(V)
+    n = PAGE * d // 2
+    kb = kv.k_pool[:, :, :n].reshape(P, H, PAGE, d // 2)
+    kcodes = np.stack([kb & 15, kb >> 4], axis=-1).reshape(P, H, PAGE, d)
+    K = nvfp4_decode(kcodes, kv.k_pool[:, :, n:].reshape(P, H, PAGE, d // 16))
+    vb = kv.v_pool[:, :, :n].reshape(P, H, d // 2, PAGE).transpose(0, 1, 3, 2)          # [P,H,16,d/2]
+    vcodes = np.stack([vb & 15, vb >> 4], axis=-1).reshape(P, H, PAGE, d)
+    V = nvfp4_decode(vcodes, kv.v_pool[:, :, n:].reshape(P, H, d // 16, PAGE).transpose(0, 1, 3, 2))
+    return np.nan_to_num(K), np.nan_to_num(V)
+
+
+def batch_of_page(kv):
+    bop = np.full(kv.k_pool.shape[0], -1, dtype=np.int64)
+    for b in range(kv.block_table.shape[0]):
+        npg = (int(kv.seq_lens[b]) + PAGE - 1) // PAGE
+        bop[kv.block_table[b, :npg]] = b
+    return bop
+
+
+def gather_all(kv):
+    """Dequantised caches of every sequence: lists K[b], V[b] of fp32 [L_b, Hkv, d]."""
+    Kp, Vp = dequant_pools(kv, batch_of_page(kv) if kv.fmt == FMT_FP8 else None)
+    Ks, Vs = [], []
+    for b in range(kv.block_table.shape[0]):
+        L = int(kv.seq_lens[b])
+        npg = (L + PAGE - 1) // PAGE
+        pg = kv.block_table[b, :npg]
+        Ks.append(Kp[pg].transpose(0, 2, 1, 3).reshape(npg * PAGE, kv.hkv, kv.d)[:L])
+        Vs.append(Vp[pg].transpose(0, 2, 1, 3).reshape(npg * PAGE, kv.hkv, kv.d)[:L])
+    return Ks, Vs

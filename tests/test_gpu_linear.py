@@ -1,0 +1,112 @@
+"""LinearCompressed.forward on the GPU against the oracle and the reference's outputs."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import linear as olin
+from oracle import weight_quant as wq
+
+pytestmark = pytest.mark.gpu
+DT = {"fp32": torch.float32, "bf16": torch.bfloat16}
+# stated tolerance: bf16 max-rel-err <= 1e-2 (relative to the largest |y|); fp32 1e-4
+TOL = {"fp32": 1e-4, "bf16": 1e-2}
+
+
+def rel_err(y, ref):
+    return ((y.float() - ref.float()).abs().max() / ref.float().abs().max()).item()
+
+
+@pytest.mark.parametrize("name", ["fp32", "bf16"])
+@pytest.mark.parametrize("simt", [True, False])
+def test_reference_fixture(cuda, golden, name, simt):
+    from transformer_surgeon_b200 import ops
+    g = golden("linear.npz")
+    dt = DT[name]
+    x = g[f"x_{name}"].to(cuda)
+    lin = ops.PackedLinear(ops.Factor.dense(g["W"].to(dt).to(cuda)), None, g["bias"].to(dt).to(cuda), dt)
+    lin.force_simt = simt
+    y = lin(x)
+    assert y.shape == (2, 5, 192)
+    assert rel_err(y.cpu(), g[f"y_full_{name}"]) < TOL[name]
+    lin = ops.PackedLinear(ops.Factor.dense(g[f"US_{name}"].to(cuda)), ops.Factor.dense(g[f"V_{name}"].to(cuda)), None, dt)
+    lin.force_simt = simt
+    assert rel_err(lin(x).cpu(), g[f"y_lrd_{name}"]) < TOL[name]
+    for p in (8, 4, "binary"):
+        fu = ops.Factor.from_codes(g[f"qu_{p}_{name}"].to(cuda), g[f"su_{p}_{name}"].to(cuda), p)
+        fv = ops.Factor.from_codes(g[f"qv_{p}_{name}"].to(cuda), g[f"sv_{p}_{name}"].to(cuda), p)
+        lin = ops.PackedLinear(fu, fv, None, dt)
+        lin.force_simt = simt
+        assert rel_err(lin(x).cpu(), g[f"y_lrd_q{p}_{name}"]) < TOL[name], (p, name)
+
+
+def _case(M, K, N, r, p, name, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    dt = DT[name]
+    x = torch.randn(M, K, generator=g).to(dt)
+    if r:
+        U = (torch.randn(N, r, generator=g) * 0.05).to(dt)
+        V = (torch.randn(r, K, generator=g) * 0.05).to(dt)
+    else:
+        U = (torch.randn(N, K, generator=g) * 0.05).to(dt)
+        V = None
+    b = (torch.randn(N, generator=g) * 0.1).to(dt)
+    return x, U, V, b
+
+
+@pytest.mark.parametrize("name", ["bf16", "fp32"])
+@pytest.mark.parametrize("p", [8, 4, 2, "binary", None])
+@pytest.mark.parametrize("M,K,N,r", [(1, 256, 192, 64), (5, 896, 128, 0), (16, 512, 320, 128), (33, 1024, 256, 0),
+                                     (128, 1024, 512, 256), (200, 320, 72, 64)])
+def test_against_oracle(cuda, name, p, M, K, N, r):
+    from transformer_surgeon_b200 import ops
+    dt = DT[name]
+    x, U, V, b = _case(M, K, N, r, p, name)
+    if p is None:
+        fu, fv = ops.Factor.dense(U.to(cuda)), (ops.Factor.dense(V.to(cuda)) if r else None)
+        Ud, Vd = U, V
+    else:
+        fu = ops.Factor.quantize(U.to(cuda), p)
+        fv = ops.Factor.quantize(V.to(cuda), p) if r else None
+        qu, su = wq.quantize_vanilla(U.float().numpy(), p, 1e-6, "per_channel", name)
+        assert np.array_equal(fu.codes().cpu().numpy(), qu)
+        Ud = torch.from_numpy(wq.dequantize(qu, su, name)).to(dt)
+        Vd = None
+        if r:
+            qv, sv = wq.quantize_vanilla(V.float().numpy(), p, 1e-6, "per_channel", name)
+            Vd = torch.from_numpy(wq.dequantize(qv, sv, name)).to(dt)
+    ref32 = olin.linear_compressed_fp32(x, Ud, b, Vd)
+    for simt in (True, False):
+        lin = ops.PackedLinear(fu, fv, b.to(cuda), dt)
+        lin.force_simt = simt
+        y = lin(x.to(cuda)).cpu()
+        assert rel_err(y, ref32) < TOL[name], (simt, rel_err(y, ref32))
+
+
+def test_config2_shape_sweep(cuda):
+    """x [M, 4096], W 4096x4096 factored at r in {256, 1024}, 8/4-bit + binary factors, bf16:
+    compared with the dequantized fp32 result (max-rel-err <= 1e-2)."""
+    from transformer_surgeon_b200 import ops
+    g = torch.Generator().manual_seed(2)
+    for r in (256, 1024):
+        U = (torch.randn(4096, r, generator=g) * 0.02).bfloat16().to(cuda)
+        V = (torch.randn(r, 4096, generator=g) * 0.02).bfloat16().to(cuda)
+        for p in (8, 4, "binary"):
+            fu, fv = ops.Factor.quantize(U, p), ops.Factor.quantize(V, p)
+            Ud, Vd = fu.reconstruct(torch.bfloat16).float(), fv.reconstruct(torch.bfloat16).float()
+            lin = ops.PackedLinear(fu, fv, None, torch.bfloat16)
+            for M in (1, 16, 128, 2048):
+                x = torch.randn(M, 4096, generator=g).bfloat16().to(cuda)
+                ref = (x.float() @ Vd.T) @ Ud.T
+                y = lin(x)
+                assert rel_err(y, ref) < 1e-2, (r, p, M, rel_err(y, ref))
+
+
+def test_linearity_and_leading_shape(cuda):
+    from transformer_surgeon_b200 import ops
+    x, U, V, b = _case(6, 512, 128, 64, 4, "fp32")
+    lin = ops.PackedLinear(ops.Factor.quantize(U.to(cuda), 4), ops.Factor.quantize(V.to(cuda), 4), None, torch.float32)
+    xa = x.to(cuda)
+    y1 = lin(xa)
+    y2 = lin((2.0 * xa).reshape(2, 3, 512)).reshape(6, 128)
+    torch.testing.assert_close(2.0 * y1, y2, rtol=1e-5, atol=1e-5)
+    assert lin(xa[:0]).shape == (0, 128)

@@ -1,0 +1,70 @@
+// Shared helpers for the sm_100a kernels behind the C ABI in include/tsb200.h.
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_fp8.h>
+#include <cuda_fp4.h>
+#include <stdint.h>
+#include "../../include/tsb200.h"
+
+namespace tsb {
+
+extern int g_last_cuda_error;
+
+inline int cuda_fail(cudaError_t e) {
+  g_last_cuda_error = (int)e;
+  return TSB200_ERR_CUDA;
+}
+#define TSB_CUDA(expr)                                   \
+  do {                                                   \
+    cudaError_t _e = (expr);                             \
+    if (_e != cudaSuccess) return ::tsb::cuda_fail(_e);  \
+  } while (0)
+#define TSB_LAUNCH_CHECK() TSB_CUDA(cudaPeekAtLastError())
+
+int check_device_cached();   // TSB200_OK iff current device is CC 10.0
+#define TSB_REQUIRE_DEVICE()                    \
+  do {                                          \
+    int _s = ::tsb::check_device_cached();      \
+    if (_s != TSB200_OK) return _s;             \
+  } while (0)
+
+inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
+inline cudaStream_t as_stream(void* s) { return reinterpret_cast<cudaStream_t>(s); }
+
+// ---- dtype access ---------------------------------------------------------------
+template <typename T> __device__ __forceinline__ float to_f32(T v);
+template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+// Round an fp32 value to the precision of T and return it as fp32.
+template <typename T> __device__ __forceinline__ float rnd(float v) { return to_f32<T>(from_f32<T>(v)); }
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+// Sign-extend the low `bits` of v.
+__device__ __forceinline__ int sext(int v, int bits) { return (v << (32 - bits)) >> (32 - bits); }
+
+// Decode code `col` of a packed row (container layouts: see tsb200_pack_codes).
+__device__ __forceinline__ int load_code(const uint8_t* row, int64_t col, int bits) {
+  if (bits == 8) return (int)(int8_t)row[col];
+  if (bits == 4) return sext(row[col >> 1] >> ((col & 1) * 4), 4);
+  if (bits == 2) return sext(row[col >> 2] >> ((col & 3) * 2), 2);
+  return ((row[col >> 3] >> (col & 7)) & 1) * 2 - 1;
+}
+
+}  // namespace tsb

@@ -1,0 +1,62 @@
+// Shared pieces of the paged decode-attention kernels: split bookkeeping, the partial
+// (m, l, acc) workspace layout and the cross-split reduction.
+#pragma once
+#include "common.cuh"
+
+namespace tsb {
+
+// Workspace: float [B][H][S][2 + d]  ->  m, l, acc[d] per (sequence, q head, split).
+struct AttnSplit {
+  int splits;
+};
+
+inline int choose_splits(int64_t B, int hkv, int64_t max_seq_len) {
+  const int64_t base = B * hkv;
+  const int64_t pages = (max_seq_len + 15) / 16;
+  int64_t s = (148 * 8 + base - 1) / (base > 0 ? base : 1);
+  const int64_t cap = pages / 4 > 0 ? pages / 4 : 1;   // at least 4 pages per split
+  if (s > cap) s = cap;
+  if (s < 1) s = 1;
+  if (s > 64) s = 64;
+  return (int)s;
+}
+
+// Pages [begin, end) of sequence with `len` tokens handled by split s of S.
+__device__ __forceinline__ void split_range(int len, int s, int S, int& begin, int& end) {
+  const int pages = (len + 15) >> 4;
+  const int per = (pages + S - 1) / S;
+  begin = s * per;
+  end = min(pages, begin + per);
+}
+
+__device__ __forceinline__ float e4m3_byte_to_f32(unsigned int c) {
+  __half_raw h = __nv_cvt_fp8_to_halfraw((__nv_fp8_storage_t)c, __NV_E4M3);
+  return __half2float(*reinterpret_cast<__half*>(&h));
+}
+__device__ __forceinline__ float e2m1_nibble_to_f32(unsigned int c) {
+  __half_raw h = __nv_cvt_fp4_to_halfraw((__nv_fp4_storage_t)(c & 15), __NV_E2M1);
+  return __half2float(*reinterpret_cast<__half*>(&h));
+}
+
+// Dequantized K / V element (token slot t, element e) of one page record; slow path used
+// by the CUDA-core kernel.  fp8 scale is applied by the caller.
+template <int D>
+__device__ __forceinline__ float k_elem(const uint8_t* __restrict__ rec, int fmt, int t, int e) {
+  if (fmt == TSB200_KV_INT8)
+    return (float)(int8_t)rec[t * D + e] * reinterpret_cast<const float*>(rec + 16 * D)[t];
+  if (fmt == TSB200_KV_FP8) return e4m3_byte_to_f32(rec[t * D + e]);
+  const unsigned b = rec[t * (D / 2) + (e >> 1)];
+  return e2m1_nibble_to_f32(b >> ((e & 1) * 4)) * e4m3_byte_to_f32(rec[16 * (D / 2) + t * (D / 16) + (e >> 4)]);
+}
+template <int D>
+__device__ __forceinline__ float v_elem(const uint8_t* __restrict__ rec, int fmt, int t, int e) {
+  if (fmt == TSB200_KV_INT8)
+    return (float)(int8_t)rec[e * 16 + t] * reinterpret_cast<const float*>(rec + 16 * D)[t];
+  if (fmt == TSB200_KV_FP8) return e4m3_byte_to_f32(rec[e * 16 + t]);
+  const unsigned b = rec[(e >> 1) * 16 + t];
+  return e2m1_nibble_to_f32(b >> ((e & 1) * 4)) * e4m3_byte_to_f32(rec[16 * (D / 2) + (e >> 4) * 16 + t]);
+}
+
+int validate_kv(const tsb200_kv_desc* kv, bool need_table);
+
+}  // namespace tsb

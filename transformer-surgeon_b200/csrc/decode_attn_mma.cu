@@ -1,0 +1,305 @@
+// Split-K paged decode attention on tensor cores (int8 and FP8-e4m3 pages).
+//
+// Replaces transformersurgeon/blocks/mha.py:9-103 (attention(): GQA, softmax, @V) for the
+// decode step.  One CTA = one (sequence, kv head, split); its 4 warps take pages
+// round-robin.  Each warp streams its pages through a private ring of shared-memory
+// stages with 16-byte cp.async copies (K record placed with an XOR swizzle so the
+// fragment reads are bank-conflict free), and computes, per 16-token page,
+//     S^T[token, head] = K_page . Q^T          (8 x mma.m16n8k16, f16 in / f32 acc)
+//     online softmax over tokens per head       (warp shuffles over the token lanes)
+//     O^T[dim, head]  += V^T_page . P^T         (8 x mma.m16n8k16)
+// so the whole GQA group (<= 8 query heads) shares one read of the page.  Codes are
+// widened to f16 in registers (exact for e4m3 and int8); scales are applied in fp32.
+// Partials (m, l, acc) go to the workspace; decode_attn_reduce_kernel merges splits.
+#include "decode_attn_common.cuh"
+
+namespace tsb {
+
+template <typename T, int D> int launch_reduce(const float* ws, int64_t BH, int S, void* out, cudaStream_t st);
+int validate_attn_args(const tsb200_kv_desc* kv, const void* q, void* out, int dtype, int64_t B, int H,
+                       int64_t max_seq_len, void* workspace, size_t workspace_bytes, bool& noop);
+
+namespace {
+
+constexpr int kWarps = 4;
+constexpr int kStages = 4;
+
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc) {
+  const unsigned s = (unsigned)__cvta_generic_to_shared(smem_dst);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(s), "l"(gsrc) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory"); }
+
+__device__ __forceinline__ void mma16816(float (&c)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3, unsigned b0, unsigned b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ unsigned movmatrix_trans(unsigned a) {
+  unsigned d;
+  asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;\n" : "=r"(d) : "r"(a));
+  return d;
+}
+__device__ __forceinline__ unsigned pack_h2(float lo, float hi) {
+  __half2 h = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<unsigned*>(&h);
+}
+// Two 8-bit codes (low 16 bits of w) -> f16x2, low byte in the low half.
+template <int FMT> __device__ __forceinline__ unsigned widen2(unsigned w16) {
+  if (FMT == TSB200_KV_FP8) {
+    __half2_raw r = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(w16 & 0xffffu), __NV_E4M3);
+    return (unsigned)r.x | ((unsigned)r.y << 16);
+  } else {
+    // int8 -> f16: (code ^ 0x80) | 0x6400 is the f16 1024 + 128 + code; subtract 1152.
+    const unsigned u = (w16 ^ 0x8080u);
+    unsigned v = __byte_perm(u, 0x64646464u, 0x4140);   // {0x64, b1, 0x64, b0}
+    const __half2 bias = __half2half2(__ushort_as_half((unsigned short)0x6480));
+    __half2 h = __hsub2(*reinterpret_cast<__half2*>(&v), bias);
+    return *reinterpret_cast<unsigned*>(&h);
+  }
+}
+// Row swizzle of the K record (rows of 128 bytes = 8 chunks): adjacent token rows land in
+// different halves of the bank space, rows two apart in different chunks.
+__device__ __forceinline__ int kswz(int row) { return ((row & 1) << 2) | ((row >> 1) & 3); }
+
+template <int D> __device__ __forceinline__ int k_phys_chunk(int row, int j) {
+  return row * (D / 16) + (D == 128 ? (j ^ kswz(row)) : j);
+}
+
+template <typename T, int D, int FMT>
+__global__ void __launch_bounds__(kWarps * 32)
+decode_attn_mma_kernel(tsb200_kv_desc kv, const T* __restrict__ q, int H, float sm_scale, int64_t max_seq_len, int S,
+                       float* __restrict__ ws) {
+  constexpr int REC = (FMT == TSB200_KV_INT8) ? 16 * D + 64 : 16 * D;
+  constexpr int CODE_CHUNKS = D;               // 16*D bytes / 16
+  constexpr int REC_CHUNKS = REC / 16;
+  constexpr int STAGE = 2 * REC;
+  constexpr int NC = D / 16;                    // k-steps of QK, m-tiles of PV
+  extern __shared__ __align__(128) uint8_t smem[];
+
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  const int gid = lane >> 2, tid = lane & 3;
+  const int b = blockIdx.x / kv.hkv, hk = blockIdx.x % kv.hkv, s = blockIdx.y;
+  const int g = H / kv.hkv;
+  const int g0 = blockIdx.z * 8, gn = min(8, g - g0);
+  int len = kv.seq_lens[b];
+  len = len < 0 ? 0 : (len > max_seq_len ? (int)max_seq_len : len);
+  int pb, pe;
+  split_range(len, s, S, pb, pe);
+
+  // Q^T fragments (B operand): this lane holds head g0+gid at the dims of its k-slots.
+  unsigned qf[NC][2];
+  {
+    const bool valid = gid < gn;
+    const T* qp = q + ((int64_t)b * H + hk * g + g0 + (valid ? gid : 0)) * D;
+#pragma unroll
+    for (int c = 0; c < NC; ++c) {
+      const int base = 16 * (tid + 4 * (c >> 2)) + 4 * (c & 3);
+      float f0 = 0.f, f1 = 0.f, f2 = 0.f, f3 = 0.f;
+      if (valid) { f0 = to_f32<T>(qp[base]); f1 = to_f32<T>(qp[base + 1]); f2 = to_f32<T>(qp[base + 2]); f3 = to_f32<T>(qp[base + 3]); }
+      qf[c][0] = pack_h2(f0, f1);
+      qf[c][1] = pack_h2(f2, f3);
+    }
+  }
+  float kscale = 1.f, vscale = 1.f;
+  if (FMT == TSB200_KV_FP8) { kscale = kv.k_scale[b * kv.hkv + hk]; vscale = kv.v_scale[b * kv.hkv + hk]; }
+  const float sc = sm_scale * 1.4426950408889634f * kscale;
+
+  float oacc[NC][4];
+#pragma unroll
+  for (int i = 0; i < NC; ++i) { oacc[i][0] = oacc[i][1] = oacc[i][2] = oacc[i][3] = 0.f; }
+  float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;   // heads 2*tid, 2*tid+1 (log2 domain)
+
+  uint8_t* ring = smem + (size_t)w * kStages * STAGE;
+  const int n_my = (pe - pb - w + kWarps - 1) / kWarps > 0 ? (pe - pb - w + kWarps - 1) / kWarps : 0;
+  const int64_t rec_stride = (int64_t)kv.hkv * REC;
+
+  auto issue = [&](int it) {
+    if (it < n_my) {
+      const int pg = pb + w + it * kWarps;
+      int64_t page = kv.block_table[(int64_t)b * kv.bt_stride + pg];
+      page = page < 0 ? 0 : (page >= kv.num_pages ? kv.num_pages - 1 : page);
+      const uint8_t* kr = kv.k_pool + page * rec_stride + (int64_t)hk * REC;
+      const uint8_t* vr = kv.v_pool + page * rec_stride + (int64_t)hk * REC;
+      uint8_t* sK = ring + (it % kStages) * STAGE;
+      uint8_t* sV = sK + REC;
+#pragma unroll
+      for (int ci = lane; ci < REC_CHUNKS; ci += 32) {
+        int phys = ci;
+        if (ci < CODE_CHUNKS) phys = k_phys_chunk<D>(ci / (D / 16), ci % (D / 16));
+        cp_async16(sK + phys * 16, kr + ci * 16);
+        cp_async16(sV + ci * 16, vr + ci * 16);
+      }
+    }
+    cp_async_commit();
+  };
+
+#pragma unroll
+  for (int i = 0; i < kStages - 1; ++i) issue(i);
+
+  const int r1 = 4 * (gid >> 1) + (gid & 1), r2 = r1 + 2;   // token rows of this lane in S^T
+  for (int it = 0; it < n_my; ++it) {
+    issue(it + kStages - 1);
+    cp_async_wait<kStages - 1>();
+    __syncwarp();
+    const int pg = pb + w + it * kWarps;
+    const int nt = min(16, len - pg * 16);
+    const uint8_t* sK = ring + (it % kStages) * STAGE;
+    const uint8_t* sV = sK + REC;
+
+    // ---- S^T = K . Q^T -----------------------------------------------------------
+    float sacc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int hh = 0; hh < D / 64; ++hh) {
+      const int j = tid + 4 * hh;
+      const uint4 ka = *reinterpret_cast<const uint4*>(sK + k_phys_chunk<D>(r1, j) * 16);
+      const uint4 kb = *reinterpret_cast<const uint4*>(sK + k_phys_chunk<D>(r2, j) * 16);
+      const unsigned wa[4] = {ka.x, ka.y, ka.z, ka.w};
+      const unsigned wb[4] = {kb.x, kb.y, kb.z, kb.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int c = 4 * hh + i;
+        mma16816(sacc, widen2<FMT>(wa[i]), widen2<FMT>(wb[i]), widen2<FMT>(wa[i] >> 16), widen2<FMT>(wb[i] >> 16),
+                 qf[c][0], qf[c][1]);
+      }
+    }
+    // ---- online softmax over the page's tokens (rows) per head (column) -------------
+    float ks1 = 1.f, ks2 = 1.f, vs1 = 1.f, vs2 = 1.f;
+    if (FMT == TSB200_KV_INT8) {
+      const float* ksc = reinterpret_cast<const float*>(sK + 16 * D);
+      const float* vsc = reinterpret_cast<const float*>(sV + 16 * D);
+      ks1 = ksc[r1]; ks2 = ksc[r2]; vs1 = vsc[r1]; vs2 = vsc[r2];
+    }
+    const bool ok1 = r1 < nt, ok2 = r2 < nt;
+    const float s0 = ok1 ? sacc[0] * (sc * ks1) : -INFINITY;
+    const float s1 = ok1 ? sacc[1] * (sc * ks1) : -INFINITY;
+    const float s2 = ok2 ? sacc[2] * (sc * ks2) : -INFINITY;
+    const float s3 = ok2 ? sacc[3] * (sc * ks2) : -INFINITY;
+    float mx0 = fmaxf(s0, s2), mx1 = fmaxf(s1, s3);
+#pragma unroll
+    for (int o = 4; o < 32; o <<= 1) {
+      mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, o));
+      mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, o));
+    }
+    const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);   // finite: token 0 of a page is always valid
+    const float c0 = exp2f(m0 - mn0), c1 = exp2f(m1 - mn1);
+    const float p0 = exp2f(s0 - mn0), p1 = exp2f(s1 - mn1), p2 = exp2f(s2 - mn0), p3 = exp2f(s3 - mn1);
+    l0 = l0 * c0 + (p0 + p2);
+    l1 = l1 * c1 + (p1 + p3);
+    m0 = mn0; m1 = mn1;
+    const unsigned P1 = pack_h2(ok1 ? p0 * vs1 : 0.f, ok1 ? p1 * vs1 : 0.f);
+    const unsigned P2 = pack_h2(ok2 ? p2 * vs2 : 0.f, ok2 ? p3 * vs2 : 0.f);
+    const unsigned pb0 = movmatrix_trans(P1);   // tokens 4*tid, 4*tid+1 of head gid
+    const unsigned pb1 = movmatrix_trans(P2);   // tokens 4*tid+2, 4*tid+3
+    // bytes of this lane's 4 tokens that are inside the sequence (stale slots -> +0)
+    unsigned vmask = 0xffffffffu;
+    if (nt < 16) {
+      const int left = nt - 4 * tid;
+      vmask = left >= 4 ? 0xffffffffu : (left <= 0 ? 0u : (0xffffffffu >> (8 * (4 - left))));
+    }
+    // ---- O^T += V^T . P^T -----------------------------------------------------------
+#pragma unroll
+    for (int mt = 0; mt < NC; ++mt) {
+      const unsigned w1 = *reinterpret_cast<const unsigned*>(sV + (16 * mt + gid) * 16 + 4 * tid) & vmask;
+      const unsigned w2 = *reinterpret_cast<const unsigned*>(sV + (16 * mt + gid + 8) * 16 + 4 * tid) & vmask;
+      oacc[mt][0] *= c0; oacc[mt][1] *= c1; oacc[mt][2] *= c0; oacc[mt][3] *= c1;
+      mma16816(oacc[mt], widen2<FMT>(w1), widen2<FMT>(w2), widen2<FMT>(w1 >> 16), widen2<FMT>(w2 >> 16), pb0, pb1);
+    }
+    __syncwarp();
+  }
+  cp_async_wait<0>();
+  // row sums: add the partial sums of the 8 token lanes
+#pragma unroll
+  for (int o = 4; o < 32; o <<= 1) {
+    l0 += __shfl_xor_sync(0xffffffffu, l0, o);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, o);
+  }
+  __syncthreads();   // every warp is done with its ring; reuse shared memory for the merge
+  float* sm_m = reinterpret_cast<float*>(smem);              // [warps][8]
+  float* sm_l = sm_m + kWarps * 8;                           // [warps][8]
+  float* sm_acc = sm_l + kWarps * 8;                         // [warps][8][D]
+  if (gid == 0) {
+    sm_m[w * 8 + 2 * tid] = m0; sm_m[w * 8 + 2 * tid + 1] = m1;
+    sm_l[w * 8 + 2 * tid] = l0; sm_l[w * 8 + 2 * tid + 1] = l1;
+  }
+#pragma unroll
+  for (int mt = 0; mt < NC; ++mt) {
+    float* a = sm_acc + (size_t)w * 8 * D;
+    a[(2 * tid) * D + 16 * mt + gid] = oacc[mt][0];
+    a[(2 * tid + 1) * D + 16 * mt + gid] = oacc[mt][1];
+    a[(2 * tid) * D + 16 * mt + gid + 8] = oacc[mt][2];
+    a[(2 * tid + 1) * D + 16 * mt + gid + 8] = oacc[mt][3];
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < gn * D; idx += blockDim.x) {
+    const int i = idx / D, e = idx % D;
+    float mm = -INFINITY;
+#pragma unroll
+    for (int ww = 0; ww < kWarps; ++ww) mm = fmaxf(mm, sm_m[ww * 8 + i]);
+    float ll = 0.f, a = 0.f;
+#pragma unroll
+    for (int ww = 0; ww < kWarps; ++ww) {
+      const float mw = sm_m[ww * 8 + i];
+      const float c = mw == -INFINITY ? 0.f : exp2f(mw - mm);
+      ll += sm_l[ww * 8 + i] * c;
+      a += sm_acc[((size_t)ww * 8 + i) * D + e] * c;
+    }
+    float* o = ws + (((int64_t)b * H + hk * g + g0 + i) * S + s) * (2 + D);
+    if (e == 0) { o[0] = mm * 0.6931471805599453f; o[1] = ll; }   // natural-log domain for the reducer
+    o[2 + e] = a * vscale;
+  }
+}
+
+template <typename T, int D, int FMT>
+int launch_mma(const tsb200_kv_desc& kv, const void* q, int H, float sm_scale, int64_t max_seq_len, int S, int64_t B,
+               float* ws, cudaStream_t st) {
+  constexpr int REC = (FMT == TSB200_KV_INT8) ? 16 * D + 64 : 16 * D;
+  constexpr size_t pipe = (size_t)kWarps * kStages * 2 * REC;
+  constexpr size_t merge = (size_t)(kWarps * 16 + kWarps * 8 * D) * sizeof(float);
+  constexpr size_t smem = pipe > merge ? pipe : merge;
+  static bool configured[64] = {false};   // per device: the attribute lives in the device's context
+  int dev = 0;
+  TSB_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return TSB200_ERR_DEVICE;
+  if (!configured[dev]) {
+    TSB_CUDA(cudaFuncSetAttribute(decode_attn_mma_kernel<T, D, FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    configured[dev] = true;
+  }
+  const int g = H / kv.hkv;
+  dim3 grid((unsigned)(B * kv.hkv), (unsigned)S, (unsigned)((g + 7) / 8));
+  decode_attn_mma_kernel<T, D, FMT><<<grid, kWarps * 32, smem, st>>>(kv, (const T*)q, H, sm_scale, max_seq_len, S, ws);
+  TSB_LAUNCH_CHECK();
+  return TSB200_OK;
+}
+
+}  // namespace
+}  // namespace tsb
+
+using namespace tsb;
+
+extern "C" int tsb200_paged_decode_attn(const tsb200_kv_desc* kv, const void* q, void* out, int dtype, int64_t B, int H,
+                                        float sm_scale, int64_t max_seq_len, void* workspace, size_t workspace_bytes,
+                                        void* stream) {
+  TSB_REQUIRE_DEVICE();
+  bool noop;
+  int st = validate_attn_args(kv, q, out, dtype, B, H, max_seq_len, workspace, workspace_bytes, noop);
+  if (st != TSB200_OK || noop) return st;
+  if (kv->format == TSB200_KV_NVFP4)   // NVFP4 pages: CUDA-core kernel until the tensor-core variant lands
+    return tsb200_paged_decode_attn_simt(kv, q, out, dtype, B, H, sm_scale, max_seq_len, workspace, workspace_bytes, stream);
+  cudaStream_t s = as_stream(stream);
+  const int S = choose_splits(B, kv->hkv, max_seq_len);
+  float* ws = (float*)workspace;
+  const int D = kv->head_dim;
+  int r;
+#define TSB_GO(TT, DD, FF) r = launch_mma<TT, DD, FF>(*kv, q, H, sm_scale, max_seq_len, S, B, ws, s); if (r != TSB200_OK) return r; return launch_reduce<TT, DD>(ws, B * H, S, out, s)
+  if (dtype == TSB200_F32) {
+    if (D == 64) { if (kv->format == TSB200_KV_INT8) { TSB_GO(float, 64, TSB200_KV_INT8); } else { TSB_GO(float, 64, TSB200_KV_FP8); } }
+    else { if (kv->format == TSB200_KV_INT8) { TSB_GO(float, 128, TSB200_KV_INT8); } else { TSB_GO(float, 128, TSB200_KV_FP8); } }
+  } else {
+    if (D == 64) { if (kv->format == TSB200_KV_INT8) { TSB_GO(__nv_bfloat16, 64, TSB200_KV_INT8); } else { TSB_GO(__nv_bfloat16, 64, TSB200_KV_FP8); } }
+    else { if (kv->format == TSB200_KV_INT8) { TSB_GO(__nv_bfloat16, 128, TSB200_KV_INT8); } else { TSB_GO(__nv_bfloat16, 128, TSB200_KV_FP8); } }
+  }
+#undef TSB_GO
+}

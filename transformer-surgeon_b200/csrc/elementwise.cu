@@ -1,0 +1,169 @@
+// Small decoder ops: RoPE (half-split), residual-add + RMSNorm (two variants), SwiGLU.
+// Each op rounds to the activation dtype at the same points as the chain of torch ops
+// it replaces, so bf16 results track the reference closely.
+#include "common.cuh"
+
+namespace tsb {
+
+// x [B, T, heads, d]; one thread per (token, head, i < d/2).
+template <typename T>
+__global__ void rope_kernel(T* __restrict__ x, int64_t B, int64_t Tn, int heads, int d, const int32_t* __restrict__ pos0,
+                            const float* __restrict__ cosT, const float* __restrict__ sinT, int64_t rope_rows) {
+  const int half = d / 2;
+  const int64_t total = B * Tn * heads * half;
+  for (int64_t idx = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; idx < total; idx += (int64_t)gridDim.x * blockDim.x) {
+    const int i = (int)(idx % half);
+    const int64_t th = idx / half;           // (b, t, head)
+    const int64_t bt = th / heads;
+    const int64_t b = bt / Tn, t = bt - b * Tn;
+    int64_t pos = (pos0 ? (int64_t)pos0[b] : 0) + t;
+    pos = pos < 0 ? 0 : (pos >= rope_rows ? rope_rows - 1 : pos);
+    const float c = rnd<T>(cosT[pos * half + i]);
+    const float s = rnd<T>(sinT[pos * half + i]);
+    T* p = x + th * d;
+    const float xr = to_f32<T>(p[i]), xi = to_f32<T>(p[i + half]);
+    const float yr = __fsub_rn(rnd<T>(__fmul_rn(xr, c)), rnd<T>(__fmul_rn(xi, s)));
+    const float yi = __fadd_rn(rnd<T>(__fmul_rn(xr, s)), rnd<T>(__fmul_rn(xi, c)));
+    p[i] = from_f32<T>(yr);
+    p[i + half] = from_f32<T>(yi);
+  }
+}
+
+__device__ __forceinline__ float block_reduce_sum(float v, float* sh) {
+  v = warp_sum(v);
+  int w = threadIdx.x >> 5, l = threadIdx.x & 31, nw = blockDim.x >> 5;
+  if (l == 0) sh[w] = v;
+  __syncthreads();
+  float r = (l < nw) ? sh[l] : 0.f;
+  r = warp_sum(r);
+  __syncthreads();
+  return r;
+}
+__device__ __forceinline__ float block_reduce_max(float v, float* sh) {
+  v = warp_max(v);
+  int w = threadIdx.x >> 5, l = threadIdx.x & 31, nw = blockDim.x >> 5;
+  if (l == 0) sh[w] = v;
+  __syncthreads();
+  float r = (l < nw) ? sh[l] : 0.f;
+  r = warp_max(r);
+  __syncthreads();
+  return r;
+}
+
+// One CTA per row.
+template <typename T>
+__global__ void add_rmsnorm_kernel(T* __restrict__ residual, const T* __restrict__ delta, const T* __restrict__ w,
+                                   T* __restrict__ y, int64_t hidden, float eps, int variant) {
+  __shared__ float sh[32];
+  const int64_t row = blockIdx.x;
+  T* r = residual + row * hidden;
+  const T* dl = delta ? delta + row * hidden : nullptr;
+  T* yo = y + row * hidden;
+  float ss = 0.f, mx = 0.f;
+  for (int64_t c = threadIdx.x; c < hidden; c += blockDim.x) {
+    float v = to_f32<T>(r[c]);
+    if (dl) {
+      v = rnd<T>(__fadd_rn(v, to_f32<T>(dl[c])));
+      r[c] = from_f32<T>(v);
+    }
+    ss += v * v;
+    mx = fmaxf(mx, fabsf(v));
+  }
+  if (variant == 0) {
+    const float var = block_reduce_sum(ss, sh) / (float)hidden;
+    const float inv = 1.0f / sqrtf(var + eps);
+    for (int64_t c = threadIdx.x; c < hidden; c += blockDim.x) {
+      const float v = to_f32<T>(r[c]);
+      yo[c] = from_f32<T>(__fmul_rn(to_f32<T>(w[c]), rnd<T>(__fmul_rn(v, inv))));
+    }
+  } else {
+    mx = fmaxf(block_reduce_max(mx, sh), 1.0f);
+    float s2 = 0.f;
+    for (int64_t c = threadIdx.x; c < hidden; c += blockDim.x) {
+      const float v = rnd<T>(__fdiv_rn(to_f32<T>(r[c]), mx));
+      s2 += rnd<T>(__fmul_rn(v, v));
+    }
+    const float var = rnd<T>(block_reduce_sum(s2, sh) / (float)hidden);
+    const float inv = rnd<T>(1.0f / sqrtf(rnd<T>(__fadd_rn(var, 1e-5f))));
+    for (int64_t c = threadIdx.x; c < hidden; c += blockDim.x) {
+      const float v = rnd<T>(__fdiv_rn(to_f32<T>(r[c]), mx));
+      yo[c] = from_f32<T>(__fmul_rn(to_f32<T>(w[c]), rnd<T>(__fmul_rn(v, inv))));
+    }
+  }
+}
+
+template <typename T>
+__global__ void swiglu_kernel(const T* __restrict__ gate, const T* __restrict__ up, T* __restrict__ y, int64_t M, int64_t n,
+                              int64_t gs, int64_t us, int64_t ys) {
+  const int64_t total = M * n;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t m = i / n, c = i - m * n;
+    const float g = to_f32<T>(gate[m * gs + c]);
+    const float u = to_f32<T>(up[m * us + c]);
+    const float a = rnd<T>(g / (1.0f + expf(-g)));
+    y[m * ys + c] = from_f32<T>(__fmul_rn(a, u));
+  }
+}
+
+inline int egrid(int64_t n) {
+  int64_t g = (n + 255) / 256;
+  return (int)(g < 1 ? 1 : (g > 148 * 8 ? 148 * 8 : g));
+}
+}  // namespace tsb
+
+using namespace tsb;
+
+extern "C" {
+
+int tsb200_rope(void* x, int dtype, int64_t B, int64_t T, int heads, int head_dim, const int32_t* pos0,
+                const float* rope_cos, const float* rope_sin, int64_t rope_rows, void* stream) {
+  TSB_REQUIRE_DEVICE();
+  if (B < 0 || T < 0 || heads <= 0 || head_dim <= 0 || (head_dim & 1)) return TSB200_ERR_ARG;
+  if (B == 0 || T == 0) return TSB200_OK;
+  if (!x || !rope_cos || !rope_sin || rope_rows <= 0) return TSB200_ERR_ARG;
+  const int64_t n = B * T * heads * (head_dim / 2);
+  if (dtype == TSB200_F32)
+    rope_kernel<float><<<egrid(n), 256, 0, as_stream(stream)>>>((float*)x, B, T, heads, head_dim, pos0, rope_cos, rope_sin, rope_rows);
+  else if (dtype == TSB200_BF16)
+    rope_kernel<__nv_bfloat16><<<egrid(n), 256, 0, as_stream(stream)>>>((__nv_bfloat16*)x, B, T, heads, head_dim, pos0, rope_cos, rope_sin, rope_rows);
+  else
+    return TSB200_ERR_UNSUPPORTED;
+  TSB_LAUNCH_CHECK();
+  return TSB200_OK;
+}
+
+int tsb200_add_rmsnorm(void* residual, const void* delta, const void* w, void* y, int dtype, int64_t M,
+                       int64_t hidden, float eps, int variant, void* stream) {
+  TSB_REQUIRE_DEVICE();
+  if (M < 0 || hidden <= 0) return TSB200_ERR_ARG;
+  if (variant != 0 && variant != 1) return TSB200_ERR_UNSUPPORTED;
+  if (M == 0) return TSB200_OK;
+  if (!residual || !w || !y) return TSB200_ERR_ARG;
+  if (M > 0x7fffffffLL) return TSB200_ERR_UNSUPPORTED;
+  if (dtype == TSB200_F32)
+    add_rmsnorm_kernel<float><<<(unsigned)M, 256, 0, as_stream(stream)>>>((float*)residual, (const float*)delta, (const float*)w, (float*)y, hidden, eps, variant);
+  else if (dtype == TSB200_BF16)
+    add_rmsnorm_kernel<__nv_bfloat16><<<(unsigned)M, 256, 0, as_stream(stream)>>>((__nv_bfloat16*)residual, (const __nv_bfloat16*)delta, (const __nv_bfloat16*)w, (__nv_bfloat16*)y, hidden, eps, variant);
+  else
+    return TSB200_ERR_UNSUPPORTED;
+  TSB_LAUNCH_CHECK();
+  return TSB200_OK;
+}
+
+int tsb200_swiglu(const void* gate, const void* up, void* y, int dtype, int64_t M, int64_t n, int64_t gate_stride,
+                  int64_t up_stride, int64_t y_stride, void* stream) {
+  TSB_REQUIRE_DEVICE();
+  if (M < 0 || n < 0) return TSB200_ERR_ARG;
+  if (M == 0 || n == 0) return TSB200_OK;
+  if (!gate || !up || !y || gate_stride < n || up_stride < n || y_stride < n) return TSB200_ERR_ARG;
+  if (dtype == TSB200_F32)
+    swiglu_kernel<float><<<egrid(M * n), 256, 0, as_stream(stream)>>>((const float*)gate, (const float*)up, (float*)y, M, n, gate_stride, up_stride, y_stride);
+  else if (dtype == TSB200_BF16)
+    swiglu_kernel<__nv_bfloat16><<<egrid(M * n), 256, 0, as_stream(stream)>>>((const __nv_bfloat16*)gate, (const __nv_bfloat16*)up, (__nv_bfloat16*)y, M, n, gate_stride, up_stride, y_stride);
+  else
+    return TSB200_ERR_UNSUPPORTED;
+  TSB_LAUNCH_CHECK();
+  return TSB200_OK;
+}
+
+}  // extern "C"
