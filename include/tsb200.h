@@ -76,6 +76,10 @@ int tsb200_quantize_weight(const void* w, int dtype, int64_t rows, int64_t cols,
                            void* workspace, size_t workspace_bytes, void* stream);
 
 /* codes int8 [rows, cols] -> packed [rows, tsb200_packed_row_bytes(cols,bits)].
+ * Container: bits=8 one byte per code in column order; bits<8 little-endian 32-bit words
+ * of per = 32/bits fields covering `per` consecutive columns, pair-interleaved (field
+ * i < per/2 = column 2i of the group, field i >= per/2 = column 2(i-per/2)+1), two's
+ * complement fields (bits=1: 1 -> +1, 0 -> -1); rows zero-padded to 64 columns.
  * bits=1 requires codes in {-1,+1}; *zero_flag (device int32, may be NULL) is set to 1
  * when a zero code was met (the caller then repacks with bits=2). */
 int tsb200_pack_codes(const int8_t* codes, int64_t rows, int64_t cols, int bits,

@@ -11,10 +11,13 @@ with every rounding step written out, so a CUDA kernel can follow it bit for bit
   (transformersurgeon/compression/quantization.py:112,126).
 
 Packed container layouts (defined by this build; the reference keeps no codes):
-  bits=8 : one two's-complement byte per code
-  bits=4 : two codes per byte, low nibble = even column, two's-complement nibbles
-  bits=2 : four codes per byte, bits[2i+1:2i] = column 4j+i, two's complement
-  bits=1 : eight codes per byte, bit i = column 8j+i, 1 -> +1, 0 -> -1 (no zero code)
+  bits=8 : one two's-complement byte per code, natural column order
+  bits<8 : little-endian 32-bit words of per = 32/bits fields; a word covers `per`
+           consecutive columns, "pair-interleaved": field i < per/2 holds column 2i of
+           the group, field i >= per/2 holds column 2(i - per/2) + 1.  (Masking the word
+           with a 16-bit-periodic mask then yields columns (2j, 2j+1) in the two halves
+           of a register: the order a bf16x2 tensor-core operand wants.)
+           bits=4 / 2: two's-complement fields; bits=1: 1 -> +1, 0 -> -1 (no zero code).
 Rows are padded with zero bytes to a multiple of 64 columns.
 """
 import numpy as np
@@ -85,41 +88,50 @@ def container_bits(precision, codes=None):
     return 2
 
 
+def _field_of_column(per):
+    """Position (field index inside its word) of each of the `per` columns of a group."""
+    c = np.arange(per)
+    return (c >> 1) + (c & 1) * (per // 2)
+
+
 def pack_codes(q, bits):
     """int8 codes [rows, cols] -> uint8 [rows, ceil64(cols)*bits/8]."""
     q = np.asarray(q, dtype=np.int8)
     rows, cols = q.shape
     cpad = (cols + 63) // 64 * 64
-    if bits == 1:
-        b = np.zeros((rows, cpad), dtype=np.uint8)
-        b[:, :cols] = (q > 0).astype(np.uint8)
-        return np.packbits(b, axis=1, bitorder="little")
     qq = np.zeros((rows, cpad), dtype=np.int8)
     qq[:, :cols] = q
-    u = qq.view(np.uint8)
     if bits == 8:
-        return u.copy()
-    per = 8 // bits
+        return qq.view(np.uint8).copy()
+    per = 32 // bits
     mask = (1 << bits) - 1
-    u = (u & mask).reshape(rows, cpad // per, per).astype(np.uint32)
-    out = np.zeros((rows, cpad // per), dtype=np.uint32)
-    for i in range(per):
-        out |= u[:, :, i] << (bits * i)
-    return out.astype(np.uint8)
+    if bits == 1:
+        u = np.zeros((rows, cpad), dtype=np.uint32)
+        u[:, :cols] = (q > 0)
+    else:
+        u = qq.view(np.uint8).astype(np.uint32) & mask
+    u = u.reshape(rows, cpad // per, per)
+    words = np.zeros((rows, cpad // per), dtype=np.uint32)
+    pos = _field_of_column(per)
+    for c in range(per):
+        words |= u[:, :, c] << np.uint32(bits * int(pos[c]))
+    return words.view(np.uint8).reshape(rows, -1).copy()
 
 
 def unpack_codes(p, bits, cols):
-    p = np.asarray(p, dtype=np.uint8)
+    p = np.ascontiguousarray(p, dtype=np.uint8)
     rows = p.shape[0]
-    if bits == 1:
-        b = np.unpackbits(p, axis=1, bitorder="little")[:, :cols]
-        return (b.astype(np.int8) * 2 - 1).astype(np.int8)
     if bits == 8:
         return p.view(np.int8)[:, :cols].copy()
-    per = 8 // bits
+    per = 32 // bits
     mask = (1 << bits) - 1
-    out = np.zeros((rows, p.shape[1], per), dtype=np.int16)
-    for i in range(per):
-        f = ((p >> (bits * i)) & mask).astype(np.int16)
-        out[:, :, i] = np.where(f >= (1 << (bits - 1)), f - (1 << bits), f)
+    words = p.view(np.uint32)                                    # [rows, groups]
+    pos = _field_of_column(per)
+    out = np.zeros((rows, words.shape[1], per), dtype=np.int16)
+    for c in range(per):
+        f = ((words >> np.uint32(bits * int(pos[c]))) & mask).astype(np.int16)
+        if bits == 1:
+            out[:, :, c] = f * 2 - 1
+        else:
+            out[:, :, c] = np.where(f >= (1 << (bits - 1)), f - (1 << bits), f)
     return out.reshape(rows, -1)[:, :cols].astype(np.int8)

@@ -11,9 +11,10 @@ from oracle import attention as oatt
 pytestmark = pytest.mark.gpu
 DT = {"fp32": torch.float32, "bf16": torch.bfloat16}
 FMTS = ["int8", "fp8", "nvfp4"]
-# decode-attention tolerance: |out - oracle| <= ATOL + RTOL*|oracle| (fp32 accumulation; P and the
-# widened codes pass through f16 in the tensor-core kernel)
-ATOL, RTOL = 3e-3, 1e-2
+# decode-attention tolerance: |out - oracle| <= ATOL_V*max|V| + RTOL*|oracle| (+2e-2*|oracle| for bf16
+# outputs).  Accumulation is fp32; in the tensor-core kernel the softmax weights P pass through f16
+# (relative step 2^-11 = 4.9e-4), which bounds the absolute error by ~5e-4 * sum_t p_t |V_t|.
+ATOL_V, RTOL = 6e-4, 1e-2
 
 
 def outlier_kv(rng, B, T, Hkv, d, dtype):
@@ -131,7 +132,7 @@ def test_decode_attention_against_oracle(cuda, fmt, name, H, Hkv, d, simt):
     ref = oatt.paged_decode_attention(o, q.float().numpy())
     out = ops.paged_decode_attention(g, q.to(cuda), max_seq_len=144, simt=simt).float().cpu().numpy()
     assert np.all(out[4] == 0)
-    tol = ATOL + RTOL * np.abs(ref) + (2e-2 * np.abs(ref) if name == "bf16" else 0)
+    tol = ATOL_V * float(v.float().abs().max()) + RTOL * np.abs(ref) + (2e-2 * np.abs(ref) if name == "bf16" else 0)
     assert np.all(np.abs(out - ref) <= tol), np.abs(out - ref).max()
 
 
@@ -154,7 +155,7 @@ def test_decode_attention_config3_shape(cuda, fmt):
     ref = oatt.paged_decode_attention(o, q.float().numpy())
     out = ops.paged_decode_attention(g, q.to(cuda), max_seq_len=L).float().cpu().numpy()
     out_simt = ops.paged_decode_attention(g, q.to(cuda), max_seq_len=L, simt=True).float().cpu().numpy()
-    tol = ATOL + (RTOL + 2e-2) * np.abs(ref)
+    tol = ATOL_V * float(v.float().abs().max()) + (RTOL + 2e-2) * np.abs(ref)
     assert np.all(np.abs(out - ref) <= tol), np.abs(out - ref).max()
     assert np.all(np.abs(out_simt - ref) <= tol)
 

@@ -59,12 +59,20 @@ __device__ __forceinline__ float warp_sum(float v) {
 // Sign-extend the low `bits` of v.
 __device__ __forceinline__ int sext(int v, int bits) { return (v << (32 - bits)) >> (32 - bits); }
 
-// Decode code `col` of a packed row (container layouts: see tsb200_pack_codes).
+// Sub-byte containers are little-endian 32-bit words of per = 32/bits fields covering `per`
+// consecutive columns in "pair-interleaved" order: field i < per/2 holds column 2i of the
+// group, field i >= per/2 holds column 2(i - per/2) + 1.  Returns the field index of column
+// c (0 <= c < per) inside its word.
+__device__ __host__ __forceinline__ int field_of_column(int c, int per) { return (c >> 1) + (c & 1) * (per >> 1); }
+
+// Decode code `col` of a packed row.
 __device__ __forceinline__ int load_code(const uint8_t* row, int64_t col, int bits) {
   if (bits == 8) return (int)(int8_t)row[col];
-  if (bits == 4) return sext(row[col >> 1] >> ((col & 1) * 4), 4);
-  if (bits == 2) return sext(row[col >> 2] >> ((col & 3) * 2), 2);
-  return ((row[col >> 3] >> (col & 7)) & 1) * 2 - 1;
+  const int per = 32 / bits;
+  const unsigned w = reinterpret_cast<const unsigned*>(row)[col / per];
+  const unsigned f = (w >> (bits * field_of_column((int)(col % per), per))) & ((1u << bits) - 1u);
+  if (bits == 1) return (int)f * 2 - 1;
+  return sext((int)f, bits);
 }
 
 }  // namespace tsb

@@ -37,18 +37,29 @@ __device__ __forceinline__ void load8(const uint8_t* __restrict__ row, int64_t k
       wv[i] = (float)(int8_t)(a.x >> (8 * i));
       wv[4 + i] = (float)(int8_t)(a.y >> (8 * i));
     }
-  } else if (BITS == 4) {
+  } else if (BITS == 4) {          // one word = 8 columns: field j -> column 2j, field j+4 -> column 2j+1
     const unsigned a = *reinterpret_cast<const unsigned*>(row + k0 / 2);
 #pragma unroll
-    for (int i = 0; i < 8; ++i) wv[i] = (float)sext((int)(a >> (4 * i)), 4);
-  } else if (BITS == 2) {
-    const unsigned a = *reinterpret_cast<const uint16_t*>(row + k0 / 4);
+    for (int j = 0; j < 4; ++j) {
+      wv[2 * j] = (float)sext((int)(a >> (4 * j)), 4);
+      wv[2 * j + 1] = (float)sext((int)(a >> (4 * j + 16)), 4);
+    }
+  } else if (BITS == 2) {          // one word = 16 columns; k0 % 16 in {0, 8}
+    const unsigned a = *reinterpret_cast<const unsigned*>(row + (k0 / 16) * 4);
+    const int j0 = (int)(k0 % 16) / 2;
 #pragma unroll
-    for (int i = 0; i < 8; ++i) wv[i] = (float)sext((int)(a >> (2 * i)), 2);
-  } else {
-    const unsigned a = row[k0 / 8];
+    for (int j = 0; j < 4; ++j) {
+      wv[2 * j] = (float)sext((int)(a >> (2 * (j0 + j))), 2);
+      wv[2 * j + 1] = (float)sext((int)(a >> (2 * (j0 + j) + 16)), 2);
+    }
+  } else {                         // one word = 32 columns; k0 % 32 in {0, 8, 16, 24}
+    const unsigned a = *reinterpret_cast<const unsigned*>(row + (k0 / 32) * 4);
+    const int j0 = (int)(k0 % 32) / 2;
 #pragma unroll
-    for (int i = 0; i < 8; ++i) wv[i] = (float)(int)(((a >> i) & 1u) * 2u) - 1.0f;
+    for (int j = 0; j < 4; ++j) {
+      wv[2 * j] = (float)(int)(((a >> (j0 + j)) & 1u) * 2u) - 1.0f;
+      wv[2 * j + 1] = (float)(int)(((a >> (j0 + j + 16)) & 1u) * 2u) - 1.0f;
+    }
   }
 }
 
@@ -167,10 +178,15 @@ using namespace tsb;
 
 extern "C" {
 
+// Workspace layout shared by both kernels: [0, 256) status word (zeroed once by the caller;
+// a kernel that gave up on a bounded wait stores a non-zero code there), then the rank-r
+// intermediate [M, rank] in the act dtype, then an fp32 [M, max(rank, out)] split-K buffer.
 size_t tsb200_linear_workspace_bytes(const tsb200_linear_desc* d, int64_t M) {
-  if (!d || M <= 0 || d->rank <= 0) return 256;
+  if (!d || M <= 0) return 256;
   const size_t elt = d->act_dtype == TSB200_F32 ? 4 : 2;
-  return ((size_t)M * (size_t)d->rank * elt + 255) / 256 * 256 + 256;
+  const size_t h = ((size_t)M * (size_t)(d->rank > 0 ? d->rank : 0) * elt + 255) / 256 * 256;
+  const size_t nmax = (size_t)(d->rank > d->out_features ? d->rank : d->out_features);
+  return 256 + h + ((size_t)M * nmax * 4 + 255) / 256 * 256;
 }
 
 int tsb200_linear_simt(const tsb200_linear_desc* d, const void* x, void* y, int64_t M, void* workspace,
@@ -185,11 +201,12 @@ int tsb200_linear_simt(const tsb200_linear_desc* d, const void* x, void* y, int6
   if (d->rank > 0) {
     if (!workspace || !aligned(workspace, 16)) return TSB200_ERR_ARG;
     if (workspace_bytes < tsb200_linear_workspace_bytes(d, M)) return TSB200_ERR_WORKSPACE;
+    void* h = (uint8_t*)workspace + 256;
     st = d->act_dtype == TSB200_F32
-             ? launch_bits<float>(d->v_bits, d->v, d->v_scale, nullptr, x, workspace, M, d->in_features, d->rank, s)
-             : launch_bits<__nv_bfloat16>(d->v_bits, d->v, d->v_scale, nullptr, x, workspace, M, d->in_features, d->rank, s);
+             ? launch_bits<float>(d->v_bits, d->v, d->v_scale, nullptr, x, h, M, d->in_features, d->rank, s)
+             : launch_bits<__nv_bfloat16>(d->v_bits, d->v, d->v_scale, nullptr, x, h, M, d->in_features, d->rank, s);
     if (st != TSB200_OK) return st;
-    in = workspace;
+    in = h;
     K = d->rank;
   }
   return d->act_dtype == TSB200_F32

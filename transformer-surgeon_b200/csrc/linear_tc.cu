@@ -1,9 +1,484 @@
-// Tensor-core (tcgen05) path of LinearCompressed.forward.  Placeholder dispatch until the
-// kernel is enabled: reports every shape as unsupported so the CUDA-core kernel runs.
+// LinearCompressed.forward on the 5th-generation tensor cores (tcgen05 / TMEM / TMA).
+//
+// Replaces transformersurgeon/blocks/linear_compressed.py:96-100 for bf16 activations:
+//   Y[M, N] = (X[M, K] . Wq[N, K]^T) * scale[N] + bias[N]
+// called once for the V factor (N = rank, result rounded to bf16 = the rank-r intermediate)
+// and once for the U factor.  The GEMM is issued "swapped": the weight tile is the MMA A
+// operand (M_mma = 128 weight rows), the activations are the B operand (N_mma = token tile),
+// so decode batches of 16..128 tokens still fill the 128-row datapath, and the per-row
+// dequantization scale and bias are per-TMEM-lane constants in the epilogue.
+//
+// Warp roles (6 warps):
+//   warp 0      TMA producer: activation tile (TN x 64 bf16, 128-byte swizzle) and the packed
+//               weight tile (128 rows x 64 codes, raw bytes) per k-block into a 4-stage ring
+//   warp 1      TMEM allocation; one lane issues tcgen05.mma (4 x K=16 per k-block) and
+//               tcgen05.commit to release stages / publish the accumulator
+//   warps 2..5  dequantize: raw codes -> bf16 (exact integers) written in the 128-byte-swizzled
+//               K-major layout the MMA descriptor expects; afterwards the epilogue:
+//               tcgen05.ld the fp32 accumulator (one TMEM lane = one weight row per thread),
+//               scale, bias, store (or fp32 atomics into a split-K buffer)
+// Every mbarrier wait is bounded; on expiry the kernel records a code in the status word
+// (first 4 bytes of the workspace), drains and frees TMEM, and returns.
+#include <cuda.h>
 #include "common.cuh"
 
 namespace tsb {
-int linear_tc(const tsb200_linear_desc*, const void*, void*, int64_t, void*, size_t, cudaStream_t) {
-  return TSB200_ERR_UNSUPPORTED;
+namespace {
+
+constexpr int BM = 128;            // weight rows per CTA = MMA M
+constexpr int BK = 64;             // k per stage: one 128-byte swizzle atom of bf16
+constexpr int NSTG = 4;
+constexpr int kThreads = 192;
+constexpr unsigned kSpinLimit = 1u << 20;   // try_wait attempts before giving up
+
+// ---------------------------------------------------------------- PTX wrappers -----
+__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(unsigned long long* bar, unsigned count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(count) : "memory");
 }
+__device__ __forceinline__ void mbar_expect_tx(unsigned long long* bar, unsigned bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(unsigned long long* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(unsigned long long* bar, unsigned parity) {
+  unsigned ok;
+  asm volatile(
+      "{\n.reg .pred p;\n"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "selp.u32 %0, 1, 0, p;\n}\n"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait.  Returns false (and raises the CTA-wide abort flag) when it gives up.
+__device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned parity, volatile int* abort_flag, int code) {
+  for (unsigned i = 0; i < kSpinLimit; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((i & 63u) == 63u && *abort_flag) return false;
+  }
+  *abort_flag = code;
+  return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, unsigned long long* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n" ::"r"(
+          smem_u32(dst)),
+      "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar))
+      : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc(unsigned* smem_dst, unsigned ncols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(smem_dst)), "r"(ncols) : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(unsigned taddr, unsigned ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void fence_async_proxy() { asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory"); }
+
+__device__ __forceinline__ void umma_bf16(unsigned d_tmem, unsigned long long adesc, unsigned long long bdesc, unsigned idesc,
+                                          unsigned accumulate) {
+  asm volatile(
+      "{\n.reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n" ::"r"(d_tmem),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(unsigned long long* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(unsigned taddr, unsigned (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];\n"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
+
+// Shared-memory matrix descriptor: K-major operand tile with 128-byte swizzle, rows of 128
+// bytes, 8-row groups 1024 bytes apart (stride byte offset), descriptor version 1.
+__device__ __forceinline__ unsigned long long smem_desc_sw128(unsigned saddr) {
+  unsigned long long d = 0;
+  d |= (unsigned long long)((saddr >> 4) & 0x3FFFu);
+  d |= (unsigned long long)1u << 16;                 // leading byte offset (unused for swizzled K-major)
+  d |= (unsigned long long)(1024u >> 4) << 32;       // stride byte offset
+  d |= (unsigned long long)1u << 46;                 // version
+  d |= (unsigned long long)2u << 61;                 // SWIZZLE_128B
+  return d;
+}
+// Instruction descriptor, kind::f16: D=f32, A=B=bf16, both K-major, M=128, N=n.
+__host__ __device__ constexpr unsigned idesc_bf16(int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(n >> 3) << 17) | ((unsigned)(BM >> 4) << 24);
+}
+
+// ---------------------------------------------------------------- dequantization ---
+// Write 8 bf16 (one 16-byte chunk `c` of row `r`) into the swizzled A tile.
+__device__ __forceinline__ void store_chunk(uint8_t* a_tile, int r, int c, uint4 v) {
+  *reinterpret_cast<uint4*>(a_tile + r * 128 + ((c ^ (r & 7)) << 4)) = v;
+}
+__device__ __forceinline__ unsigned bf16x2_sub(unsigned a, unsigned b) {
+  __nv_bfloat162 r = __hsub2(*reinterpret_cast<__nv_bfloat162*>(&a), *reinterpret_cast<__nv_bfloat162*>(&b));
+  return *reinterpret_cast<unsigned*>(&r);
+}
+
+// One thread converts one weight row of the k-block: 64 codes -> 64 bf16.
+template <int BITS>
+__device__ __forceinline__ void dequant_row(const uint8_t* __restrict__ raw_row, uint8_t* a_tile, int r) {
+  if (BITS == 4) {
+    // word = 8 columns, field j -> column 2j, field j+4 -> column 2j+1.  (w ^ 0x88888888) biases every
+    // nibble by +8; 0x4300 | u is the bf16 128 + u; subtracting 136 leaves the signed code.
+    const uint4 q0 = *reinterpret_cast<const uint4*>(raw_row);
+    const uint4 q1 = *reinterpret_cast<const uint4*>(raw_row + 16);
+    const unsigned w[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+      const unsigned t = w[c] ^ 0x88888888u;
+      uint4 o;
+      o.x = bf16x2_sub(((t)&0x000f000fu) | 0x43004300u, 0x43084308u);
+      o.y = bf16x2_sub(((t >> 4) & 0x000f000fu) | 0x43004300u, 0x43084308u);
+      o.z = bf16x2_sub(((t >> 8) & 0x000f000fu) | 0x43004300u, 0x43084308u);
+      o.w = bf16x2_sub(((t >> 12) & 0x000f000fu) | 0x43004300u, 0x43084308u);
+      store_chunk(a_tile, r, c, o);
+    }
+  } else if (BITS == 2) {
+    // word = 16 columns, field j -> column 2j, field j+8 -> column 2j+1; bias +2, subtract 130.
+    const uint4 q0 = *reinterpret_cast<const uint4*>(raw_row);
+    const unsigned w[4] = {q0.x, q0.y, q0.z, q0.w};
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+      const unsigned t = w[g] ^ 0xAAAAAAAAu;
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        uint4 o;
+        o.x = bf16x2_sub(((t >> (8 * h)) & 0x00030003u) | 0x43004300u, 0x43024302u);
+        o.y = bf16x2_sub(((t >> (8 * h + 2)) & 0x00030003u) | 0x43004300u, 0x43024302u);
+        o.z = bf16x2_sub(((t >> (8 * h + 4)) & 0x00030003u) | 0x43004300u, 0x43024302u);
+        o.w = bf16x2_sub(((t >> (8 * h + 6)) & 0x00030003u) | 0x43004300u, 0x43024302u);
+        store_chunk(a_tile, r, 2 * g + h, o);
+      }
+    }
+  } else {  // BITS == 8: natural byte order; int8 -> f32 by the 2^23 trick, then pack to bf16x2
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+      const uint2 q = *reinterpret_cast<const uint2*>(raw_row + 8 * c);
+      const unsigned t0 = q.x ^ 0x80808080u, t1 = q.y ^ 0x80808080u;
+      float f[8];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        f[i] = __uint_as_float(0x4B000000u | ((t0 >> (8 * i)) & 0xffu)) - 8388736.0f;       // 2^23 + 128
+        f[4 + i] = __uint_as_float(0x4B000000u | ((t1 >> (8 * i)) & 0xffu)) - 8388736.0f;
+      }
+      uint4 o;
+      __nv_bfloat162 p;
+      p = __floats2bfloat162_rn(f[0], f[1]); o.x = *reinterpret_cast<unsigned*>(&p);
+      p = __floats2bfloat162_rn(f[2], f[3]); o.y = *reinterpret_cast<unsigned*>(&p);
+      p = __floats2bfloat162_rn(f[4], f[5]); o.z = *reinterpret_cast<unsigned*>(&p);
+      p = __floats2bfloat162_rn(f[6], f[7]); o.w = *reinterpret_cast<unsigned*>(&p);
+      store_chunk(a_tile, r, c, o);
+    }
+  }
+}
+
+struct TcParams {
+  int64_t M, N, K;
+  int kb_total;            // k-blocks of 64 over the whole K
+  int kb_per_split;
+  const float* scale;      // [N] or null (dense)
+  const __nv_bfloat16* bias;  // [N] or null
+  __nv_bfloat16* y;        // [M, N]
+  float* partial;          // [M, N] fp32 accumulation buffer when gridDim.z > 1
+  int* status;             // device status word
+};
+
+template <int TN> struct SmemLayout {
+  static constexpr int kA = BM * 128;            // 16 KB bf16 A tile
+  static constexpr int kX = TN * 128;            // activation tile
+  static constexpr int kRaw = BM * 64;           // raw codes (sized for 8-bit)
+  static constexpr int kStage = kA + kX + kRaw;
+  static constexpr int kBytes = NSTG * kStage + 1024 /*alignment slack*/ + 256 /*barriers*/;
+};
+
+template <int TN, int BITS>
+__global__ void __launch_bounds__(kThreads, 1)
+linear_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, TcParams p) {
+  using L = SmemLayout<TN>;
+  constexpr int RAW_ROW = BITS == 16 ? 0 : BK * BITS / 8;     // bytes of one weight row per k-block
+  constexpr unsigned TX_BYTES = (unsigned)(TN * 128 + (BITS == 16 ? BM * 128 : BM * RAW_ROW));
+  constexpr unsigned TMEM_COLS = TN < 32 ? 32 : TN;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  unsigned long long* bars = reinterpret_cast<unsigned long long*>(smem + NSTG * L::kStage);
+  unsigned long long* full_bar = bars;                 // TMA landed            [NSTG]
+  unsigned long long* ready_bar = bars + NSTG;         // A tile dequantized    [NSTG]
+  unsigned long long* empty_bar = bars + 2 * NSTG;     // MMA done with stage   [NSTG]
+  unsigned long long* acc_bar = bars + 3 * NSTG;       // accumulator complete  [1]
+  unsigned* tmem_slot = reinterpret_cast<unsigned*>(bars + 3 * NSTG + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n0 = blockIdx.x * BM;                      // first weight row of this CTA
+  const int m0 = blockIdx.y * TN;                      // first token
+  const int kb0 = blockIdx.z * p.kb_per_split;
+  const int nkb = min(p.kb_per_split, p.kb_total - kb0);
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < NSTG; ++i) {
+      mbar_init(&full_bar[i], 1);
+      mbar_init(&ready_bar[i], 4);                     // one arrival per dequant warp
+      mbar_init(&empty_bar[i], 1);
+    }
+    mbar_init(acc_bar, 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  }
+  if (warp == 1) tmem_alloc(tmem_slot, TMEM_COLS);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const unsigned tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer -----
+    if (lane == 0) {
+      for (int i = 0; i < nkb; ++i) {
+        const int s = i % NSTG;
+        if (i >= NSTG && !mbar_wait(&empty_bar[s], ((i / NSTG) - 1) & 1, abort_flag, 1)) break;
+        uint8_t* st = smem + s * L::kStage;
+        mbar_expect_tx(&full_bar[s], TX_BYTES);
+        const int kcol = (kb0 + i) * BK;
+        tma_load_2d(st + L::kA, &map_x, kcol, m0, &full_bar[s]);
+        if (BITS == 16) tma_load_2d(st, &map_w, kcol, n0, &full_bar[s]);
+        else tma_load_2d(st + L::kA + L::kX, &map_w, kcol * BITS / 8, n0, &full_bar[s]);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer -------
+    if (lane == 0) {
+      constexpr unsigned idesc = idesc_bf16(TN);
+      bool ok = true;
+      for (int i = 0; i < nkb && ok; ++i) {
+        const int s = i % NSTG;
+        const unsigned ph = (i / NSTG) & 1;
+        ok = mbar_wait(&full_bar[s], ph, abort_flag, 2) && mbar_wait(&ready_bar[s], ph, abort_flag, 3);
+        if (!ok) break;
+        tc_fence_after();
+        uint8_t* st = smem + s * L::kStage;
+        const unsigned long long adesc = smem_desc_sw128(smem_u32(st));
+        const unsigned long long bdesc = smem_desc_sw128(smem_u32(st + L::kA));
+#pragma unroll
+        for (int k = 0; k < BK / 16; ++k)   // +32 bytes (2 x 16-byte units) along K inside the swizzle atom
+          umma_bf16(tmem_base, adesc + 2 * k, bdesc + 2 * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
+        umma_commit(&empty_bar[s]);
+      }
+      if (ok) umma_commit(acc_bar);
+    }
+  } else {
+    // ------------------------------------------------------------ dequant + epilogue
+    const int t = threadIdx.x - 64;                    // 0..127 = weight row inside the tile
+    bool ok = true;
+    for (int i = 0; i < nkb && ok; ++i) {
+      const int s = i % NSTG;
+      const unsigned ph = (i / NSTG) & 1;
+      ok = mbar_wait(&full_bar[s], ph, abort_flag, 4);
+      if (!ok) break;
+      if (BITS != 16) {
+        uint8_t* st = smem + s * L::kStage;
+        dequant_row<BITS == 16 ? 8 : BITS>(st + L::kA + L::kX + t * RAW_ROW, st, t);
+        fence_async_proxy();                           // generic-proxy writes -> visible to the MMA (async proxy)
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&ready_bar[s]);
+    }
+    // epilogue: TMEM lane quarter of this warp is (warp % 4)
+    if (ok && nkb > 0) ok = mbar_wait(acc_bar, 0, abort_flag, 5);
+    if (ok && nkb > 0) {
+      tc_fence_after();
+      const int q = warp & 3;
+      const int row = q * 32 + lane;                   // TMEM lane = weight row in tile
+      const int64_t n = (int64_t)n0 + row;
+      const float sc = (p.scale && n < p.N) ? p.scale[n] : 1.0f;
+      const float bv = (p.bias && n < p.N && blockIdx.z == 0) ? __bfloat162float(p.bias[n]) : 0.f;
+#pragma unroll 1
+      for (int c0 = 0; c0 < TN; c0 += 16) {
+        unsigned r[16];
+        tmem_ld16(tmem_base + ((unsigned)(q * 32) << 16) + (unsigned)c0, r);
+        tmem_ld_wait();
+        if (n < p.N) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const int64_t m = (int64_t)m0 + c0 + j;
+            if (m < p.M) {
+              const float v = __uint_as_float(r[j]) * sc + bv;
+              if (gridDim.z == 1) p.y[m * p.N + n] = __float2bfloat16_rn(v);
+              else atomicAdd(&p.partial[m * p.N + n], v);
+            }
+          }
+        }
+      }
+    }
+  }
+  if (*abort_flag) {
+    // error path only: give copies that may still be in flight a bounded time to land
+    for (int i = 0; i < 200; ++i) __nanosleep(1000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+  if (threadIdx.x == 0 && *abort_flag) atomicMax(p.status, *abort_flag);
+}
+
+// fp32 split-K buffer -> bf16 output.
+__global__ void splitk_finalize_kernel(const float* __restrict__ partial, __nv_bfloat16* __restrict__ y, int64_t n) {
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
+    y[i] = __float2bfloat16_rn(partial[i]);
+}
+
+// ---------------------------------------------------------------- host side --------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  }
+  return fn;
+}
+
+// 2-D row-major tensor [rows, row_bytes or cols]; box = [box_rows, box_inner].
+bool make_map(CUtensorMap* map, CUtensorMapDataType dt, int elt, const void* base, uint64_t inner, uint64_t rows,
+              uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_rows, CUtensorMapSwizzle swz) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  cuuint64_t dims[2] = {inner, rows};
+  cuuint64_t strides[1] = {row_stride_bytes};
+  cuuint32_t box[2] = {box_inner, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  (void)elt;
+  return fn(map, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swz,
+            CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int TN, int BITS>
+int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, const TcParams& p, dim3 grid, cudaStream_t s) {
+  using L = SmemLayout<TN>;
+  static bool configured[64] = {false};
+  int dev = 0;
+  TSB_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return TSB200_ERR_DEVICE;
+  if (!configured[dev]) {
+    TSB_CUDA(cudaFuncSetAttribute(linear_tc_kernel<TN, BITS>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kBytes));
+    configured[dev] = true;
+  }
+  linear_tc_kernel<TN, BITS><<<grid, kThreads, L::kBytes, s>>>(mw, mx, p);
+  TSB_LAUNCH_CHECK();
+  return TSB200_OK;
+}
+
+template <int TN>
+int launch_tc_bits(int bits, const CUtensorMap& mw, const CUtensorMap& mx, const TcParams& p, dim3 grid, cudaStream_t s) {
+  switch (bits) {
+    case 2: return launch_tc<TN, 2>(mw, mx, p, grid, s);
+    case 4: return launch_tc<TN, 4>(mw, mx, p, grid, s);
+    case 8: return launch_tc<TN, 8>(mw, mx, p, grid, s);
+    case 16: return launch_tc<TN, 16>(mw, mx, p, grid, s);
+    default: return TSB200_ERR_UNSUPPORTED;
+  }
+}
+
+// One quantized GEMM: y[M, N] = x[M, K] . W[N, K]^T * scale + bias (bf16 in/out).
+int gemm_tc(const void* W, int bits, const float* scale, const void* bias, const void* x, void* y, int64_t M, int64_t K,
+            int64_t N, float* partial, int* status, cudaStream_t s) {
+  const int tn = M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : 128));
+  CUtensorMap mw, mx;
+  if (bits == 16) {
+    if (!make_map(&mw, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, W, (uint64_t)K, (uint64_t)N, (uint64_t)K * 2, BK, BM,
+                  CU_TENSOR_MAP_SWIZZLE_128B))
+      return TSB200_ERR_CUDA;
+  } else {
+    const uint64_t rb = tsb200_packed_row_bytes(K, bits);
+    if (!make_map(&mw, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, W, rb, (uint64_t)N, rb, (uint32_t)(BK * bits / 8), BM,
+                  CU_TENSOR_MAP_SWIZZLE_NONE))
+      return TSB200_ERR_CUDA;
+  }
+  if (!make_map(&mx, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, x, (uint64_t)K, (uint64_t)M, (uint64_t)K * 2, BK, (uint32_t)tn,
+                CU_TENSOR_MAP_SWIZZLE_128B))
+    return TSB200_ERR_CUDA;
+  const int kb_total = (int)((K + BK - 1) / BK);
+  const int64_t n_tiles = (N + BM - 1) / BM, m_tiles = (M + tn - 1) / tn;
+  // split K until the grid covers the 148 SMs (each split keeps >= 4 k-blocks)
+  int splits = 1;
+  while (n_tiles * m_tiles * splits < 148 && splits * 2 <= 16 && kb_total / (splits * 2) >= 4) splits *= 2;
+  const int kb_per_split = (kb_total + splits - 1) / splits;
+  splits = (kb_total + kb_per_split - 1) / kb_per_split;
+  if (n_tiles > 0x7fffffffLL || m_tiles > 65535) return TSB200_ERR_UNSUPPORTED;
+  TcParams p;
+  p.M = M; p.N = N; p.K = K; p.kb_total = kb_total; p.kb_per_split = kb_per_split;
+  p.scale = scale; p.bias = (const __nv_bfloat16*)bias; p.y = (__nv_bfloat16*)y; p.partial = partial; p.status = status;
+  if (splits > 1) TSB_CUDA(cudaMemsetAsync(partial, 0, (size_t)M * N * sizeof(float), s));
+  dim3 grid((unsigned)n_tiles, (unsigned)m_tiles, (unsigned)splits);
+  int st;
+  switch (tn) {
+    case 16: st = launch_tc_bits<16>(bits, mw, mx, p, grid, s); break;
+    case 32: st = launch_tc_bits<32>(bits, mw, mx, p, grid, s); break;
+    case 64: st = launch_tc_bits<64>(bits, mw, mx, p, grid, s); break;
+    default: st = launch_tc_bits<128>(bits, mw, mx, p, grid, s); break;
+  }
+  if (st != TSB200_OK) return st;
+  if (splits > 1) {
+    const int64_t n = M * N;
+    int64_t g = (n + 255) / 256;
+    if (g > 148 * 8) g = 148 * 8;
+    splitk_finalize_kernel<<<(unsigned)g, 256, 0, s>>>(partial, (__nv_bfloat16*)y, n);
+    TSB_LAUNCH_CHECK();
+  }
+  return TSB200_OK;
+}
+
+bool tc_supported_factor(int bits, int64_t K) { return (bits == 2 || bits == 4 || bits == 8 || bits == 16) && (K % 8) == 0; }
+
+}  // namespace
+
+int linear_tc(const tsb200_linear_desc* d, const void* x, void* y, int64_t M, void* workspace, size_t workspace_bytes,
+              cudaStream_t s) {
+  if (d->act_dtype != TSB200_BF16) return TSB200_ERR_UNSUPPORTED;
+  if (M < 9) return TSB200_ERR_UNSUPPORTED;    // a handful of tokens: the weight-streaming CUDA-core kernel
+  const int64_t ku = d->rank > 0 ? d->rank : d->in_features;
+  if (!tc_supported_factor(d->u_bits, ku)) return TSB200_ERR_UNSUPPORTED;
+  if (d->rank > 0 && !tc_supported_factor(d->v_bits, d->in_features)) return TSB200_ERR_UNSUPPORTED;
+  if (!aligned(x, 16) || !aligned(y, 2)) return TSB200_ERR_ARG;
+  if (!workspace || !aligned(workspace, 256)) return TSB200_ERR_ARG;
+  if (workspace_bytes < tsb200_linear_workspace_bytes(d, M)) return TSB200_ERR_WORKSPACE;
+  uint8_t* ws = (uint8_t*)workspace;
+  int* status = (int*)ws;
+  void* h = ws + 256;
+  const size_t hbytes = ((size_t)M * (size_t)(d->rank > 0 ? d->rank : 0) * 2 + 255) / 256 * 256;
+  float* partial = (float*)(ws + 256 + hbytes);
+  const void* in = x;
+  if (d->rank > 0) {
+    int st = gemm_tc(d->v, d->v_bits, d->v_scale, nullptr, x, h, M, d->in_features, d->rank, partial, status, s);
+    if (st != TSB200_OK) return st;
+    in = h;
+  }
+  return gemm_tc(d->u, d->u_bits, d->u_scale, d->bias, in, y, M, ku, d->out_features, partial, status, s);
+}
+
 }  // namespace tsb

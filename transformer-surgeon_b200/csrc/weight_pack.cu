@@ -102,27 +102,36 @@ __global__ void quantize_rows_kernel(const T* __restrict__ w, int64_t rows, int6
   if (threadIdx.x == 0) scales[r] = scale;
 }
 
-// One thread per packed byte.
+// One thread per packed 32-bit word (bits < 8) or per byte (bits == 8).
 __global__ void pack_codes_kernel(const int8_t* __restrict__ codes, int64_t rows, int64_t cols, int bits,
                                   int64_t row_bytes, uint8_t* __restrict__ packed, int32_t* zero_flag) {
-  const int per = 8 / bits;
-  const int64_t total = rows * row_bytes;
+  if (bits == 8) {
+    const int64_t total = rows * row_bytes;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+      const int64_t r = i / row_bytes, c = i - r * row_bytes;
+      packed[i] = c < cols ? (uint8_t)codes[r * cols + c] : (uint8_t)0;
+    }
+    return;
+  }
+  const int per = 32 / bits;
+  const int64_t row_words = row_bytes / 4;
+  const int64_t total = rows * row_words;
   for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
-    const int64_t r = i / row_bytes, b = i - r * row_bytes;
+    const int64_t r = i / row_words, g = i - r * row_words;
     const int8_t* cr = codes + r * cols;
     unsigned int out = 0;
-#pragma unroll 8
     for (int j = 0; j < per; ++j) {
-      const int64_t c = b * per + j;
-      int q = (c < cols) ? (int)cr[c] : 0;
+      const int64_t c = g * per + j;
+      const int q = (c < cols) ? (int)cr[c] : 0;
+      const int f = field_of_column(j, per);
       if (bits == 1) {
         if (c < cols && q == 0 && zero_flag) *zero_flag = 1;
-        out |= (unsigned)(q > 0) << j;
+        out |= (unsigned)(q > 0) << f;
       } else {
-        out |= ((unsigned)q & ((1u << bits) - 1u)) << (bits * j);
+        out |= ((unsigned)q & ((1u << bits) - 1u)) << (bits * f);
       }
     }
-    packed[i] = (uint8_t)out;
+    reinterpret_cast<unsigned*>(packed)[i] = out;
   }
 }
 
@@ -200,8 +209,8 @@ int tsb200_pack_codes(const int8_t* codes, int64_t rows, int64_t cols, int bits,
   const size_t rb = tsb200_packed_row_bytes(cols > 0 ? cols : 1, bits);
   if (rb == 0) return TSB200_ERR_UNSUPPORTED;
   if (rows == 0 || cols == 0) return TSB200_OK;
-  if (!codes || !packed) return TSB200_ERR_ARG;
-  pack_codes_kernel<<<grid_for(rows * (int64_t)rb, 256), 256, 0, as_stream(stream)>>>(codes, rows, cols, bits, (int64_t)rb, packed, zero_flag);
+  if (!codes || !packed || !aligned(packed, 4)) return TSB200_ERR_ARG;
+  pack_codes_kernel<<<grid_for(rows * (int64_t)(bits == 8 ? rb : rb / 4), 256), 256, 0, as_stream(stream)>>>(codes, rows, cols, bits, (int64_t)rb, packed, zero_flag);
   TSB_LAUNCH_CHECK();
   return TSB200_OK;
 }

@@ -153,7 +153,7 @@ def workspace(device, nbytes):
     """Grow-only scratch buffer per device (PyTorch owns the memory)."""
     buf = _workspaces.get(device)
     if buf is None or buf.numel() < nbytes:
-        buf = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        buf = torch.zeros(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)   # status word starts at 0
         _workspaces[device] = buf
     return buf
 
@@ -198,6 +198,12 @@ class PackedLinear:
         fn = lib.tsb200_linear_simt if self.force_simt else lib.tsb200_linear
         check(fn(C.byref(self.desc), _p(x2), _p(out), M, _p(ws), ws.numel(), _stream()), "tsb200_linear")
         return out.reshape(*lead, self.out_features)
+
+    @staticmethod
+    def device_status(ws=None, device=None):
+        """Status word of a workspace (synchronises): 0, or the code of a bounded wait that ran out."""
+        ws = ws if ws is not None else _workspaces[device]
+        return int(ws[:4].view(torch.int32).item())
 
 
 # ---------------------------------------------------------------- KV cache ---------
