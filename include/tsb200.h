@@ -46,7 +46,10 @@ typedef enum {
   TSB200_W_BF16 = 16, TSB200_W_F32 = 32
 } tsb200_wbits;
 
-typedef enum { TSB200_KV_INT8 = 0, TSB200_KV_FP8 = 1, TSB200_KV_NVFP4 = 2 } tsb200_kv_format;
+typedef enum {
+  TSB200_KV_INT8 = 0, TSB200_KV_FP8 = 1, TSB200_KV_NVFP4 = 2,
+  TSB200_KV_F32 = 3, TSB200_KV_BF16 = 4   /* unquantized pages in the act dtype */
+} tsb200_kv_format;
 
 const char* tsb200_strerror(int status);
 int tsb200_version(void);
@@ -138,6 +141,9 @@ int tsb200_linear_simt(const tsb200_linear_desc* d, const void* x, void* y, int6
  *   V int8  : codes [d][16] (token-minor), then fp32 scale [16]
  *   V fp8   : codes [d][16]
  *   V nvfp4 : codes [d/2][16] (byte = elements 2i | 2i+1<<4 of one token), scales [d/16][16]
+ *   K, V f32 / bf16 (unquantized): values [16][d] in the act dtype
+ * Pools must be zero-filled once when allocated: slots of a page beyond the sequence length
+ * are read (and masked) by the attention kernels and must hold finite bit patterns.
  * ---------------------------------------------------------------------------------- */
 size_t tsb200_kv_record_bytes(int format, int head_dim);
 
@@ -171,8 +177,11 @@ int tsb200_kv_fp8_scales(const void* k, const void* v, int dtype, int64_t B, int
  * rope_cos/rope_sin: fp32 tables [rope_rows, d/2] indexed by position, or NULL (k is
  * appended as given).  Rotation is the half-split form of blocks/rope.py:140-173 with
  * each product and sum rounded to the act dtype.  seq_lens is NOT modified.
- * Positions beyond the block table (>= bt_stride*16) are skipped. */
+ * Positions beyond the block table (>= bt_stride*16) are skipped.
+ * k/v_token_stride: elements between consecutive tokens (0 = hkv*d, i.e. dense), so k and v
+ * may be column slices of one fused [B*T, (H + 2 hkv) d] projection output. */
 int tsb200_kv_append(const tsb200_kv_desc* kv, const void* k, const void* v, int dtype,
+                     int64_t k_token_stride, int64_t v_token_stride,
                      int64_t B, int64_t T, const int32_t* new_lens,
                      const float* rope_cos, const float* rope_sin, int64_t rope_rows,
                      void* stream);
@@ -181,22 +190,24 @@ int tsb200_kv_append(const tsb200_kv_desc* kv, const void* k, const void* v, int
  * Replaces blocks/mha.py:9-103 (attention(): GQA, softmax(q k^T / sqrt(d)) v) for the
  * decode step, reading the quantized pages directly.
  * q, out [B, H, d] act dtype; attends over seq_lens[b] tokens (0 -> zeros).
- * max_seq_len bounds seq_lens (sizes the split grid; lengths above it are clamped). */
+ * max_seq_len bounds seq_lens (sizes the split grid; lengths above it are clamped).
+ * q_batch_stride: elements between consecutive sequences of q (0 = H*d); out is dense. */
 size_t tsb200_paged_decode_attn_workspace_bytes(int64_t B, int H, int head_dim, int64_t max_seq_len);
 int tsb200_paged_decode_attn(const tsb200_kv_desc* kv, const void* q, void* out, int dtype,
-                             int64_t B, int H, float sm_scale, int64_t max_seq_len,
+                             int64_t q_batch_stride, int64_t B, int H, float sm_scale, int64_t max_seq_len,
                              void* workspace, size_t workspace_bytes, void* stream);
 /* Same contract; CUDA-core kernel (cross-check of the tensor-core kernel). */
 int tsb200_paged_decode_attn_simt(const tsb200_kv_desc* kv, const void* q, void* out, int dtype,
-                                  int64_t B, int H, float sm_scale, int64_t max_seq_len,
+                                  int64_t q_batch_stride, int64_t B, int H, float sm_scale, int64_t max_seq_len,
                                   void* workspace, size_t workspace_bytes, void* stream);
 
 /* ------------------------------------------------------------------------------------
  * Small decoder ops
  * ---------------------------------------------------------------------------------- */
 /* In-place half-split RoPE (blocks/rope.py:140-173) on x [B, T, heads, d]; position of
- * token (b, j) is pos0[b] + j (pos0 int32 [B], NULL = 0). */
-int tsb200_rope(void* x, int dtype, int64_t B, int64_t T, int heads, int head_dim,
+ * token (b, j) is pos0[b] + j (pos0 int32 [B], NULL = 0); token_stride = elements between
+ * consecutive tokens (0 = heads*d). */
+int tsb200_rope(void* x, int dtype, int64_t token_stride, int64_t B, int64_t T, int heads, int head_dim,
                 const int32_t* pos0, const float* rope_cos, const float* rope_sin,
                 int64_t rope_rows, void* stream);
 

@@ -143,8 +143,9 @@ def _mlp_accepts_activation():
 def gen_model(family):
     import transformersurgeon as T
     torch.manual_seed(21 if family == "qwen2" else 22)
-    kw = dict(vocab_size=256, hidden_size=64, intermediate_size=128, num_hidden_layers=2,
-              num_attention_heads=4, num_key_value_heads=2, max_position_embeddings=128,
+    # head_dim = 128 / 2 = 64 (the smallest head size the kernels support), GQA group of 2
+    kw = dict(vocab_size=256, hidden_size=128, intermediate_size=256, num_hidden_layers=2,
+              num_attention_heads=2, num_key_value_heads=1, max_position_embeddings=128,
               tie_word_embeddings=False)
     if family == "qwen2":
         cfg = T.Qwen2ConfigCompress(**kw); model = T.Qwen2ForCausalLMCompress(cfg)

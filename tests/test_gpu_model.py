@@ -1,0 +1,121 @@
+"""Model-level parity: the CUDA decode engine against logits / greedy tokens produced by the
+reference's `Qwen2ForCausalLMCompress` / `LlamaForCausalLMCompress` (tests/golden/model_*.npz:
+tiny random models, LRD rank 16/32 + 8-bit per-channel weights, fp32, dense fp32 KV cache)."""
+import numpy as np
+import pytest
+import torch
+
+from conftest import load_golden
+
+pytestmark = pytest.mark.gpu
+
+CC_PATHS = ("self_attn.q_proj", "self_attn.k_proj", "self_attn.v_proj", "self_attn.o_proj",
+            "mlp.gate_proj", "mlp.up_proj", "mlp.down_proj")
+
+
+def build(family, cuda, kv_format, dtype=torch.float32, quantized=True, batch=2):
+    from transformer_surgeon_b200 import surgeon
+    from transformer_surgeon_b200.decoder import DecoderConfig
+    g = load_golden(f"model_{family}.npz")
+    sd = {k[4:]: v for k, v in g.items() if k.startswith("sd::")}
+    cfg = DecoderConfig(num_layers=2, hidden=128, num_heads=2, num_kv_heads=1, head_dim=64, intermediate=256,
+                        vocab=256, rope_theta=float(g["rope_theta"]), rms_eps=float(g["rms_norm_eps"]),
+                        dtype=dtype, kv_format=kv_format, max_positions=128)
+    cc = None
+    if quantized:
+        cc = {f"model.layers.{i}.{p}": {"quantization": {"precision": 8, "granularity": "per_channel", "eps": 1e-6}}
+              for i in range(2) for p in CC_PATHS}
+    dec = surgeon.decoder_from_state_dict(sd, cfg, cc, batch=batch, max_seq_len=64, device=cuda)
+    return g, dec
+
+
+def rel(a, b):
+    return ((a.float() - b.float()).abs().max() / b.float().abs().max()).item()
+
+
+@pytest.mark.parametrize("family", ["qwen2", "llama"])
+def test_fp32_dense_kv_logits_and_greedy_tokens(cuda, family):
+    """Config-1 style run (fp32, dense fp32 KV): prompt logits within 1e-3 max-rel-err of the
+    reference and the greedy continuation identical token for token."""
+    g, dec = build(family, cuda, "fp32")
+    toks, logits = dec.generate(g["ids"], max_new_tokens=8)
+    assert rel(logits.cpu(), g["logits"][:, -1]) < 1e-3
+    assert torch.equal(toks.cpu(), g["tokens"])
+
+
+@pytest.mark.parametrize("family", ["qwen2", "llama"])
+def test_unquantized_weights_path(cuda, family):
+    """The stored factors used as dense fp32 matrices (no repacking) give the same result."""
+    g, dec = build(family, cuda, "fp32", quantized=False)
+    toks, logits = dec.generate(g["ids"], max_new_tokens=8)
+    assert rel(logits.cpu(), g["logits"][:, -1]) < 1e-3
+    assert torch.equal(toks.cpu(), g["tokens"])
+
+
+@pytest.mark.parametrize("family", ["qwen2", "llama"])
+@pytest.mark.parametrize("kv,tol", [("int8", 2e-2), ("fp8", 6e-2), ("nvfp4", 2.5e-1)])
+def test_quantized_kv_logits_close(cuda, family, kv, tol):
+    """Quantized KV changes the numbers (the reference has no such cache): logits stay within a
+    format-dependent max-rel-err of the dense-cache reference."""
+    g, dec = build(family, cuda, kv)
+    if kv == "fp8":
+        for c in dec.kv:
+            c.k_scale.fill_(16.0 / 448)
+            c.v_scale.fill_(4.0 / 448)
+    _, logits = dec.generate(g["ids"], max_new_tokens=1)
+    assert rel(logits.cpu(), g["logits"][:, -1]) < tol
+
+
+@pytest.mark.parametrize("family", ["qwen2", "llama"])
+def test_bf16_engine(cuda, family):
+    """bf16 activations / bf16 KV / tensor-core linears: logits max-rel-err vs the fp32 reference."""
+    g, dec = build(family, cuda, "bf16", dtype=torch.bfloat16)
+    _, logits = dec.generate(g["ids"], max_new_tokens=1)
+    assert rel(logits.cpu(), g["logits"][:, -1]) < 3e-2
+
+
+def test_cuda_graph_step_matches_eager(cuda):
+    g, dec = build("llama", cuda, "int8", dtype=torch.bfloat16, batch=2)
+    ids = g["ids"].to(cuda)
+    for t in range(6):
+        dec.step(ids[:, t])
+    eager = [dec.step(ids[:, 6 + t]).clone() for t in range(3)]
+    dec.reset()
+    for t in range(6):
+        dec.step(ids[:, t])
+    dec.capture()
+    for t in range(3):
+        out = dec.step(ids[:, 6 + t])
+        assert torch.equal(out, eager[t])
+    assert dec.seq_lens.tolist() == [9, 9]
+    assert dec.kernel_launches_per_step > 0
+
+
+def test_pack_model_rebinds_per_instance(cuda):
+    """pack_model keeps the class of each module (the reference checks `type(m) is LinearCompressed`)
+    and routes forward through the kernels; unpack_model restores the class's forward."""
+    from transformer_surgeon_b200 import surgeon
+
+    class LinearCompressed(torch.nn.Linear):           # same attribute contract as blocks/linear_compressed.py:9-62
+        def __init__(self, i, o, bias=True, rank=None):
+            super().__init__(i, o, bias=bias)
+            self.skip, self.rank, self.linear_V = False, ("full" if rank is None else rank), None
+            if isinstance(rank, int):
+                self.linear_V = torch.nn.Linear(i, rank, bias=False)
+                self.weight = torch.nn.Parameter(torch.randn(o, rank) * 0.1)
+
+        def forward(self, x):
+            if isinstance(self.rank, int):
+                x = self.linear_V(x)
+            return torch.nn.functional.linear(x, self.weight, self.bias)
+
+    torch.manual_seed(0)
+    net = torch.nn.Sequential(LinearCompressed(64, 128, rank=16), torch.nn.ReLU(), LinearCompressed(128, 64)).to(cuda)
+    x = torch.randn(3, 5, 64, device=cuda)
+    ref = net(x)
+    assert surgeon.pack_model(net, cuda) == 2
+    assert type(net[0]) is LinearCompressed and "forward" in net[0].__dict__
+    torch.testing.assert_close(net(x), ref, rtol=1e-4, atol=1e-5)
+    surgeon.unpack_model(net)
+    assert "forward" not in net[0].__dict__ and not hasattr(net[0], "_tsb200")
+    assert torch.equal(net(x), ref)

@@ -11,7 +11,7 @@ LIB_PATH = os.path.join(_HERE, "libtsb200.so")
 
 OK, ERR_ARG, ERR_UNSUPPORTED, ERR_CUDA, ERR_WORKSPACE, ERR_DEVICE, ERR_TIMEOUT = 0, -1, -2, -3, -4, -5, -6
 F32, BF16 = 0, 1
-KV_INT8, KV_FP8, KV_NVFP4 = 0, 1, 2
+KV_INT8, KV_FP8, KV_NVFP4, KV_F32, KV_BF16 = 0, 1, 2, 3, 4
 
 
 class Tsb200Error(RuntimeError):
@@ -53,11 +53,11 @@ SIGNATURES = {
     "tsb200_linear_simt": (_i32, [_LD, _vp, _vp, _i64, _vp, _sz, _vp]),
     "tsb200_kv_record_bytes": (_sz, [_i32, _i32]),
     "tsb200_kv_fp8_scales": (_i32, [_vp, _vp, _i32, _i64, _i64, _i32, _i32, _vp, _vp, _vp, _i64, _vp, _vp, _vp]),
-    "tsb200_kv_append": (_i32, [_KD, _vp, _vp, _i32, _i64, _i64, _vp, _vp, _vp, _i64, _vp]),
+    "tsb200_kv_append": (_i32, [_KD, _vp, _vp, _i32, _i64, _i64, _i64, _i64, _vp, _vp, _vp, _i64, _vp]),
     "tsb200_paged_decode_attn_workspace_bytes": (_sz, [_i64, _i32, _i32, _i64]),
-    "tsb200_paged_decode_attn": (_i32, [_KD, _vp, _vp, _i32, _i64, _i32, _f32, _i64, _vp, _sz, _vp]),
-    "tsb200_paged_decode_attn_simt": (_i32, [_KD, _vp, _vp, _i32, _i64, _i32, _f32, _i64, _vp, _sz, _vp]),
-    "tsb200_rope": (_i32, [_vp, _i32, _i64, _i64, _i32, _i32, _vp, _vp, _vp, _i64, _vp]),
+    "tsb200_paged_decode_attn": (_i32, [_KD, _vp, _vp, _i32, _i64, _i64, _i32, _f32, _i64, _vp, _sz, _vp]),
+    "tsb200_paged_decode_attn_simt": (_i32, [_KD, _vp, _vp, _i32, _i64, _i64, _i32, _f32, _i64, _vp, _sz, _vp]),
+    "tsb200_rope": (_i32, [_vp, _i32, _i64, _i64, _i64, _i32, _i32, _vp, _vp, _vp, _i64, _vp]),
     "tsb200_add_rmsnorm": (_i32, [_vp, _vp, _vp, _vp, _i32, _i64, _i64, _f32, _i32, _vp]),
     "tsb200_swiglu": (_i32, [_vp, _vp, _vp, _i32, _i64, _i64, _i64, _i64, _i64, _vp]),
 }

@@ -41,7 +41,13 @@ __device__ __forceinline__ float e2m1_nibble_to_f32(unsigned int c) {
 // Dequantized K / V element (token slot t, element e) of one page record; slow path used
 // by the CUDA-core kernel.  fp8 scale is applied by the caller.
 template <int D>
+__device__ __forceinline__ float dense_elem(const uint8_t* __restrict__ rec, int fmt, int t, int e) {
+  if (fmt == TSB200_KV_F32) return reinterpret_cast<const float*>(rec)[t * D + e];
+  return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(rec)[t * D + e]);
+}
+template <int D>
 __device__ __forceinline__ float k_elem(const uint8_t* __restrict__ rec, int fmt, int t, int e) {
+  if (fmt >= TSB200_KV_F32) return dense_elem<D>(rec, fmt, t, e);
   if (fmt == TSB200_KV_INT8)
     return (float)(int8_t)rec[t * D + e] * reinterpret_cast<const float*>(rec + 16 * D)[t];
   if (fmt == TSB200_KV_FP8) return e4m3_byte_to_f32(rec[t * D + e]);
@@ -50,6 +56,7 @@ __device__ __forceinline__ float k_elem(const uint8_t* __restrict__ rec, int fmt
 }
 template <int D>
 __device__ __forceinline__ float v_elem(const uint8_t* __restrict__ rec, int fmt, int t, int e) {
+  if (fmt >= TSB200_KV_F32) return dense_elem<D>(rec, fmt, t, e);
   if (fmt == TSB200_KV_INT8)
     return (float)(int8_t)rec[e * 16 + t] * reinterpret_cast<const float*>(rec + 16 * D)[t];
   if (fmt == TSB200_KV_FP8) return e4m3_byte_to_f32(rec[e * 16 + t]);

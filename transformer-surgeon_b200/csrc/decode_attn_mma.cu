@@ -70,7 +70,7 @@ template <int D> __device__ __forceinline__ int k_phys_chunk(int row, int j) {
 
 template <typename T, int D, int FMT>
 __global__ void __launch_bounds__(kWarps * 32)
-decode_attn_mma_kernel(tsb200_kv_desc kv, const T* __restrict__ q, int H, float sm_scale, int64_t max_seq_len, int S,
+decode_attn_mma_kernel(tsb200_kv_desc kv, const T* __restrict__ q, int64_t qs, int H, float sm_scale, int64_t max_seq_len, int S,
                        float* __restrict__ ws) {
   constexpr int REC = (FMT == TSB200_KV_INT8) ? 16 * D + 64 : 16 * D;
   constexpr int CODE_CHUNKS = D;               // 16*D bytes / 16
@@ -93,7 +93,7 @@ decode_attn_mma_kernel(tsb200_kv_desc kv, const T* __restrict__ q, int H, float 
   unsigned qf[NC][2];
   {
     const bool valid = gid < gn;
-    const T* qp = q + ((int64_t)b * H + hk * g + g0 + (valid ? gid : 0)) * D;
+    const T* qp = q + (int64_t)b * qs + (int64_t)(hk * g + g0 + (valid ? gid : 0)) * D;
 #pragma unroll
     for (int c = 0; c < NC; ++c) {
       const int base = 16 * (tid + 4 * (c >> 2)) + 4 * (c & 3);
@@ -253,7 +253,7 @@ decode_attn_mma_kernel(tsb200_kv_desc kv, const T* __restrict__ q, int H, float 
 }
 
 template <typename T, int D, int FMT>
-int launch_mma(const tsb200_kv_desc& kv, const void* q, int H, float sm_scale, int64_t max_seq_len, int S, int64_t B,
+int launch_mma(const tsb200_kv_desc& kv, const void* q, int64_t qs, int H, float sm_scale, int64_t max_seq_len, int S, int64_t B,
                float* ws, cudaStream_t st) {
   constexpr int REC = (FMT == TSB200_KV_INT8) ? 16 * D + 64 : 16 * D;
   constexpr size_t pipe = (size_t)kWarps * kStages * 2 * REC;
@@ -269,7 +269,7 @@ int launch_mma(const tsb200_kv_desc& kv, const void* q, int H, float sm_scale, i
   }
   const int g = H / kv.hkv;
   dim3 grid((unsigned)(B * kv.hkv), (unsigned)S, (unsigned)((g + 7) / 8));
-  decode_attn_mma_kernel<T, D, FMT><<<grid, kWarps * 32, smem, st>>>(kv, (const T*)q, H, sm_scale, max_seq_len, S, ws);
+  decode_attn_mma_kernel<T, D, FMT><<<grid, kWarps * 32, smem, st>>>(kv, (const T*)q, qs, H, sm_scale, max_seq_len, S, ws);
   TSB_LAUNCH_CHECK();
   return TSB200_OK;
 }
@@ -279,21 +279,23 @@ int launch_mma(const tsb200_kv_desc& kv, const void* q, int H, float sm_scale, i
 
 using namespace tsb;
 
-extern "C" int tsb200_paged_decode_attn(const tsb200_kv_desc* kv, const void* q, void* out, int dtype, int64_t B, int H,
+extern "C" int tsb200_paged_decode_attn(const tsb200_kv_desc* kv, const void* q, void* out, int dtype, int64_t q_batch_stride, int64_t B, int H,
                                         float sm_scale, int64_t max_seq_len, void* workspace, size_t workspace_bytes,
                                         void* stream) {
   TSB_REQUIRE_DEVICE();
   bool noop;
   int st = validate_attn_args(kv, q, out, dtype, B, H, max_seq_len, workspace, workspace_bytes, noop);
   if (st != TSB200_OK || noop) return st;
-  if (kv->format == TSB200_KV_NVFP4)   // NVFP4 pages: CUDA-core kernel until the tensor-core variant lands
-    return tsb200_paged_decode_attn_simt(kv, q, out, dtype, B, H, sm_scale, max_seq_len, workspace, workspace_bytes, stream);
+  const int64_t qs = q_batch_stride ? q_batch_stride : (int64_t)H * kv->head_dim;
+  if (qs < (int64_t)H * kv->head_dim) return TSB200_ERR_ARG;
+  if (kv->format >= TSB200_KV_NVFP4)   // NVFP4 and unquantized pages: CUDA-core kernel (fp32 math)
+    return tsb200_paged_decode_attn_simt(kv, q, out, dtype, q_batch_stride, B, H, sm_scale, max_seq_len, workspace, workspace_bytes, stream);
   cudaStream_t s = as_stream(stream);
   const int S = choose_splits(B, kv->hkv, max_seq_len);
   float* ws = (float*)workspace;
   const int D = kv->head_dim;
   int r;
-#define TSB_GO(TT, DD, FF) r = launch_mma<TT, DD, FF>(*kv, q, H, sm_scale, max_seq_len, S, B, ws, s); if (r != TSB200_OK) return r; return launch_reduce<TT, DD>(ws, B * H, S, out, s)
+#define TSB_GO(TT, DD, FF) r = launch_mma<TT, DD, FF>(*kv, q, qs, H, sm_scale, max_seq_len, S, B, ws, s); if (r != TSB200_OK) return r; return launch_reduce<TT, DD>(ws, B * H, S, out, s)
   if (dtype == TSB200_F32) {
     if (D == 64) { if (kv->format == TSB200_KV_INT8) { TSB_GO(float, 64, TSB200_KV_INT8); } else { TSB_GO(float, 64, TSB200_KV_FP8); } }
     else { if (kv->format == TSB200_KV_INT8) { TSB_GO(float, 128, TSB200_KV_INT8); } else { TSB_GO(float, 128, TSB200_KV_FP8); } }

@@ -7,7 +7,7 @@ namespace tsb {
 
 // grid (B*hkv, S, ceil(g/8)); 128 threads = 4 warps; warp w takes pages w, w+4, ...
 template <typename T, int D>
-__global__ void decode_attn_simt_kernel(tsb200_kv_desc kv, const T* __restrict__ q, int H, float sm_scale,
+__global__ void decode_attn_simt_kernel(tsb200_kv_desc kv, const T* __restrict__ q, int64_t qs, int H, float sm_scale,
                                         int64_t max_seq_len, int S, int64_t rec_bytes, float* __restrict__ ws) {
   constexpr int EPL = D / 32, GC = 8;
   const int b = blockIdx.x / kv.hkv, hk = blockIdx.x % kv.hkv, s = blockIdx.y;
@@ -27,7 +27,7 @@ __global__ void decode_attn_simt_kernel(tsb200_kv_desc kv, const T* __restrict__
 #pragma unroll
     for (int e = 0; e < EPL; ++e) {
       acc[i][e] = 0.f;
-      qv[i][e] = i < gn ? to_f32<T>(q[((int64_t)b * H + hk * g + g0 + i) * D + lane * EPL + e]) * sm_scale * kscale : 0.f;
+      qv[i][e] = i < gn ? to_f32<T>(q[(int64_t)b * qs + (int64_t)(hk * g + g0 + i) * D + lane * EPL + e]) * sm_scale * kscale : 0.f;
     }
   }
   for (int pg = pb + w; pg < pe; pg += 4) {
@@ -150,13 +150,15 @@ size_t tsb200_paged_decode_attn_workspace_bytes(int64_t B, int H, int head_dim, 
   return (size_t)(B * H * smax * (2 + head_dim)) * sizeof(float);
 }
 
-int tsb200_paged_decode_attn_simt(const tsb200_kv_desc* kv, const void* q, void* out, int dtype, int64_t B, int H,
+int tsb200_paged_decode_attn_simt(const tsb200_kv_desc* kv, const void* q, void* out, int dtype, int64_t q_batch_stride, int64_t B, int H,
                                   float sm_scale, int64_t max_seq_len, void* workspace, size_t workspace_bytes,
                                   void* stream) {
   TSB_REQUIRE_DEVICE();
   bool noop;
   int st = validate_attn_args(kv, q, out, dtype, B, H, max_seq_len, workspace, workspace_bytes, noop);
   if (st != TSB200_OK || noop) return st;
+  const int64_t qs = q_batch_stride ? q_batch_stride : (int64_t)H * kv->head_dim;
+  if (qs < (int64_t)H * kv->head_dim) return TSB200_ERR_ARG;
   cudaStream_t s = as_stream(stream);
   const int S = choose_splits(B, kv->hkv, max_seq_len);
   const int g = H / kv->hkv;
@@ -164,7 +166,7 @@ int tsb200_paged_decode_attn_simt(const tsb200_kv_desc* kv, const void* q, void*
   dim3 grid((unsigned)(B * kv->hkv), (unsigned)S, (unsigned)((g + 7) / 8));
   float* ws = (float*)workspace;
 #define TSB_GO(TT, DD)                                                                                       \
-  decode_attn_simt_kernel<TT, DD><<<grid, 128, 0, s>>>(*kv, (const TT*)q, H, sm_scale, max_seq_len, S, rec, ws); \
+  decode_attn_simt_kernel<TT, DD><<<grid, 128, 0, s>>>(*kv, (const TT*)q, qs, H, sm_scale, max_seq_len, S, rec, ws); \
   TSB_LAUNCH_CHECK();                                                                                        \
   return launch_reduce<TT, DD>(ws, B * H, S, out, s)
   if (dtype == TSB200_F32) { if (kv->head_dim == 64) { TSB_GO(float, 64); } else { TSB_GO(float, 128); } }

@@ -7,7 +7,7 @@ namespace tsb {
 
 // x [B, T, heads, d]; one thread per (token, head, i < d/2).
 template <typename T>
-__global__ void rope_kernel(T* __restrict__ x, int64_t B, int64_t Tn, int heads, int d, const int32_t* __restrict__ pos0,
+__global__ void rope_kernel(T* __restrict__ x, int64_t xs, int64_t B, int64_t Tn, int heads, int d, const int32_t* __restrict__ pos0,
                             const float* __restrict__ cosT, const float* __restrict__ sinT, int64_t rope_rows) {
   const int half = d / 2;
   const int64_t total = B * Tn * heads * half;
@@ -15,12 +15,13 @@ __global__ void rope_kernel(T* __restrict__ x, int64_t B, int64_t Tn, int heads,
     const int i = (int)(idx % half);
     const int64_t th = idx / half;           // (b, t, head)
     const int64_t bt = th / heads;
+    const int hd = (int)(th - bt * heads);
     const int64_t b = bt / Tn, t = bt - b * Tn;
     int64_t pos = (pos0 ? (int64_t)pos0[b] : 0) + t;
     pos = pos < 0 ? 0 : (pos >= rope_rows ? rope_rows - 1 : pos);
     const float c = rnd<T>(cosT[pos * half + i]);
     const float s = rnd<T>(sinT[pos * half + i]);
-    T* p = x + th * d;
+    T* p = x + bt * xs + (int64_t)hd * d;
     const float xr = to_f32<T>(p[i]), xi = to_f32<T>(p[i + half]);
     const float yr = __fsub_rn(rnd<T>(__fmul_rn(xr, c)), rnd<T>(__fmul_rn(xi, s)));
     const float yi = __fadd_rn(rnd<T>(__fmul_rn(xr, s)), rnd<T>(__fmul_rn(xi, c)));
@@ -115,17 +116,19 @@ using namespace tsb;
 
 extern "C" {
 
-int tsb200_rope(void* x, int dtype, int64_t B, int64_t T, int heads, int head_dim, const int32_t* pos0,
+int tsb200_rope(void* x, int dtype, int64_t token_stride, int64_t B, int64_t T, int heads, int head_dim, const int32_t* pos0,
                 const float* rope_cos, const float* rope_sin, int64_t rope_rows, void* stream) {
   TSB_REQUIRE_DEVICE();
   if (B < 0 || T < 0 || heads <= 0 || head_dim <= 0 || (head_dim & 1)) return TSB200_ERR_ARG;
   if (B == 0 || T == 0) return TSB200_OK;
   if (!x || !rope_cos || !rope_sin || rope_rows <= 0) return TSB200_ERR_ARG;
   const int64_t n = B * T * heads * (head_dim / 2);
+  const int64_t xs = token_stride ? token_stride : (int64_t)heads * head_dim;
+  if (xs < (int64_t)heads * head_dim) return TSB200_ERR_ARG;
   if (dtype == TSB200_F32)
-    rope_kernel<float><<<egrid(n), 256, 0, as_stream(stream)>>>((float*)x, B, T, heads, head_dim, pos0, rope_cos, rope_sin, rope_rows);
+    rope_kernel<float><<<egrid(n), 256, 0, as_stream(stream)>>>((float*)x, xs, B, T, heads, head_dim, pos0, rope_cos, rope_sin, rope_rows);
   else if (dtype == TSB200_BF16)
-    rope_kernel<__nv_bfloat16><<<egrid(n), 256, 0, as_stream(stream)>>>((__nv_bfloat16*)x, B, T, heads, head_dim, pos0, rope_cos, rope_sin, rope_rows);
+    rope_kernel<__nv_bfloat16><<<egrid(n), 256, 0, as_stream(stream)>>>((__nv_bfloat16*)x, xs, B, T, heads, head_dim, pos0, rope_cos, rope_sin, rope_rows);
   else
     return TSB200_ERR_UNSUPPORTED;
   TSB_LAUNCH_CHECK();

@@ -42,6 +42,15 @@ __device__ __forceinline__ void load_vec(const T* __restrict__ src, int lane, fl
   }
 }
 
+// Unquantized pages (TSB200_KV_F32 / TSB200_KV_BF16): K and V records are both [16 tok][d] of T.
+template <typename T, int D>
+__device__ __forceinline__ void dense_store(const float (&x)[D / 32], int lane, uint8_t* __restrict__ rec, int slot) {
+  constexpr int EPL = D / 32;
+  T* dst = reinterpret_cast<T*>(rec) + slot * D + lane * EPL;
+#pragma unroll
+  for (int i = 0; i < EPL; ++i) dst[i] = from_f32<T>(x[i]);
+}
+
 template <int D, int FMT, bool IS_V>
 __device__ __forceinline__ void quant_store(const float (&x)[D / 32], int lane, uint8_t* __restrict__ rec, int slot,
                                             float fp8_scale) {
@@ -110,7 +119,8 @@ __device__ __forceinline__ void quant_store(const float (&x)[D / 32], int lane, 
 }
 
 template <typename T, int D, int FMT>
-__global__ void kv_append_kernel(tsb200_kv_desc kv, const T* __restrict__ k, const T* __restrict__ v, int64_t B,
+__global__ void kv_append_kernel(tsb200_kv_desc kv, const T* __restrict__ k, const T* __restrict__ v, int64_t ks,
+                                 int64_t vs_, int64_t B,
                                  int64_t Tn, const int32_t* __restrict__ new_lens, const float* __restrict__ rope_cos,
                                  const float* __restrict__ rope_sin, int64_t rope_rows, int64_t rec_bytes) {
   const int lane = threadIdx.x & 31;
@@ -130,15 +140,17 @@ __global__ void kv_append_kernel(tsb200_kv_desc kv, const T* __restrict__ k, con
   const bool rope = rope_cos != nullptr;
   const int64_t rp = p >= rope_rows ? rope_rows - 1 : p;
   float x[D / 32];
-  float ks = 1.f, vs = 1.f;
+  float kscale = 1.f, vscale = 1.f;
   if (FMT == TSB200_KV_FP8) {
-    ks = kv.k_scale[b * kv.hkv + h];
-    vs = kv.v_scale[b * kv.hkv + h];
+    kscale = kv.k_scale[b * kv.hkv + h];
+    vscale = kv.v_scale[b * kv.hkv + h];
   }
-  load_vec<T, D>(k + warp * D, lane, x, rope, rope ? rope_cos + rp * (D / 2) : nullptr, rope ? rope_sin + rp * (D / 2) : nullptr);
-  quant_store<D, FMT, false>(x, lane, kv.k_pool + rec, slot, ks);
-  load_vec<T, D>(v + warp * D, lane, x, false, nullptr, nullptr);
-  quant_store<D, FMT, true>(x, lane, kv.v_pool + rec, slot, vs);
+  load_vec<T, D>(k + bt * ks + (int64_t)h * D, lane, x, rope, rope ? rope_cos + rp * (D / 2) : nullptr, rope ? rope_sin + rp * (D / 2) : nullptr);
+  if (FMT >= TSB200_KV_F32) dense_store<T, D>(x, lane, kv.k_pool + rec, slot);
+  else quant_store<D, FMT, false>(x, lane, kv.k_pool + rec, slot, kscale);
+  load_vec<T, D>(v + bt * vs_ + (int64_t)h * D, lane, x, false, nullptr, nullptr);
+  if (FMT >= TSB200_KV_F32) dense_store<T, D>(x, lane, kv.v_pool + rec, slot);
+  else quant_store<D, FMT, true>(x, lane, kv.v_pool + rec, slot, vscale);
 }
 
 // One CTA per (b, h): amax over the T tokens of the prompt -> scale = amax/448 (1 if 0).
@@ -180,7 +192,7 @@ __global__ void kv_fp8_scales_kernel(const T* __restrict__ k, const T* __restric
 }
 
 template <typename T, int D>
-int launch_append(const tsb200_kv_desc& kv, const void* k, const void* v, int64_t B, int64_t Tn, const int32_t* new_lens,
+int launch_append(const tsb200_kv_desc& kv, const void* k, const void* v, int64_t ks, int64_t vs, int64_t B, int64_t Tn, const int32_t* new_lens,
                   const float* rc, const float* rs, int64_t rr, cudaStream_t s) {
   const int64_t warps = B * Tn * kv.hkv;
   const int64_t blocks = (warps + 7) / 8;
@@ -188,13 +200,16 @@ int launch_append(const tsb200_kv_desc& kv, const void* k, const void* v, int64_
   const int64_t rec = (int64_t)tsb200_kv_record_bytes(kv.format, D);
   switch (kv.format) {
     case TSB200_KV_INT8:
-      kv_append_kernel<T, D, TSB200_KV_INT8><<<(unsigned)blocks, 256, 0, s>>>(kv, (const T*)k, (const T*)v, B, Tn, new_lens, rc, rs, rr, rec);
+      kv_append_kernel<T, D, TSB200_KV_INT8><<<(unsigned)blocks, 256, 0, s>>>(kv, (const T*)k, (const T*)v, ks, vs, B, Tn, new_lens, rc, rs, rr, rec);
       break;
     case TSB200_KV_FP8:
-      kv_append_kernel<T, D, TSB200_KV_FP8><<<(unsigned)blocks, 256, 0, s>>>(kv, (const T*)k, (const T*)v, B, Tn, new_lens, rc, rs, rr, rec);
+      kv_append_kernel<T, D, TSB200_KV_FP8><<<(unsigned)blocks, 256, 0, s>>>(kv, (const T*)k, (const T*)v, ks, vs, B, Tn, new_lens, rc, rs, rr, rec);
       break;
-    default:
-      kv_append_kernel<T, D, TSB200_KV_NVFP4><<<(unsigned)blocks, 256, 0, s>>>(kv, (const T*)k, (const T*)v, B, Tn, new_lens, rc, rs, rr, rec);
+    case TSB200_KV_NVFP4:
+      kv_append_kernel<T, D, TSB200_KV_NVFP4><<<(unsigned)blocks, 256, 0, s>>>(kv, (const T*)k, (const T*)v, ks, vs, B, Tn, new_lens, rc, rs, rr, rec);
+      break;
+    default:   // unquantized pages in the act dtype
+      kv_append_kernel<T, D, TSB200_KV_F32><<<(unsigned)blocks, 256, 0, s>>>(kv, (const T*)k, (const T*)v, ks, vs, B, Tn, new_lens, rc, rs, rr, rec);
   }
   TSB_LAUNCH_CHECK();
   return TSB200_OK;
@@ -202,7 +217,7 @@ int launch_append(const tsb200_kv_desc& kv, const void* k, const void* v, int64_
 
 int validate_kv(const tsb200_kv_desc* kv, bool need_table) {
   if (!kv) return TSB200_ERR_ARG;
-  if (kv->format < 0 || kv->format > 2) return TSB200_ERR_UNSUPPORTED;
+  if (kv->format < 0 || kv->format > TSB200_KV_BF16) return TSB200_ERR_UNSUPPORTED;
   if (kv->head_dim != 64 && kv->head_dim != 128) return TSB200_ERR_UNSUPPORTED;
   if (kv->hkv <= 0 || kv->num_pages < 0 || kv->bt_stride < 0) return TSB200_ERR_ARG;
   if (!kv->k_pool || !kv->v_pool || !aligned(kv->k_pool, 16) || !aligned(kv->v_pool, 16)) return TSB200_ERR_ARG;
@@ -223,6 +238,8 @@ size_t tsb200_kv_record_bytes(int format, int head_dim) {
     case TSB200_KV_INT8: return (size_t)16 * head_dim + 64;
     case TSB200_KV_FP8: return (size_t)16 * head_dim;
     case TSB200_KV_NVFP4: return (size_t)16 * head_dim / 2 + (size_t)head_dim;
+    case TSB200_KV_F32: return (size_t)16 * head_dim * 4;
+    case TSB200_KV_BF16: return (size_t)16 * head_dim * 2;
     default: return 0;
   }
 }
@@ -248,8 +265,8 @@ int tsb200_kv_fp8_scales(const void* k, const void* v, int dtype, int64_t B, int
   return TSB200_OK;
 }
 
-int tsb200_kv_append(const tsb200_kv_desc* kv, const void* k, const void* v, int dtype, int64_t B, int64_t T,
-                     const int32_t* new_lens, const float* rope_cos, const float* rope_sin, int64_t rope_rows,
+int tsb200_kv_append(const tsb200_kv_desc* kv, const void* k, const void* v, int dtype, int64_t k_token_stride,
+                     int64_t v_token_stride, int64_t B, int64_t T, const int32_t* new_lens, const float* rope_cos, const float* rope_sin, int64_t rope_rows,
                      void* stream) {
   TSB_REQUIRE_DEVICE();
   int st = validate_kv(kv, true);
@@ -258,13 +275,18 @@ int tsb200_kv_append(const tsb200_kv_desc* kv, const void* k, const void* v, int
   if (dtype != TSB200_F32 && dtype != TSB200_BF16) return TSB200_ERR_UNSUPPORTED;
   if (B == 0 || T == 0) return TSB200_OK;
   if (!k || !v) return TSB200_ERR_ARG;
+  if ((kv->format == TSB200_KV_F32 && dtype != TSB200_F32) || (kv->format == TSB200_KV_BF16 && dtype != TSB200_BF16))
+    return TSB200_ERR_UNSUPPORTED;   // unquantized pages hold the act dtype
   if ((rope_cos != nullptr) != (rope_sin != nullptr) || (rope_cos && rope_rows <= 0)) return TSB200_ERR_ARG;
+  const int64_t dense = (int64_t)kv->hkv * kv->head_dim;
+  const int64_t ks = k_token_stride ? k_token_stride : dense, vs = v_token_stride ? v_token_stride : dense;
+  if (ks < dense || vs < dense) return TSB200_ERR_ARG;
   cudaStream_t s = as_stream(stream);
   if (dtype == TSB200_F32)
-    return kv->head_dim == 64 ? launch_append<float, 64>(*kv, k, v, B, T, new_lens, rope_cos, rope_sin, rope_rows, s)
-                              : launch_append<float, 128>(*kv, k, v, B, T, new_lens, rope_cos, rope_sin, rope_rows, s);
-  return kv->head_dim == 64 ? launch_append<__nv_bfloat16, 64>(*kv, k, v, B, T, new_lens, rope_cos, rope_sin, rope_rows, s)
-                            : launch_append<__nv_bfloat16, 128>(*kv, k, v, B, T, new_lens, rope_cos, rope_sin, rope_rows, s);
+    return kv->head_dim == 64 ? launch_append<float, 64>(*kv, k, v, ks, vs, B, T, new_lens, rope_cos, rope_sin, rope_rows, s)
+                              : launch_append<float, 128>(*kv, k, v, ks, vs, B, T, new_lens, rope_cos, rope_sin, rope_rows, s);
+  return kv->head_dim == 64 ? launch_append<__nv_bfloat16, 64>(*kv, k, v, ks, vs, B, T, new_lens, rope_cos, rope_sin, rope_rows, s)
+                            : launch_append<__nv_bfloat16, 128>(*kv, k, v, ks, vs, B, T, new_lens, rope_cos, rope_sin, rope_rows, s);
 }
 
 }  // extern "C"

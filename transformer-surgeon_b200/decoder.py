@@ -1,0 +1,203 @@
+"""Qwen2 / Llama decoder built from the C-ABI kernels: the decode step that
+`*ForCausalLMCompress.generate()` runs per token, with the attention and MLP modules rewired
+onto PackedLinear, the quantized paged KV cache and the fused small ops.
+
+Layer math follows Hugging Face's Qwen2/Llama decoder layer (what the reference's
+`Qwen2ForCausalLMCompress` / `LlamaForCausalLMCompress` inherit, models/qwen2_c/define_qwen2_c.py:22-27,
+models/llama_c/define_llama_c.py:24-30):
+    h = x + o_proj(attn(rope(q_proj(n1(x))), cache(rope(k_proj(n1(x))), v_proj(n1(x)))))
+    y = h + down_proj(silu(gate_proj(n2(h))) * up_proj(n2(h)))
+The `variant=1` norm and rope base of the reference's own blocks path (blocks/decoder.py:100-149,
+blocks/norm.py:8-23) are selectable through DecoderConfig.
+
+There is no CPU path: every tensor lives on the GPU and every op is a libtsb200 kernel, except
+the embedding gather, the final argmax and integer bookkeeping (torch).
+"""
+from dataclasses import dataclass
+
+import torch
+
+from . import ops
+
+
+@dataclass
+class DecoderConfig:
+    num_layers: int
+    hidden: int
+    num_heads: int
+    num_kv_heads: int
+    head_dim: int
+    intermediate: int
+    vocab: int
+    rope_theta: float = 1e6
+    rms_eps: float = 1e-6
+    norm_variant: int = 0          # 0 = Hugging Face RMSNorm, 1 = blocks/norm.py RMSNorm
+    dtype: torch.dtype = torch.bfloat16
+    kv_format: str = "fp8"         # int8 | fp8 | nvfp4 | fp32 | bf16
+    max_positions: int = 4096
+
+
+class LayerWeights:
+    """Kernel-side weights of one decoder layer.  `qkv` is one PackedLinear producing
+    [q | k | v] when the three projections could be fused (same container, full rank),
+    otherwise q, k, v are separate."""
+
+    def __init__(self, ln1, ln2, o, gate, up, down, qkv=None, q=None, k=None, v=None):
+        self.ln1, self.ln2, self.o, self.gate, self.up, self.down = ln1, ln2, o, gate, up, down
+        self.qkv, self.q, self.k, self.v = qkv, q, k, v
+
+
+def fuse_rows(factors, biases, act_dtype):
+    """Stack full-rank factors with identical containers row-wise into one PackedLinear
+    (per-row scales make this exact).  Returns None when they cannot be fused."""
+    f0 = factors[0]
+    if any(f.bits != f0.bits or f.cols != f0.cols for f in factors):
+        return None
+    data = torch.cat([f.data for f in factors], dim=0).contiguous()
+    scales = None if f0.scales is None else torch.cat([f.scales for f in factors]).contiguous()
+    rows = sum(f.rows for f in factors)
+    bias = None
+    if any(b is not None for b in biases):
+        bias = torch.cat([b if b is not None else torch.zeros(f.rows, dtype=act_dtype, device=data.device)
+                          for f, b in zip(factors, biases)]).contiguous()
+    return ops.PackedLinear(ops.Factor(data, scales, f0.bits, rows, f0.cols), None, bias, act_dtype)
+
+
+def rope_tables(head_dim, theta, max_positions, device):
+    """fp32 cos/sin [max_positions, head_dim/2]: inv_freq = theta^(-2i/d), angle = pos * inv_freq
+    (blocks/rope.py:45-94; identical to Hugging Face's default rotary embedding)."""
+    inv = 1.0 / (theta ** (torch.arange(0, head_dim, 2, dtype=torch.int64).float() / head_dim))
+    ang = torch.arange(max_positions, dtype=torch.float32).unsqueeze(-1) * inv.unsqueeze(0)
+    return torch.cos(ang).to(device).contiguous(), torch.sin(ang).to(device).contiguous()
+
+
+class CompressedDecoder:
+    def __init__(self, cfg, embed, layers, final_norm, lm_head, batch, max_seq_len, device):
+        self.cfg, self.embed, self.layers, self.final_norm, self.lm_head = cfg, embed, layers, final_norm, lm_head
+        self.B, self.max_seq_len, self.device = batch, max_seq_len, device
+        c = cfg
+        self.pages_per_seq = (max_seq_len + ops.PAGE - 1) // ops.PAGE
+        num_pages = batch * self.pages_per_seq
+        # sequence-major ascending page allocation: reproducible block tables
+        self.block_table = torch.arange(num_pages, dtype=torch.int32, device=device).reshape(batch, self.pages_per_seq)
+        self.seq_lens = torch.zeros(batch, dtype=torch.int32, device=device)    # tokens in cache (after this step's append)
+        self.write_pos = torch.zeros(batch, dtype=torch.int32, device=device)   # position of the token being appended
+        self.kv = [ops.PagedKV(c.kv_format, num_pages, c.num_kv_heads, c.head_dim, self.block_table, self.seq_lens, device)
+                   for _ in range(c.num_layers)]
+        self.cos, self.sin = rope_tables(c.head_dim, c.rope_theta, c.max_positions, device)
+        H, Hkv, d = c.num_heads, c.num_kv_heads, c.head_dim
+        dt = c.dtype
+        B = batch
+        # persistent activation buffers (stable addresses -> the step can be captured in a CUDA graph)
+        self.tokens = torch.zeros(B, dtype=torch.int64, device=device)
+        self.resid = torch.zeros((B, c.hidden), dtype=dt, device=device)
+        self.xn = torch.empty((B, c.hidden), dtype=dt, device=device)
+        self.qkv = torch.empty((B, (H + 2 * Hkv) * d), dtype=dt, device=device)
+        self.qb = torch.empty((B, H * d), dtype=dt, device=device)
+        self.kb = torch.empty((B, Hkv * d), dtype=dt, device=device)
+        self.vb = torch.empty((B, Hkv * d), dtype=dt, device=device)
+        self.attn = torch.empty((B, H * d), dtype=dt, device=device)
+        self.delta = torch.empty((B, c.hidden), dtype=dt, device=device)
+        self.gate = torch.empty((B, c.intermediate), dtype=dt, device=device)
+        self.up = torch.empty((B, c.intermediate), dtype=dt, device=device)
+        self.act = torch.empty((B, c.intermediate), dtype=dt, device=device)
+        self.logits = torch.empty((B, c.vocab), dtype=dt, device=device)
+        self.next_tokens = torch.zeros(B, dtype=torch.int64, device=device)
+        lin_ws = 256
+        for L in layers:
+            for lin in (L.qkv, L.q, L.k, L.v, L.o, L.gate, L.up, L.down):
+                if lin is not None:
+                    lin_ws = max(lin_ws, lin.workspace_bytes(B))
+        lin_ws = max(lin_ws, lm_head.workspace_bytes(B))
+        self.lin_ws = torch.zeros(lin_ws, dtype=torch.uint8, device=device)
+        self.attn_ws = torch.zeros(ops.decode_attn_workspace_bytes(B, H, d, max_seq_len), dtype=torch.uint8, device=device)
+        self.graph = None
+        self.kernel_launches_per_step = 0
+
+    # ------------------------------------------------------------------ one decode step
+    def _step_kernels(self):
+        c = self.cfg
+        B, H, Hkv, d = self.B, c.num_heads, c.num_kv_heads, c.head_dim
+        n = 0
+        torch.index_select(self.embed, 0, self.tokens, out=self.resid)
+        self.write_pos.copy_(self.seq_lens)
+        self.seq_lens.add_(1)
+        delta = None
+        rope = (self.cos, self.sin)
+        for li, L in enumerate(self.layers):
+            ops.add_rmsnorm(self.resid, delta, L.ln1, c.rms_eps, c.norm_variant, out=self.xn); n += 1
+            if L.qkv is not None:
+                L.qkv(self.xn, out=self.qkv, ws=self.lin_ws); n += 1
+                q4 = self.qkv[:, :H * d].unflatten(1, (H, d)).unsqueeze(1)                   # [B,1,H,d] views
+                k4 = self.qkv[:, H * d:(H + Hkv) * d].unflatten(1, (Hkv, d)).unsqueeze(1)
+                v4 = self.qkv[:, (H + Hkv) * d:].unflatten(1, (Hkv, d)).unsqueeze(1)
+            else:
+                L.q(self.xn, out=self.qb, ws=self.lin_ws)
+                L.k(self.xn, out=self.kb, ws=self.lin_ws)
+                L.v(self.xn, out=self.vb, ws=self.lin_ws)
+                n += sum(2 if l.rank else 1 for l in (L.q, L.k, L.v))
+                q4, k4, v4 = self.qb.view(B, 1, H, d), self.kb.view(B, 1, Hkv, d), self.vb.view(B, 1, Hkv, d)
+            ops.rope_(q4, self.cos, self.sin, self.write_pos); n += 1
+            self.kv[li].append(k4, v4, rope=rope, seq_lens=self.write_pos); n += 1
+            ops.paged_decode_attention(self.kv[li], q4[:, 0], self.max_seq_len, out=self.attn.view(B, H, d),
+                                       ws=self.attn_ws, seq_lens=self.seq_lens); n += 2
+            L.o(self.attn, out=self.delta, ws=self.lin_ws); n += 1
+            ops.add_rmsnorm(self.resid, self.delta, L.ln2, c.rms_eps, c.norm_variant, out=self.xn); n += 1
+            L.gate(self.xn, out=self.gate, ws=self.lin_ws)
+            L.up(self.xn, out=self.up, ws=self.lin_ws)
+            n += 2 * (2 if L.gate.rank else 1)
+            ops.swiglu(self.gate, self.up, out=self.act); n += 1
+            L.down(self.act, out=self.delta, ws=self.lin_ws); n += 2 if L.down.rank else 1
+            delta = self.delta
+        ops.add_rmsnorm(self.resid, delta, self.final_norm, c.rms_eps, c.norm_variant, out=self.xn); n += 1
+        self.lm_head(self.xn, out=self.logits, ws=self.lin_ws); n += 1
+        torch.argmax(self.logits, dim=-1, out=self.next_tokens)
+        self.kernel_launches_per_step = n
+        return self.logits
+
+    def capture(self):
+        """Capture one decode step in a CUDA graph (the per-token Python loop of Hugging Face's
+        `_sample` and ~15 launches per layer collapse into one graph launch)."""
+        s = torch.cuda.Stream()
+        s.wait_stream(torch.cuda.current_stream())
+        saved = self.seq_lens.clone()
+        with torch.cuda.stream(s):
+            self._step_kernels()            # warm-up outside capture (sets function attributes)
+            self.seq_lens.copy_(saved)
+        torch.cuda.current_stream().wait_stream(s)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            self._step_kernels()
+        self.seq_lens.copy_(saved)
+        self.graph = g
+
+    def step(self, tokens=None):
+        """Append one token per sequence and return logits [B, vocab] (a persistent buffer)."""
+        if tokens is not None:
+            self.tokens.copy_(tokens, non_blocking=True)
+        if self.graph is not None:
+            self.graph.replay()
+            return self.logits
+        return self._step_kernels()
+
+    def reset(self):
+        self.seq_lens.zero_()
+
+    @torch.no_grad()
+    def generate(self, input_ids, max_new_tokens):
+        """Greedy decoding.  The prompt is fed one token at a time through the decode step (as the
+        reference's blocks path does, examples/04_cache_impl_export_interface.py:128-139)."""
+        ids = input_ids.to(self.device)
+        B, T = ids.shape
+        assert B == self.B
+        self.reset()
+        for t in range(T):
+            self.step(ids[:, t])
+        prefill_logits = self.logits.clone()
+        out = [ids]
+        for _ in range(max_new_tokens):
+            nxt = self.next_tokens.clone()
+            out.append(nxt[:, None])
+            self.step(nxt)
+        return torch.cat(out, dim=1), prefill_logits

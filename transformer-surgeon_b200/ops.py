@@ -8,9 +8,9 @@ import ctypes as C
 import torch
 
 from . import _lib
-from ._lib import F32, BF16, KV_INT8, KV_FP8, KV_NVFP4, LinearDesc, KVDesc, check
+from ._lib import F32, BF16, KV_INT8, KV_FP8, KV_NVFP4, KV_F32, KV_BF16, LinearDesc, KVDesc, check
 
-KV_FORMATS = {"int8": KV_INT8, "fp8": KV_FP8, "nvfp4": KV_NVFP4}
+KV_FORMATS = {"int8": KV_INT8, "fp8": KV_FP8, "nvfp4": KV_NVFP4, "fp32": KV_F32, "bf16": KV_BF16}
 PAGE = 16
 
 
@@ -36,6 +36,23 @@ def _cuda(t, name):
     if not t.is_contiguous():
         raise ValueError(f"{name} must be contiguous")
     return t
+
+
+def _token_strided(t, name):
+    """t [B, T, heads, d] whose (heads, d) block is dense and whose tokens are evenly spaced
+    (e.g. a column slice of a fused projection output).  Returns the token stride in elements."""
+    if not t.is_cuda:
+        raise ValueError(f"{name} must be a CUDA tensor (this library has no CPU path)")
+    B, T, h, d = t.shape
+    if t.numel() == 0:
+        return h * d
+    if t.stride(3) != 1 or t.stride(2) != d:
+        raise ValueError(f"{name}: the (heads, d) block of a token must be dense")
+    if T == 1:                       # decode: one token per sequence, spaced by the batch stride
+        return t.stride(0) if B > 1 else h * d
+    if B > 1 and t.stride(0) != T * t.stride(1):
+        raise ValueError(f"{name}: tokens must be evenly strided across the batch")
+    return t.stride(1)
 
 
 # ---------------------------------------------------------------- weights ----------
@@ -233,11 +250,12 @@ class PagedKV:
             self.k_scale = self.v_scale = None
         self._desc = None
 
-    def desc(self):
+    def desc(self, seq_lens=None):
         # rebuilt on every call: block_table / seq_lens tensors may have been swapped
+        seq = self.seq_lens if seq_lens is None else seq_lens
         return KVDesc(self.fmt, self.hkv, self.head_dim, 0, self.num_pages, self.k_pool.data_ptr(),
                       self.v_pool.data_ptr(), self.block_table.data_ptr(), self.block_table.shape[1],
-                      self.seq_lens.data_ptr(), 0 if self.k_scale is None else self.k_scale.data_ptr(),
+                      seq.data_ptr(), 0 if self.k_scale is None else self.k_scale.data_ptr(),
                       0 if self.v_scale is None else self.v_scale.data_ptr())
 
     def set_fp8_scales(self, k, v, rope=None, pos0=None):
@@ -249,14 +267,16 @@ class PagedKV:
                                        _p(pos0), _p(cos), _p(sin), 0 if cos is None else cos.shape[0],
                                        _p(self.k_scale), _p(self.v_scale), _stream()), "tsb200_kv_fp8_scales")
 
-    def append(self, k, v, new_lens=None, rope=None):
+    def append(self, k, v, new_lens=None, rope=None, seq_lens=None):
         """k, v [B, T, hkv, d]; token j of sequence b -> position seq_lens[b] + j.
-        seq_lens is NOT advanced (it is shared by all layers; advance it once per step)."""
+        seq_lens is NOT advanced (it is shared by all layers; advance it once per step).
+        `seq_lens` overrides the tensor of write positions for this call."""
         lib = _lib.load()
         B, T = k.shape[:2]
         cos, sin = (None, None) if rope is None else rope
-        d = self.desc()
-        check(lib.tsb200_kv_append(C.byref(d), _p(_cuda(k, "k")), _p(_cuda(v, "v")), _dt(k), B, T, _p(new_lens),
+        d = self.desc(seq_lens)
+        ks, vs = _token_strided(k, "k"), _token_strided(v, "v")
+        check(lib.tsb200_kv_append(C.byref(d), _p(k), _p(v), _dt(k), ks, vs, B, T, _p(new_lens),
                                    _p(cos), _p(sin), 0 if cos is None else cos.shape[0], _stream()),
               "tsb200_kv_append")
 
@@ -265,22 +285,26 @@ def decode_attn_workspace_bytes(B, H, head_dim, max_seq_len):
     return int(_lib.load().tsb200_paged_decode_attn_workspace_bytes(B, H, head_dim, max_seq_len))
 
 
-def paged_decode_attention(kv, q, max_seq_len, sm_scale=None, out=None, ws=None, simt=False):
+def paged_decode_attention(kv, q, max_seq_len, sm_scale=None, out=None, ws=None, simt=False, seq_lens=None):
     """q [B, H, d] -> out [B, H, d]: softmax(q K^T * sm_scale) V over seq_lens[b] cached tokens
     (blocks/mha.py:9-103 for one query token per sequence)."""
     lib = _lib.load()
-    q = _cuda(q, "q")
+    if not q.is_cuda:
+        raise ValueError("q must be a CUDA tensor (this library has no CPU path)")
     B, H, d = q.shape
+    if q.numel() and (q.stride(2) != 1 or q.stride(1) != d):
+        raise ValueError("q: heads/d must be dense")
+    qs = q.stride(0) if q.numel() else H * d
     if out is None:
-        out = torch.empty_like(q)
+        out = torch.empty((B, H, d), dtype=q.dtype, device=q.device)
     nbytes = decode_attn_workspace_bytes(B, H, d, max_seq_len)
     if ws is None:
         ws = workspace(q.device, nbytes)
     if sm_scale is None:
         sm_scale = d ** -0.5
     fn = lib.tsb200_paged_decode_attn_simt if simt else lib.tsb200_paged_decode_attn
-    desc = kv.desc()
-    check(fn(C.byref(desc), _p(q), _p(out), _dt(q), B, H, float(sm_scale), int(max_seq_len), _p(ws), ws.numel(),
+    desc = kv.desc(seq_lens)
+    check(fn(C.byref(desc), _p(q), _p(out), _dt(q), qs, B, H, float(sm_scale), int(max_seq_len), _p(ws), ws.numel(),
              _stream()), "tsb200_paged_decode_attn")
     return out
 
@@ -290,7 +314,8 @@ def rope_(x, cos, sin, pos0=None):
     """In-place half-split RoPE on x [B, T, heads, d] (blocks/rope.py:140-173)."""
     lib = _lib.load()
     B, T, h, d = x.shape
-    check(lib.tsb200_rope(_p(_cuda(x, "x")), _dt(x), B, T, h, d, _p(pos0), _p(cos), _p(sin), cos.shape[0], _stream()),
+    xs = _token_strided(x, "x")
+    check(lib.tsb200_rope(_p(x), _dt(x), xs, B, T, h, d, _p(pos0), _p(cos), _p(sin), cos.shape[0], _stream()),
           "tsb200_rope")
     return x
 
