@@ -93,6 +93,72 @@ __global__ void add_rmsnorm_kernel(T* __restrict__ residual, const T* __restrict
   }
 }
 
+// Hugging Face variant, bf16, hidden % 8 == 0 and hidden <= 8192: one pass over global memory with
+// 16-byte loads; the row stays in registers between the statistic and the scaling.
+__global__ void __launch_bounds__(256)
+add_rmsnorm_hf_bf16_kernel(__nv_bfloat16* __restrict__ residual, const __nv_bfloat16* __restrict__ delta,
+                           const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ y, int hidden, float eps) {
+  __shared__ float sh[32];
+  const int64_t row = blockIdx.x;
+  const int nvec = hidden >> 3;
+  uint4* r = reinterpret_cast<uint4*>(residual + row * hidden);
+  const uint4* dl = delta ? reinterpret_cast<const uint4*>(delta + row * hidden) : nullptr;
+  float v[4][8];
+  float ss = 0.f;
+#pragma unroll
+  for (int it = 0; it < 4; ++it) {
+    const int i = threadIdx.x + it * 256;
+    if (i < nvec) {
+      uint4 a = r[i];
+      const __nv_bfloat162* ap = reinterpret_cast<const __nv_bfloat162*>(&a);
+      if (dl) {
+        const uint4 b = dl[i];
+        const __nv_bfloat162* bp = reinterpret_cast<const __nv_bfloat162*>(&b);
+        uint4 o;
+        __nv_bfloat162* op = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 fa = __bfloat1622float2(ap[j]), fb = __bfloat1622float2(bp[j]);
+          op[j] = __floats2bfloat162_rn(__fadd_rn(fa.x, fb.x), __fadd_rn(fa.y, fb.y));
+          const float2 fo = __bfloat1622float2(op[j]);
+          v[it][2 * j] = fo.x; v[it][2 * j + 1] = fo.y;
+        }
+        r[i] = o;
+      } else {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 fa = __bfloat1622float2(ap[j]);
+          v[it][2 * j] = fa.x; v[it][2 * j + 1] = fa.y;
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) ss += v[it][j] * v[it][j];
+    }
+  }
+  const float var = block_reduce_sum(ss, sh) / (float)hidden;
+  const float inv = 1.0f / sqrtf(var + eps);
+  const uint4* wv = reinterpret_cast<const uint4*>(w);
+  uint4* yo = reinterpret_cast<uint4*>(y + row * hidden);
+#pragma unroll
+  for (int it = 0; it < 4; ++it) {
+    const int i = threadIdx.x + it * 256;
+    if (i < nvec) {
+      const uint4 ww = wv[i];
+      const __nv_bfloat162* wp = reinterpret_cast<const __nv_bfloat162*>(&ww);
+      uint4 o;
+      __nv_bfloat162* op = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 fw = __bfloat1622float2(wp[j]);
+        const __nv_bfloat162 n = __floats2bfloat162_rn(__fmul_rn(v[it][2 * j], inv), __fmul_rn(v[it][2 * j + 1], inv));
+        const float2 fn = __bfloat1622float2(n);
+        op[j] = __floats2bfloat162_rn(__fmul_rn(fw.x, fn.x), __fmul_rn(fw.y, fn.y));
+      }
+      yo[i] = o;
+    }
+  }
+}
+
 template <typename T>
 __global__ void swiglu_kernel(const T* __restrict__ gate, const T* __restrict__ up, T* __restrict__ y, int64_t M, int64_t n,
                               int64_t gs, int64_t us, int64_t ys) {
@@ -143,6 +209,13 @@ int tsb200_add_rmsnorm(void* residual, const void* delta, const void* w, void* y
   if (M == 0) return TSB200_OK;
   if (!residual || !w || !y) return TSB200_ERR_ARG;
   if (M > 0x7fffffffLL) return TSB200_ERR_UNSUPPORTED;
+  if (dtype == TSB200_BF16 && variant == 0 && hidden % 8 == 0 && hidden <= 8192 && aligned(residual, 16) &&
+      aligned(y, 16) && aligned(w, 16) && (!delta || aligned(delta, 16))) {
+    add_rmsnorm_hf_bf16_kernel<<<(unsigned)M, 256, 0, as_stream(stream)>>>(
+        (__nv_bfloat16*)residual, (const __nv_bfloat16*)delta, (const __nv_bfloat16*)w, (__nv_bfloat16*)y, (int)hidden, eps);
+    TSB_LAUNCH_CHECK();
+    return TSB200_OK;
+  }
   if (dtype == TSB200_F32)
     add_rmsnorm_kernel<float><<<(unsigned)M, 256, 0, as_stream(stream)>>>((float*)residual, (const float*)delta, (const float*)w, (float*)y, hidden, eps, variant);
   else if (dtype == TSB200_BF16)

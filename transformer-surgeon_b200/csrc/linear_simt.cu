@@ -176,17 +176,20 @@ int validate_linear(const tsb200_linear_desc* d, const void* x, void* y, int64_t
 
 using namespace tsb;
 
+static constexpr size_t kWsHeaderBytes = 256 + 4096 * sizeof(int);   // = tc::kWsHeader
+
 extern "C" {
 
-// Workspace layout shared by both kernels: [0, 256) status word (zeroed once by the caller;
-// a kernel that gave up on a bounded wait stores a non-zero code there), then the rank-r
-// intermediate [M, rank] in the act dtype, then an fp32 [M, max(rank, out)] split-K buffer.
+// Workspace layout shared by all linear kernels: [0, 256) status word (a kernel that gave up on
+// a bounded wait stores a non-zero code there), [256, 256 + 16 KB) split-K tile counters, then the
+// rank-r intermediate [M, rank] in the act dtype, then an fp32 [M, max(rank, out)] split-K buffer.
+// The caller zero-fills the workspace once; every call leaves counters and split-K buffer zeroed.
 size_t tsb200_linear_workspace_bytes(const tsb200_linear_desc* d, int64_t M) {
-  if (!d || M <= 0) return 256;
+  if (!d || M <= 0) return kWsHeaderBytes;
   const size_t elt = d->act_dtype == TSB200_F32 ? 4 : 2;
   const size_t h = ((size_t)M * (size_t)(d->rank > 0 ? d->rank : 0) * elt + 255) / 256 * 256;
   const size_t nmax = (size_t)(d->rank > d->out_features ? d->rank : d->out_features);
-  return 256 + h + ((size_t)M * nmax * 4 + 255) / 256 * 256;
+  return kWsHeaderBytes + h + ((size_t)M * nmax * 4 + 255) / 256 * 256;
 }
 
 int tsb200_linear_simt(const tsb200_linear_desc* d, const void* x, void* y, int64_t M, void* workspace,
@@ -201,7 +204,7 @@ int tsb200_linear_simt(const tsb200_linear_desc* d, const void* x, void* y, int6
   if (d->rank > 0) {
     if (!workspace || !aligned(workspace, 16)) return TSB200_ERR_ARG;
     if (workspace_bytes < tsb200_linear_workspace_bytes(d, M)) return TSB200_ERR_WORKSPACE;
-    void* h = (uint8_t*)workspace + 256;
+    void* h = (uint8_t*)workspace + kWsHeaderBytes;
     st = d->act_dtype == TSB200_F32
              ? launch_bits<float>(d->v_bits, d->v, d->v_scale, nullptr, x, h, M, d->in_features, d->rank, s)
              : launch_bits<__nv_bfloat16>(d->v_bits, d->v, d->v_scale, nullptr, x, h, M, d->in_features, d->rank, s);

@@ -19,118 +19,16 @@
 //               scale, bias, store (or fp32 atomics into a split-K buffer)
 // Every mbarrier wait is bounded; on expiry the kernel records a code in the status word
 // (first 4 bytes of the workspace), drains and frees TMEM, and returns.
-#include <cuda.h>
-#include "common.cuh"
+#include "tc_common.cuh"
 
 namespace tsb {
+using namespace tc;
 namespace {
 
-constexpr int BM = 128;            // weight rows per CTA = MMA M
-constexpr int BK = 64;             // k per stage: one 128-byte swizzle atom of bf16
 constexpr int NSTG = 4;
 constexpr int kThreads = 192;
-constexpr unsigned kSpinLimit = 1u << 20;   // try_wait attempts before giving up
-
-// ---------------------------------------------------------------- PTX wrappers -----
-__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(unsigned long long* bar, unsigned count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(unsigned long long* bar, unsigned bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(unsigned long long* bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(unsigned long long* bar, unsigned parity) {
-  unsigned ok;
-  asm volatile(
-      "{\n.reg .pred p;\n"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-      "selp.u32 %0, 1, 0, p;\n}\n"
-      : "=r"(ok)
-      : "r"(smem_u32(bar)), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-// Bounded wait.  Returns false (and raises the CTA-wide abort flag) when it gives up.
-__device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned parity, volatile int* abort_flag, int code) {
-  for (unsigned i = 0; i < kSpinLimit; ++i) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if ((i & 63u) == 63u && *abort_flag) return false;
-  }
-  *abort_flag = code;
-  return false;
-}
-
-__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, unsigned long long* bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n" ::"r"(
-          smem_u32(dst)),
-      "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar))
-      : "memory");
-}
-
-__device__ __forceinline__ void tmem_alloc(unsigned* smem_dst, unsigned ncols) {
-  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(smem_dst)), "r"(ncols) : "memory");
-  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc(unsigned taddr, unsigned ncols) {
-  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(taddr), "r"(ncols) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
-__device__ __forceinline__ void fence_async_proxy() { asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory"); }
-
-__device__ __forceinline__ void umma_bf16(unsigned d_tmem, unsigned long long adesc, unsigned long long bdesc, unsigned idesc,
-                                          unsigned accumulate) {
-  asm volatile(
-      "{\n.reg .pred p;\n"
-      "setp.ne.b32 p, %4, 0;\n"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n" ::"r"(d_tmem),
-      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-__device__ __forceinline__ void umma_commit(unsigned long long* bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ void tmem_ld16(unsigned taddr, unsigned (&r)[16]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];\n"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-      : "r"(taddr)
-      : "memory");
-}
-__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
-
-// Shared-memory matrix descriptor: K-major operand tile with 128-byte swizzle, rows of 128
-// bytes, 8-row groups 1024 bytes apart (stride byte offset), descriptor version 1.
-__device__ __forceinline__ unsigned long long smem_desc_sw128(unsigned saddr) {
-  unsigned long long d = 0;
-  d |= (unsigned long long)((saddr >> 4) & 0x3FFFu);
-  d |= (unsigned long long)1u << 16;                 // leading byte offset (unused for swizzled K-major)
-  d |= (unsigned long long)(1024u >> 4) << 32;       // stride byte offset
-  d |= (unsigned long long)1u << 46;                 // version
-  d |= (unsigned long long)2u << 61;                 // SWIZZLE_128B
-  return d;
-}
-// Instruction descriptor, kind::f16: D=f32, A=B=bf16, both K-major, M=128, N=n.
-__host__ __device__ constexpr unsigned idesc_bf16(int n) {
-  return (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(n >> 3) << 17) | ((unsigned)(BM >> 4) << 24);
-}
 
 // ---------------------------------------------------------------- dequantization ---
-// Write 8 bf16 (one 16-byte chunk `c` of row `r`) into the swizzled A tile.
-__device__ __forceinline__ void store_chunk(uint8_t* a_tile, int r, int c, uint4 v) {
-  *reinterpret_cast<uint4*>(a_tile + r * 128 + ((c ^ (r & 7)) << 4)) = v;
-}
-__device__ __forceinline__ unsigned bf16x2_sub(unsigned a, unsigned b) {
-  __nv_bfloat162 r = __hsub2(*reinterpret_cast<__nv_bfloat162*>(&a), *reinterpret_cast<__nv_bfloat162*>(&b));
-  return *reinterpret_cast<unsigned*>(&r);
-}
-
 // One thread converts one weight row of the k-block: 64 codes -> 64 bf16.
 template <int BITS>
 __device__ __forceinline__ void dequant_row(const uint8_t* __restrict__ raw_row, uint8_t* a_tile, int r) {
@@ -341,42 +239,14 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
 }
 
 // fp32 split-K buffer -> bf16 output.
-__global__ void splitk_finalize_kernel(const float* __restrict__ partial, __nv_bfloat16* __restrict__ y, int64_t n) {
-  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
+__global__ void splitk_finalize_kernel(float* __restrict__ partial, __nv_bfloat16* __restrict__ y, int64_t n) {
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
     y[i] = __float2bfloat16_rn(partial[i]);
+    partial[i] = 0.f;     // the split-K buffer is shared with the persistent kernel, which expects zeros
+  }
 }
 
 // ---------------------------------------------------------------- host side --------
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  if (!fn) {
-    void* ptr = nullptr;
-    cudaDriverEntryPointQueryResult qres;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
-        qres == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<EncodeTiledFn>(ptr);
-  }
-  return fn;
-}
-
-// 2-D row-major tensor [rows, row_bytes or cols]; box = [box_rows, box_inner].
-bool make_map(CUtensorMap* map, CUtensorMapDataType dt, int elt, const void* base, uint64_t inner, uint64_t rows,
-              uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_rows, CUtensorMapSwizzle swz) {
-  EncodeTiledFn fn = encode_fn();
-  if (!fn) return false;
-  cuuint64_t dims[2] = {inner, rows};
-  cuuint64_t strides[1] = {row_stride_bytes};
-  cuuint32_t box[2] = {box_inner, box_rows};
-  cuuint32_t estr[2] = {1, 1};
-  (void)elt;
-  return fn(map, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swz,
-            CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-}
-
 template <int TN, int BITS>
 int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, const TcParams& p, dim3 grid, cudaStream_t s) {
   using L = SmemLayout<TN>;
@@ -410,16 +280,16 @@ int gemm_tc(const void* W, int bits, const float* scale, const void* bias, const
   const int tn = M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : 128));
   CUtensorMap mw, mx;
   if (bits == 16) {
-    if (!make_map(&mw, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, W, (uint64_t)K, (uint64_t)N, (uint64_t)K * 2, BK, BM,
+    if (!make_map(&mw, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, W, (uint64_t)K, (uint64_t)N, (uint64_t)K * 2, BK, BM,
                   CU_TENSOR_MAP_SWIZZLE_128B))
       return TSB200_ERR_CUDA;
   } else {
     const uint64_t rb = tsb200_packed_row_bytes(K, bits);
-    if (!make_map(&mw, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, W, rb, (uint64_t)N, rb, (uint32_t)(BK * bits / 8), BM,
+    if (!make_map(&mw, CU_TENSOR_MAP_DATA_TYPE_UINT8, W, rb, (uint64_t)N, rb, (uint32_t)(BK * bits / 8), BM,
                   CU_TENSOR_MAP_SWIZZLE_NONE))
       return TSB200_ERR_CUDA;
   }
-  if (!make_map(&mx, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, x, (uint64_t)K, (uint64_t)M, (uint64_t)K * 2, BK, (uint32_t)tn,
+  if (!make_map(&mx, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, x, (uint64_t)K, (uint64_t)M, (uint64_t)K * 2, BK, (uint32_t)tn,
                 CU_TENSOR_MAP_SWIZZLE_128B))
     return TSB200_ERR_CUDA;
   const int kb_total = (int)((K + BK - 1) / BK);
@@ -457,6 +327,10 @@ bool tc_supported_factor(int bits, int64_t K) { return (bits == 2 || bits == 4 |
 
 }  // namespace
 
+// Persistent kernel for packed factors (linear_tcq.cu).
+int gemm_tcq(const void* W, int bits, const float* scale, const void* bias, const void* x, void* y, int64_t M, int64_t K,
+             int64_t N, float* partial, int* counters, int* status, cudaStream_t s);
+
 int linear_tc(const tsb200_linear_desc* d, const void* x, void* y, int64_t M, void* workspace, size_t workspace_bytes,
               cudaStream_t s) {
   if (d->act_dtype != TSB200_BF16) return TSB200_ERR_UNSUPPORTED;
@@ -469,16 +343,22 @@ int linear_tc(const tsb200_linear_desc* d, const void* x, void* y, int64_t M, vo
   if (workspace_bytes < tsb200_linear_workspace_bytes(d, M)) return TSB200_ERR_WORKSPACE;
   uint8_t* ws = (uint8_t*)workspace;
   int* status = (int*)ws;
-  void* h = ws + 256;
+  int* counters = (int*)(ws + kWsCounters);
+  void* h = ws + kWsHeader;
   const size_t hbytes = ((size_t)M * (size_t)(d->rank > 0 ? d->rank : 0) * 2 + 255) / 256 * 256;
-  float* partial = (float*)(ws + 256 + hbytes);
+  float* partial = (float*)(ws + kWsHeader + hbytes);
+  auto gemm = [&](const void* W, int bits, const float* scale, const void* bias, const void* in, void* out, int64_t K,
+                  int64_t N) {
+    return bits == 16 ? gemm_tc(W, bits, scale, bias, in, out, M, K, N, partial, status, s)
+                      : gemm_tcq(W, bits, scale, bias, in, out, M, K, N, partial, counters, status, s);
+  };
   const void* in = x;
   if (d->rank > 0) {
-    int st = gemm_tc(d->v, d->v_bits, d->v_scale, nullptr, x, h, M, d->in_features, d->rank, partial, status, s);
+    int st = gemm(d->v, d->v_bits, d->v_scale, nullptr, x, h, d->in_features, d->rank);
     if (st != TSB200_OK) return st;
     in = h;
   }
-  return gemm_tc(d->u, d->u_bits, d->u_scale, d->bias, in, y, M, ku, d->out_features, partial, status, s);
+  return gemm(d->u, d->u_bits, d->u_scale, d->bias, in, y, ku, d->out_features);
 }
 
 }  // namespace tsb
