@@ -190,6 +190,18 @@ int tsb200_kv_append(const tsb200_kv_desc* kv, const void* k, const void* v, int
                      const float* rope_cos, const float* rope_sin, int64_t rope_rows,
                      void* stream);
 
+/* tsb200_kv_append plus, in the same launch, the in-place RoPE of the query heads
+ * q [B, T, q_heads, d] (token stride q_token_stride, 0 = dense) at the same positions
+ * seq_lens[b] + j: the whole post-projection step of a decoder attention block
+ * (blocks/mha.py:575-589) in one kernel.  q may be NULL (then identical to tsb200_kv_append);
+ * a non-NULL q requires the rope tables. */
+int tsb200_rope_append(const tsb200_kv_desc* kv, void* q, int q_heads, int64_t q_token_stride,
+                       const void* k, const void* v, int dtype,
+                       int64_t k_token_stride, int64_t v_token_stride,
+                       int64_t B, int64_t T, const int32_t* new_lens,
+                       const float* rope_cos, const float* rope_sin, int64_t rope_rows,
+                       void* stream);
+
 /* Split-K paged decode attention: one query token per sequence.
  * Replaces blocks/mha.py:9-103 (attention(): GQA, softmax(q k^T / sqrt(d)) v) for the
  * decode step, reading the quantized pages directly.

@@ -220,3 +220,31 @@ def test_argument_errors(cuda):
     small = torch.empty(16, dtype=torch.uint8, device=cuda)
     with pytest.raises(Tsb200Error):
         ops.paged_decode_attention(g, torch.zeros((2, 4, 64), device=cuda), max_seq_len=32, ws=small)
+
+
+@pytest.mark.parametrize("name", ["fp32", "bf16"])
+def test_rope_append_fused_equals_separate_calls(cuda, name):
+    """tsb200_rope_append on column slices of one fused [B, (H+2Hkv)d] projection buffer gives the
+    same q and the same pages as tsb200_rope + tsb200_kv_append on dense copies."""
+    from transformer_surgeon_b200 import ops
+    rng = np.random.default_rng(17)
+    B, H, Hkv, d = 6, 8, 2, 128
+    _, g1 = make_pair("int8", B, 2, Hkv, d, cuda, rng)
+    rng = np.random.default_rng(17)
+    _, g2 = make_pair("int8", B, 2, Hkv, d, cuda, rng)
+    start = torch.tensor([0, 3, 15, 16, 20, 31], dtype=torch.int32, device=cuda)
+    g1.seq_lens.copy_(start); g2.seq_lens.copy_(start)
+    cos, sin = oatt.rope_tables(d, 1e6, torch.arange(64))
+    rope = (cos.to(cuda), sin.to(cuda))
+    qkv = torch.randn((B, (H + 2 * Hkv) * d), generator=torch.Generator().manual_seed(3)).to(DT[name]).to(cuda)
+    q_ref = qkv[:, :H * d].reshape(B, 1, H, d).clone()
+    k_ref = qkv[:, H * d:(H + Hkv) * d].reshape(B, 1, Hkv, d).clone()
+    v_ref = qkv[:, (H + Hkv) * d:].reshape(B, 1, Hkv, d).clone()
+    ops.rope_(q_ref, rope[0], rope[1], start)
+    g1.append(k_ref, v_ref, rope=rope)
+    q4 = qkv[:, :H * d].unflatten(1, (H, d)).unsqueeze(1)
+    k4 = qkv[:, H * d:(H + Hkv) * d].unflatten(1, (Hkv, d)).unsqueeze(1)
+    v4 = qkv[:, (H + Hkv) * d:].unflatten(1, (Hkv, d)).unsqueeze(1)
+    g2.rope_append(q4, k4, v4, rope)
+    assert torch.equal(q4, q_ref)
+    assert torch.equal(g1.k_pool, g2.k_pool) and torch.equal(g1.v_pool, g2.v_pool)

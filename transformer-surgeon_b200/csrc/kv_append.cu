@@ -119,14 +119,31 @@ __device__ __forceinline__ void quant_store(const float (&x)[D / 32], int lane, 
 }
 
 template <typename T, int D, int FMT>
-__global__ void kv_append_kernel(tsb200_kv_desc kv, const T* __restrict__ k, const T* __restrict__ v, int64_t ks,
+__global__ void kv_append_kernel(tsb200_kv_desc kv, T* __restrict__ q, int64_t qs, int qheads,
+                                 const T* __restrict__ k, const T* __restrict__ v, int64_t ks,
                                  int64_t vs_, int64_t B,
                                  int64_t Tn, const int32_t* __restrict__ new_lens, const float* __restrict__ rope_cos,
                                  const float* __restrict__ rope_sin, int64_t rope_rows, int64_t rec_bytes) {
   const int lane = threadIdx.x & 31;
   const int64_t warp = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5;
   const int64_t total = B * Tn * kv.hkv;
-  if (warp >= total) return;
+  if (warp >= total) {
+    // extra warps: rotate the query heads in place (same rounding points as the key path)
+    const int64_t qw = warp - total;
+    if (q == nullptr || qw >= B * Tn * qheads || rope_cos == nullptr) return;
+    const int qh = (int)(qw % qheads);
+    const int64_t qbt = qw / qheads;
+    const int64_t qb = qbt / Tn, qj = qbt - qb * Tn;
+    if (new_lens && qj >= new_lens[qb]) return;
+    int64_t qp = (int64_t)kv.seq_lens[qb] + qj;
+    qp = qp < 0 ? 0 : (qp >= rope_rows ? rope_rows - 1 : qp);
+    float xq[D / 32];
+    T* dst = q + qbt * qs + (int64_t)qh * D;
+    load_vec<T, D>(dst, lane, xq, true, rope_cos + qp * (D / 2), rope_sin + qp * (D / 2));
+#pragma unroll
+    for (int i = 0; i < D / 32; ++i) dst[lane * (D / 32) + i] = from_f32<T>(xq[i]);
+    return;
+  }
   const int h = (int)(warp % kv.hkv);
   const int64_t bt = warp / kv.hkv;
   const int64_t b = bt / Tn, j = bt - b * Tn;
@@ -192,24 +209,24 @@ __global__ void kv_fp8_scales_kernel(const T* __restrict__ k, const T* __restric
 }
 
 template <typename T, int D>
-int launch_append(const tsb200_kv_desc& kv, const void* k, const void* v, int64_t ks, int64_t vs, int64_t B, int64_t Tn, const int32_t* new_lens,
+int launch_append(const tsb200_kv_desc& kv, void* q, int64_t qs, int qheads, const void* k, const void* v, int64_t ks, int64_t vs, int64_t B, int64_t Tn, const int32_t* new_lens,
                   const float* rc, const float* rs, int64_t rr, cudaStream_t s) {
-  const int64_t warps = B * Tn * kv.hkv;
+  const int64_t warps = B * Tn * (kv.hkv + (q ? qheads : 0));
   const int64_t blocks = (warps + 7) / 8;
   if (blocks > 0x7fffffffLL) return TSB200_ERR_UNSUPPORTED;
   const int64_t rec = (int64_t)tsb200_kv_record_bytes(kv.format, D);
   switch (kv.format) {
     case TSB200_KV_INT8:
-      kv_append_kernel<T, D, TSB200_KV_INT8><<<(unsigned)blocks, 256, 0, s>>>(kv, (const T*)k, (const T*)v, ks, vs, B, Tn, new_lens, rc, rs, rr, rec);
+      kv_append_kernel<T, D, TSB200_KV_INT8><<<(unsigned)blocks, 256, 0, s>>>(kv, (T*)q, qs, qheads, (const T*)k, (const T*)v, ks, vs, B, Tn, new_lens, rc, rs, rr, rec);
       break;
     case TSB200_KV_FP8:
-      kv_append_kernel<T, D, TSB200_KV_FP8><<<(unsigned)blocks, 256, 0, s>>>(kv, (const T*)k, (const T*)v, ks, vs, B, Tn, new_lens, rc, rs, rr, rec);
+      kv_append_kernel<T, D, TSB200_KV_FP8><<<(unsigned)blocks, 256, 0, s>>>(kv, (T*)q, qs, qheads, (const T*)k, (const T*)v, ks, vs, B, Tn, new_lens, rc, rs, rr, rec);
       break;
     case TSB200_KV_NVFP4:
-      kv_append_kernel<T, D, TSB200_KV_NVFP4><<<(unsigned)blocks, 256, 0, s>>>(kv, (const T*)k, (const T*)v, ks, vs, B, Tn, new_lens, rc, rs, rr, rec);
+      kv_append_kernel<T, D, TSB200_KV_NVFP4><<<(unsigned)blocks, 256, 0, s>>>(kv, (T*)q, qs, qheads, (const T*)k, (const T*)v, ks, vs, B, Tn, new_lens, rc, rs, rr, rec);
       break;
     default:   // unquantized pages in the act dtype
-      kv_append_kernel<T, D, TSB200_KV_F32><<<(unsigned)blocks, 256, 0, s>>>(kv, (const T*)k, (const T*)v, ks, vs, B, Tn, new_lens, rc, rs, rr, rec);
+      kv_append_kernel<T, D, TSB200_KV_F32><<<(unsigned)blocks, 256, 0, s>>>(kv, (T*)q, qs, qheads, (const T*)k, (const T*)v, ks, vs, B, Tn, new_lens, rc, rs, rr, rec);
   }
   TSB_LAUNCH_CHECK();
   return TSB200_OK;
@@ -265,28 +282,38 @@ int tsb200_kv_fp8_scales(const void* k, const void* v, int dtype, int64_t B, int
   return TSB200_OK;
 }
 
-int tsb200_kv_append(const tsb200_kv_desc* kv, const void* k, const void* v, int dtype, int64_t k_token_stride,
-                     int64_t v_token_stride, int64_t B, int64_t T, const int32_t* new_lens, const float* rope_cos, const float* rope_sin, int64_t rope_rows,
-                     void* stream) {
+int tsb200_rope_append(const tsb200_kv_desc* kv, void* q, int q_heads, int64_t q_token_stride, const void* k,
+                       const void* v, int dtype, int64_t k_token_stride, int64_t v_token_stride, int64_t B, int64_t T,
+                       const int32_t* new_lens, const float* rope_cos, const float* rope_sin, int64_t rope_rows,
+                       void* stream) {
   TSB_REQUIRE_DEVICE();
   int st = validate_kv(kv, true);
   if (st != TSB200_OK) return st;
-  if (B < 0 || T < 0) return TSB200_ERR_ARG;
+  if (B < 0 || T < 0 || q_heads < 0) return TSB200_ERR_ARG;
   if (dtype != TSB200_F32 && dtype != TSB200_BF16) return TSB200_ERR_UNSUPPORTED;
   if (B == 0 || T == 0) return TSB200_OK;
   if (!k || !v) return TSB200_ERR_ARG;
   if ((kv->format == TSB200_KV_F32 && dtype != TSB200_F32) || (kv->format == TSB200_KV_BF16 && dtype != TSB200_BF16))
     return TSB200_ERR_UNSUPPORTED;   // unquantized pages hold the act dtype
   if ((rope_cos != nullptr) != (rope_sin != nullptr) || (rope_cos && rope_rows <= 0)) return TSB200_ERR_ARG;
+  if (q && (!rope_cos || q_heads <= 0)) return TSB200_ERR_ARG;
   const int64_t dense = (int64_t)kv->hkv * kv->head_dim;
   const int64_t ks = k_token_stride ? k_token_stride : dense, vs = v_token_stride ? v_token_stride : dense;
-  if (ks < dense || vs < dense) return TSB200_ERR_ARG;
+  const int64_t qs = q_token_stride ? q_token_stride : (int64_t)q_heads * kv->head_dim;
+  if (ks < dense || vs < dense || (q && qs < (int64_t)q_heads * kv->head_dim)) return TSB200_ERR_ARG;
   cudaStream_t s = as_stream(stream);
   if (dtype == TSB200_F32)
-    return kv->head_dim == 64 ? launch_append<float, 64>(*kv, k, v, ks, vs, B, T, new_lens, rope_cos, rope_sin, rope_rows, s)
-                              : launch_append<float, 128>(*kv, k, v, ks, vs, B, T, new_lens, rope_cos, rope_sin, rope_rows, s);
-  return kv->head_dim == 64 ? launch_append<__nv_bfloat16, 64>(*kv, k, v, ks, vs, B, T, new_lens, rope_cos, rope_sin, rope_rows, s)
-                            : launch_append<__nv_bfloat16, 128>(*kv, k, v, ks, vs, B, T, new_lens, rope_cos, rope_sin, rope_rows, s);
+    return kv->head_dim == 64 ? launch_append<float, 64>(*kv, q, qs, q_heads, k, v, ks, vs, B, T, new_lens, rope_cos, rope_sin, rope_rows, s)
+                              : launch_append<float, 128>(*kv, q, qs, q_heads, k, v, ks, vs, B, T, new_lens, rope_cos, rope_sin, rope_rows, s);
+  return kv->head_dim == 64 ? launch_append<__nv_bfloat16, 64>(*kv, q, qs, q_heads, k, v, ks, vs, B, T, new_lens, rope_cos, rope_sin, rope_rows, s)
+                            : launch_append<__nv_bfloat16, 128>(*kv, q, qs, q_heads, k, v, ks, vs, B, T, new_lens, rope_cos, rope_sin, rope_rows, s);
+}
+
+int tsb200_kv_append(const tsb200_kv_desc* kv, const void* k, const void* v, int dtype, int64_t k_token_stride,
+                     int64_t v_token_stride, int64_t B, int64_t T, const int32_t* new_lens, const float* rope_cos,
+                     const float* rope_sin, int64_t rope_rows, void* stream) {
+  return tsb200_rope_append(kv, nullptr, 0, 0, k, v, dtype, k_token_stride, v_token_stride, B, T, new_lens, rope_cos,
+                            rope_sin, rope_rows, stream);
 }
 
 }  // extern "C"

@@ -137,8 +137,7 @@ class CompressedDecoder:
                 L.v(self.xn, out=self.vb, ws=self.lin_ws)
                 n += sum(2 if l.rank else 1 for l in (L.q, L.k, L.v))
                 q4, k4, v4 = self.qb.view(B, 1, H, d), self.kb.view(B, 1, Hkv, d), self.vb.view(B, 1, Hkv, d)
-            ops.rope_(q4, self.cos, self.sin, self.write_pos); n += 1
-            self.kv[li].append(k4, v4, rope=rope, seq_lens=self.write_pos); n += 1
+            self.kv[li].rope_append(q4, k4, v4, rope, seq_lens=self.write_pos); n += 1
             ops.paged_decode_attention(self.kv[li], q4[:, 0], self.max_seq_len, out=self.attn.view(B, H, d),
                                        ws=self.attn_ws, seq_lens=self.seq_lens); n += 2
             L.o(self.attn, out=self.delta, ws=self.lin_ws); n += 1

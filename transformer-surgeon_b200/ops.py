@@ -267,6 +267,16 @@ class PagedKV:
                                        _p(pos0), _p(cos), _p(sin), 0 if cos is None else cos.shape[0],
                                        _p(self.k_scale), _p(self.v_scale), _stream()), "tsb200_kv_fp8_scales")
 
+    def rope_append(self, q, k, v, rope, new_lens=None, seq_lens=None):
+        """One launch: RoPE on q [B, T, H, d] in place, RoPE on k, quantize-and-append k, v."""
+        lib = _lib.load()
+        B, T = k.shape[:2]
+        cos, sin = rope
+        d = self.desc(seq_lens)
+        qs, ks, vs = _token_strided(q, "q"), _token_strided(k, "k"), _token_strided(v, "v")
+        check(lib.tsb200_rope_append(C.byref(d), _p(q), q.shape[2], qs, _p(k), _p(v), _dt(k), ks, vs, B, T,
+                                     _p(new_lens), _p(cos), _p(sin), cos.shape[0], _stream()), "tsb200_rope_append")
+
     def append(self, k, v, new_lens=None, rope=None, seq_lens=None):
         """k, v [B, T, hkv, d]; token j of sequence b -> position seq_lens[b] + j.
         seq_lens is NOT advanced (it is shared by all layers; advance it once per step).
