@@ -120,8 +120,8 @@ typedef struct {
   const void* bias;      /* [out] act dtype, or NULL                                     */
 } tsb200_linear_desc;
 
-/* The workspace must be zero-filled ONCE by the caller before its first use (status word,
- * split-K counters and accumulation buffer live there); every call leaves it reusable.  Byte 0..3
+/* The first 16640 bytes of the workspace (status word + split-K counters) must be zero-filled
+ * ONCE by the caller before its first use; every call leaves them reusable.  Byte 0..3
  * is a status word: non-zero after a kernel gave up on a bounded device-side wait.  One workspace
  * must not be used by two calls that may overlap on the GPU. */
 size_t tsb200_linear_workspace_bytes(const tsb200_linear_desc* d, int64_t M);

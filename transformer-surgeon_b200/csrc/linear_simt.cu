@@ -6,7 +6,7 @@
 // dequantized on the fly: y[m,o] = scale[o] * sum_k code[o,k] * x[m,k]  (fp32 accumulate).
 // One warp per output row streams that row's packed codes once (16-byte aligned vector
 // loads) for up to 8 activation rows held in shared memory.
-#include "common.cuh"
+#include "tc_common.cuh"
 
 namespace tsb {
 namespace {
@@ -181,15 +181,21 @@ static constexpr size_t kWsHeaderBytes = 256 + 4096 * sizeof(int);   // = tc::kW
 extern "C" {
 
 // Workspace layout shared by all linear kernels: [0, 256) status word (a kernel that gave up on
-// a bounded wait stores a non-zero code there), [256, 256 + 16 KB) split-K tile counters, then the
-// rank-r intermediate [M, rank] in the act dtype, then an fp32 [M, max(rank, out)] split-K buffer.
-// The caller zero-fills the workspace once; every call leaves counters and split-K buffer zeroed.
+// a bounded wait stores a non-zero code there), [256, 256 + 16 KB) split-K tile counters (zero
+// between calls), then the rank-r intermediate [M, rank] in the act dtype, then split-K scratch
+// (fp32 [M, max(rank, out)] for the dense kernel, per-item slices for the packed kernel).
 size_t tsb200_linear_workspace_bytes(const tsb200_linear_desc* d, int64_t M) {
   if (!d || M <= 0) return kWsHeaderBytes;
   const size_t elt = d->act_dtype == TSB200_F32 ? 4 : 2;
   const size_t h = ((size_t)M * (size_t)(d->rank > 0 ? d->rank : 0) * elt + 255) / 256 * 256;
   const size_t nmax = (size_t)(d->rank > d->out_features ? d->rank : d->out_features);
-  return kWsHeaderBytes + h + ((size_t)M * nmax * 4 + 255) / 256 * 256;
+  size_t scratch = (size_t)M * nmax * 4;
+  const int64_t ku = d->rank > 0 ? d->rank : d->in_features;
+  const size_t s_u = tc::plan_gemm(M, d->out_features, ku).slice_bytes;
+  const size_t s_v = d->rank > 0 ? tc::plan_gemm(M, d->rank, d->in_features).slice_bytes : 0;
+  if (s_u > scratch) scratch = s_u;
+  if (s_v > scratch) scratch = s_v;
+  return kWsHeaderBytes + h + (scratch + 255) / 256 * 256;
 }
 
 int tsb200_linear_simt(const tsb200_linear_desc* d, const void* x, void* y, int64_t M, void* workspace,

@@ -11,9 +11,10 @@
 //     128-byte-swizzled A tiles; one lane issues tcgen05.mma (weights = A operand, M = 128;
 //     tokens = B operand, N = token tile) accumulating in TMEM;
 //   * the same 8 warps run the epilogue from TMEM (one lane = one weight row): scale, bias, store;
-//   * split-K partial sums are added into a zero-filled fp32 buffer; the last CTA to finish a
-//     tile (a per-tile counter) converts it to the output and re-zeroes buffer and counter, so
-//     no memset and no second kernel are needed and the workspace is left clean.
+//   * split-K: every item stores its fp32 partial tile in a private slice of the workspace (plain
+//     stores, no zero-fill needed); the last CTA to finish a tile (a per-tile counter, reset by
+//     that CTA) sums the slices in split order - a deterministic result - and writes the
+//     output, so no memset and no second kernel are needed.
 // Every mbarrier wait is bounded (see tc_common.cuh); on expiry the CTA records a code in the
 // status word, drains, frees its TMEM and returns.
 #include "tc_common.cuh"
@@ -116,8 +117,8 @@ struct QParams {
   const float* scale;
   const __nv_bfloat16* bias;
   __nv_bfloat16* y;
-  float* partial;      // zero-filled fp32 [M, N] (split-K only)
-  int* counters;       // zero-filled int32 [n_tiles * m_tiles] (split-K only)
+  float* partial;      // split-K: fp32 slices [items][TN][128], written before they are read
+  int* counters;       // split-K: zero-filled int32 [n_tiles * m_tiles], left zero
   int* status;
 };
 
@@ -247,26 +248,26 @@ linear_tcq_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
       const float sc = (p.scale && n < p.N) ? p.scale[n] : 1.0f;
       const float bv = (p.bias && n < p.N) ? __bfloat162float(p.bias[n]) : 0.f;
       constexpr int CH = TN / 2;                             // columns handled by this warp
+      float* slice = p.partial + (size_t)item * (TN * BM);   // [TN][128] of this item
 #pragma unroll 1
       for (int c0 = chalf * CH; c0 < (chalf + 1) * CH; c0 += 8) {
         unsigned r[8];
         tmem_ld8(tmem_base + ((unsigned)(q * 32) << 16) + (unsigned)c0, r);
         tmem_ld_wait();
-        if (n < p.N) {
+        if (split) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) __stcg(&slice[(c0 + j) * BM + trow], __uint_as_float(r[j]));
+        } else if (n < p.N) {
 #pragma unroll
           for (int j = 0; j < 8; ++j) {
             const int64_t m = m0 + c0 + j;
-            if (m < p.M) {
-              const float v = __uint_as_float(r[j]);
-              if (!split) p.y[m * p.N + n] = __float2bfloat16_rn(v * sc + bv);
-              else atomicAdd(&p.partial[m * p.N + n], v);
-            }
+            if (m < p.M) p.y[m * p.N + n] = __float2bfloat16_rn(__uint_as_float(r[j]) * sc + bv);
           }
         }
       }
       tc_fence_before();
       if (split) {
-        // last CTA of this (n tile, m tile) finalizes: partial -> y, then re-zero partial and counter
+        // last CTA of this (n tile, m tile) finalizes: sum of the slices -> y, then reset the counter
         __threadfence();
         if (!(ok = warps_rendezvous(ep_bar, ep_uses, lane, abort_flag))) break;
         if (td == 0) {
@@ -278,13 +279,13 @@ linear_tcq_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
         if (last) {
           __threadfence();
           if (n < p.N) {
+            const float* tile0 = p.partial + (size_t)(item - item % p.splits) * (TN * BM);
             for (int c = chalf * CH; c < (chalf + 1) * CH; ++c) {
               const int64_t m = m0 + c;
               if (m < p.M) {
-                float* pp = &p.partial[m * p.N + n];
-                const float v = __ldcg(pp);
+                float v = 0.f;
+                for (int sp = 0; sp < p.splits; ++sp) v += __ldcg(&tile0[(size_t)sp * (TN * BM) + c * BM + trow]);
                 p.y[m * p.N + n] = __float2bfloat16_rn(v * sc + bv);
-                __stcg(pp, 0.f);
               }
             }
           }
@@ -354,10 +355,11 @@ int num_sms() {
 }  // namespace
 
 // y[M, N] = x[M, K] . Wq[N, K]^T * scale + bias; Wq packed at `bits` in {2, 4, 8}; bf16 in/out.
-// partial / counters: zero-filled split-K scratch (left zero-filled).
+// partial: split-K slice scratch (plan_gemm().slice_bytes); counters: zero-filled, left zero.
 int gemm_tcq(const void* W, int bits, const float* scale, const void* bias, const void* x, void* y, int64_t M, int64_t K,
              int64_t N, float* partial, int* counters, int* status, cudaStream_t s) {
-  const int tn = M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : 128));
+  const GemmPlan g = plan_gemm(M, N, K);
+  const int tn = g.tn;
   CUtensorMap mw, mx;
   const uint64_t rb = tsb200_packed_row_bytes(K, bits);
   if (!make_map(&mw, CU_TENSOR_MAP_DATA_TYPE_UINT8, W, rb, (uint64_t)N, rb, (uint32_t)(BK * bits / 8), BM, CU_TENSOR_MAP_SWIZZLE_NONE))
@@ -365,25 +367,11 @@ int gemm_tcq(const void* W, int bits, const float* scale, const void* bias, cons
   if (!make_map(&mx, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, x, (uint64_t)K, (uint64_t)M, (uint64_t)K * 2, BK, (uint32_t)tn, CU_TENSOR_MAP_SWIZZLE_128B))
     return TSB200_ERR_CUDA;
   const int sms = num_sms();
-  const int kb_total = (int)((K + BK - 1) / BK);
-  const int64_t n_tiles = (N + BM - 1) / BM, m_tiles = (M + tn - 1) / tn;
-  const int64_t base = n_tiles * m_tiles;
-  if (base > 0x3fffffffLL) return TSB200_ERR_UNSUPPORTED;
-  // K splits: fill the SMs once (prefer a single, nearly full wave); each split keeps >= 4 k-blocks
-  int splits = 1;
-  if (base < sms * 3 / 4 && base <= kMaxCounters) {
-    int lo = (int)(sms / base), hi = (int)((sms + base - 1) / base);
-    splits = (base * lo >= sms * 3 / 4) ? lo : hi;
-    const int cap = kb_total / 4 > 0 ? kb_total / 4 : 1;
-    if (splits > cap) splits = cap;
-    if (splits < 1) splits = 1;
-  }
-  const int kb_per_split = (kb_total + splits - 1) / splits;
-  splits = (kb_total + kb_per_split - 1) / kb_per_split;
+  if ((int64_t)g.n_tiles * g.m_tiles * g.splits > 0x3fffffffLL) return TSB200_ERR_UNSUPPORTED;
   QParams p;
   p.M = M; p.N = N; p.K = K;
-  p.kb_total = kb_total; p.kb_per_split = kb_per_split; p.splits = splits;
-  p.n_tiles = (int)n_tiles; p.m_tiles = (int)m_tiles; p.items = (int)(base * splits);
+  p.kb_total = g.kb_total; p.kb_per_split = g.kb_per_split; p.splits = g.splits;
+  p.n_tiles = g.n_tiles; p.m_tiles = g.m_tiles; p.items = g.items;
   p.scale = scale; p.bias = (const __nv_bfloat16*)bias; p.y = (__nv_bfloat16*)y;
   p.partial = partial; p.counters = counters; p.status = status;
   const int grid = p.items < sms ? p.items : sms;

@@ -16,6 +16,38 @@ constexpr size_t kWsCounters = 256;
 constexpr int kMaxCounters = 4096;
 constexpr size_t kWsHeader = kWsCounters + kMaxCounters * sizeof(int);
 
+// Work decomposition of one packed-weight GEMM (host): token tile, K splits, item count.
+// Planned for a fixed 148-SM part so that workspace sizing and launch agree; the launch clamps
+// the grid to the SMs actually present.
+constexpr int kPlanSMs = 148;
+struct GemmPlan {
+  int tn, kb_total, kb_per_split, splits, n_tiles, m_tiles, items;
+  size_t slice_bytes;      // split-K scratch: one fp32 [tn][128] slice per item (0 when splits == 1)
+};
+inline GemmPlan plan_gemm(int64_t M, int64_t N, int64_t K) {
+  GemmPlan g;
+  g.tn = M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : 128));
+  g.kb_total = (int)((K + BK - 1) / BK);
+  const int64_t n_tiles = (N + BM - 1) / BM, m_tiles = (M + g.tn - 1) / g.tn;
+  const int64_t base = n_tiles * m_tiles;
+  int splits = 1;
+  if (base > 0 && base < kPlanSMs * 3 / 4 && base <= kMaxCounters) {
+    // fill the SMs once (prefer a single, nearly full wave); each split keeps >= 4 k-blocks
+    const int lo = (int)(kPlanSMs / base), hi = (int)((kPlanSMs + base - 1) / base);
+    splits = (base * lo >= kPlanSMs * 3 / 4) ? lo : hi;
+    const int cap = g.kb_total / 4 > 0 ? g.kb_total / 4 : 1;
+    if (splits > cap) splits = cap;
+    if (splits < 1) splits = 1;
+  }
+  g.kb_per_split = (g.kb_total + splits - 1) / splits;
+  g.splits = (g.kb_total + g.kb_per_split - 1) / g.kb_per_split;
+  g.n_tiles = (int)n_tiles;
+  g.m_tiles = (int)m_tiles;
+  g.items = (int)(base * g.splits);
+  g.slice_bytes = g.splits > 1 ? (size_t)g.items * g.tn * BM * sizeof(float) : 0;
+  return g;
+}
+
 // ---------------------------------------------------------------- PTX wrappers -----
 __device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
 
