@@ -6,7 +6,7 @@
 // keeping many weight bytes in flight per SM and paying the set-up cost once per SM:
 //   * grid = min(#work items, #SMs); a work item = (128-row weight tile, token tile, K split);
 //     each CTA walks its items round-robin while one producer lane keeps issuing TMA loads
-//     across item boundaries into a deep ring (up to 16 stages) of {raw codes, activation tile};
+//     across item boundaries into a ring of stages {raw codes of several k-blocks, activation tiles};
 //   * 8 dequant warps turn raw codes into bf16 (exact integers) inside a small ring of
 //     128-byte-swizzled A tiles; one lane issues tcgen05.mma (weights = A operand, M = 128;
 //     tokens = B operand, N = token tile) accumulating in TMEM;
@@ -28,11 +28,17 @@ constexpr int kDqWarps = 8;
 constexpr int kThreadsQ = 64 + kDqWarps * 32;
 constexpr int kSmemBudget = 200 * 1024;
 
+// A ring stage holds KBS consecutive k-blocks: one weight box of 128 rows x (KBS*64 codes) - rows of
+// up to 128 bytes, so every row is one full-width DRAM request - and KBS activation tiles.
 template <int TN, int BITS> struct QLayout {
+  static constexpr int kKbsFull = 1024 / BITS / BK;        // k-blocks in a 128-byte row of codes
+  static constexpr int KBS = TN <= 32 ? kKbsFull : (kKbsFull < 2 ? kKbsFull : 2);
   static constexpr int kRawRow = BK * BITS / 8;            // bytes of one weight row per k-block
-  static constexpr int kRaw = BM * kRawRow;
-  static constexpr int kX = TN * 128;
-  static constexpr int kStage = kX + kRaw;                 // multiple of 1024 (TN >= 16, BITS >= 2 -> kRaw >= 2048)
+  static constexpr int kRawStageRow = KBS * kRawRow;       // bytes of one weight row per stage
+  static constexpr int kRaw = BM * kRawStageRow;
+  static constexpr int kXTile = TN * 128;
+  static constexpr int kX = KBS * kXTile;
+  static constexpr int kStage = kX + kRaw;                 // multiple of 1024
   static constexpr int kATile = BM * 128;
   static constexpr int kNRraw = (kSmemBudget - NA * kATile) / kStage;
   static constexpr int NR = kNRraw > 16 ? 16 : kNRraw;
@@ -40,11 +46,21 @@ template <int TN, int BITS> struct QLayout {
   static constexpr int kBytes = NA * kATile + NR * kStage + kBarBytes + 1024;
 };
 
-// One dequant thread converts half a weight row of the k-block: 32 codes -> 4 chunks of 8 bf16.
-template <int BITS>
-__device__ __forceinline__ void dequant_half_row(const uint8_t* __restrict__ raw_row, uint8_t* a_tile, int r, int half) {
+// Address of 16-byte chunk `chunk` of weight row `row` inside a raw stage whose rows are RB bytes and
+// which the copy engine wrote with the RB-byte swizzle (chunk index XOR a function of the row), so
+// that threads reading the same chunk of consecutive rows hit different banks.
+template <int RB>
+__device__ __forceinline__ const uint8_t* raw_chunk(const uint8_t* raw, int row, int chunk) {
+  const int x = RB == 128 ? (row & 7) : (RB == 64 ? ((row >> 1) & 3) : ((row >> 2) & 1));
+  return raw + row * RB + ((chunk ^ x) << 4);
+}
+
+// One dequant thread converts half a weight row of k-block `sub` of the stage: 32 codes -> 4 chunks of
+// 8 bf16 written into the 128-byte-swizzled A tile.
+template <int BITS, int RB>
+__device__ __forceinline__ void dequant_half_row(const uint8_t* __restrict__ raw, uint8_t* a_tile, int r, int sub, int half) {
   if (BITS == 4) {
-    const uint4 q = *reinterpret_cast<const uint4*>(raw_row + 16 * half);
+    const uint4 q = *reinterpret_cast<const uint4*>(raw_chunk<RB>(raw, r, sub * 2 + half));
     const unsigned w[4] = {q.x, q.y, q.z, q.w};
 #pragma unroll
     for (int c = 0; c < 4; ++c) {
@@ -57,7 +73,7 @@ __device__ __forceinline__ void dequant_half_row(const uint8_t* __restrict__ raw
       store_chunk(a_tile, r, 4 * half + c, o);
     }
   } else if (BITS == 2) {
-    const uint2 q = *reinterpret_cast<const uint2*>(raw_row + 8 * half);
+    const uint2 q = *reinterpret_cast<const uint2*>(raw_chunk<RB>(raw, r, sub) + 8 * half);
     const unsigned w[2] = {q.x, q.y};
 #pragma unroll
     for (int g = 0; g < 2; ++g) {
@@ -75,7 +91,7 @@ __device__ __forceinline__ void dequant_half_row(const uint8_t* __restrict__ raw
   } else {  // 8-bit
 #pragma unroll
     for (int c = 0; c < 4; ++c) {
-      const uint2 q = *reinterpret_cast<const uint2*>(raw_row + 32 * half + 8 * c);
+      const uint2 q = *reinterpret_cast<const uint2*>(raw_chunk<RB>(raw, r, sub * 4 + half * 2 + (c >> 1)) + 8 * (c & 1));
       const unsigned t0 = q.x ^ 0x80808080u, t1 = q.y ^ 0x80808080u;
       float f[8];
 #pragma unroll
@@ -127,6 +143,7 @@ __global__ void __launch_bounds__(kThreadsQ, 1)
 linear_tcq_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, QParams p) {
   using L = QLayout<TN, BITS>;
   constexpr int NR = L::NR;
+  constexpr int KBS = L::KBS;
   constexpr unsigned TX_BYTES = (unsigned)L::kStage;
   constexpr unsigned TMEM_COLS = TN < 32 ? 32 : TN;
   extern __shared__ uint8_t smem_raw[];
@@ -174,18 +191,20 @@ linear_tcq_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
   if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer
     if (lane == 0) {
-      int g = 0;                                              // global k-block counter of this CTA
+      int gs = 0;                                             // global stage counter of this CTA
       bool ok = true;
       for (int item = blockIdx.x; item < p.items && ok; item += gridDim.x) {
         int nt, mt, kb0, nkb;
         decode(item, nt, mt, kb0, nkb);
-        for (int i = 0; i < nkb; ++i, ++g) {
-          const int s = g % NR;
-          if (g >= NR && !mbar_wait(&raw_empty[s], ((g / NR) - 1) & 1, abort_flag, 1)) { ok = false; break; }
+        for (int i = 0; i < nkb; i += KBS, ++gs) {
+          const int s = gs % NR;
+          if (gs >= NR && !mbar_wait(&raw_empty[s], ((gs / NR) - 1) & 1, abort_flag, 1)) { ok = false; break; }
           uint8_t* st = r_ring + s * L::kStage;
           mbar_expect_tx(&raw_full[s], TX_BYTES);
           const int kcol = (kb0 + i) * BK;
-          tma_load_2d(st, &map_x, kcol, mt * TN, &raw_full[s]);
+#pragma unroll
+          for (int j = 0; j < KBS; ++j)                       // columns beyond K are zero-filled by the copy engine
+            tma_load_2d(st + j * L::kXTile, &map_x, kcol + j * BK, mt * TN, &raw_full[s]);
           tma_load_2d(st + L::kX, &map_w, kcol * BITS / 8, nt * BM, &raw_full[s]);
         }
       }
@@ -194,23 +213,24 @@ linear_tcq_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
     // ---------------------------------------------------------------- MMA issuer
     if (lane == 0) {
       constexpr unsigned idesc = idesc_bf16(TN);
-      int g = 0;
+      int g = 0, gs = 0;                                      // k-block / stage counters of this CTA
       bool ok = true;
       for (int item = blockIdx.x; item < p.items && ok; item += gridDim.x) {
         int nt, mt, kb0, nkb;
         decode(item, nt, mt, kb0, nkb);
         for (int i = 0; i < nkb; ++i, ++g) {
-          const int s = g % NR, a = g % NA;
-          ok = mbar_wait(&raw_full[s], (g / NR) & 1, abort_flag, 2) && mbar_wait(&a_ready[a], (g / NA) & 1, abort_flag, 3);
+          const int sub = i % KBS;
+          const int s = gs % NR, a = g % NA;
+          ok = mbar_wait(&raw_full[s], (gs / NR) & 1, abort_flag, 2) && mbar_wait(&a_ready[a], (g / NA) & 1, abort_flag, 3);
           if (!ok) break;
           tc_fence_after();
           const unsigned long long adesc = smem_desc_sw128(smem_u32(a_ring + a * L::kATile));
-          const unsigned long long bdesc = smem_desc_sw128(smem_u32(r_ring + s * L::kStage));
+          const unsigned long long bdesc = smem_desc_sw128(smem_u32(r_ring + s * L::kStage + sub * L::kXTile));
 #pragma unroll
           for (int k = 0; k < BK / 16; ++k)
             umma_bf16(tmem_base, adesc + 2 * k, bdesc + 2 * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
           umma_commit(&a_empty[a]);
-          umma_commit(&raw_empty[s]);
+          if (sub == KBS - 1 || i == nkb - 1) { umma_commit(&raw_empty[s]); ++gs; }
         }
         if (ok) umma_commit(acc_full);
       }
@@ -221,21 +241,27 @@ linear_tcq_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
     const int row = td & 127, half = td >> 7;
     const int q = warp & 3;                                  // TMEM lane quarter of this warp
     const int chalf = (warp - 2) >> 2;                       // which half of the token columns
-    int g = 0, it = 0, ep_uses = 0;
+    int g = 0, gs = 0, it = 0, ep_uses = 0;
     bool ok = true;
     for (int item = blockIdx.x; item < p.items && ok; item += gridDim.x, ++it) {
       int nt, mt, kb0, nkb;
       decode(item, nt, mt, kb0, nkb);
       for (int i = 0; i < nkb; ++i, ++g) {
-        const int s = g % NR, a = g % NA;
-        ok = mbar_wait(&raw_full[s], (g / NR) & 1, abort_flag, 4);
+        const int sub = i % KBS;
+        const int s = gs % NR, a = g % NA;
+        ok = mbar_wait(&raw_full[s], (gs / NR) & 1, abort_flag, 4);
         if (ok && g >= NA) ok = mbar_wait(&a_empty[a], ((g / NA) - 1) & 1, abort_flag, 5);
         if (!ok) break;
         const uint8_t* raw = r_ring + s * L::kStage + L::kX;
-        dequant_half_row<BITS>(raw + row * L::kRawRow, a_ring + a * L::kATile, row, half);
+        dequant_half_row<BITS, L::kRawStageRow>(raw, a_ring + a * L::kATile, row, sub, half);
         fence_async_proxy();
         __syncwarp();
-        if (lane == 0) { mbar_arrive(&a_ready[a]); mbar_arrive(&raw_empty[s]); }
+        const bool stage_done = (sub == KBS - 1 || i == nkb - 1);
+        if (lane == 0) {
+          mbar_arrive(&a_ready[a]);
+          if (stage_done) mbar_arrive(&raw_empty[s]);
+        }
+        if (stage_done) ++gs;
       }
       if (!ok) break;
       ok = mbar_wait(acc_full, it & 1, abort_flag, 6);
@@ -340,6 +366,13 @@ int launch_q_bits(int bits, const CUtensorMap& mw, const CUtensorMap& mx, const 
   }
 }
 
+// Inner extent (bytes) of the weight box: must equal QLayout<TN, BITS>::kRawStageRow.
+int raw_box_bytes(int tn, int bits) {
+  const int full = 1024 / bits / BK;
+  const int kbs = tn <= 32 ? full : (full < 2 ? full : 2);
+  return kbs * BK * bits / 8;
+}
+
 int num_sms() {
   static int sms[64] = {0};
   int dev = 0;
@@ -362,7 +395,9 @@ int gemm_tcq(const void* W, int bits, const float* scale, const void* bias, cons
   const int tn = g.tn;
   CUtensorMap mw, mx;
   const uint64_t rb = tsb200_packed_row_bytes(K, bits);
-  if (!make_map(&mw, CU_TENSOR_MAP_DATA_TYPE_UINT8, W, rb, (uint64_t)N, rb, (uint32_t)(BK * bits / 8), BM, CU_TENSOR_MAP_SWIZZLE_NONE))
+  if (!make_map(&mw, CU_TENSOR_MAP_DATA_TYPE_UINT8, W, rb, (uint64_t)N, rb, (uint32_t)raw_box_bytes(tn, bits), BM,
+                raw_box_bytes(tn, bits) == 128 ? CU_TENSOR_MAP_SWIZZLE_128B
+                                               : (raw_box_bytes(tn, bits) == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B)))
     return TSB200_ERR_CUDA;
   if (!make_map(&mx, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, x, (uint64_t)K, (uint64_t)M, (uint64_t)K * 2, BK, (uint32_t)tn, CU_TENSOR_MAP_SWIZZLE_128B))
     return TSB200_ERR_CUDA;
