@@ -3,18 +3,23 @@
 // restating transformersurgeon/blocks/linear_compressed.py:96-100 on packed codes.
 //
 // Decode-time GEMMs stream a few MB of packed weights per call, so the kernel is built around
-// keeping many weight bytes in flight per SM and paying the set-up cost once per SM:
+// keeping many weight bytes in flight per SM, paying the set-up cost once per SM, and
+// synchronising once per 16 KB of weights rather than once per k-block:
 //   * grid = min(#work items, #SMs); a work item = (128-row weight tile, token tile, K split);
 //     each CTA walks its items round-robin while one producer lane keeps issuing TMA loads
-//     across item boundaries into a ring of stages {raw codes of several k-blocks, activation tiles};
-//   * 8 dequant warps turn raw codes into bf16 (exact integers) inside a small ring of
-//     128-byte-swizzled A tiles; one lane issues tcgen05.mma (weights = A operand, M = 128;
-//     tokens = B operand, N = token tile) accumulating in TMEM;
-//   * the same 8 warps run the epilogue from TMEM (one lane = one weight row): scale, bias, store;
+//     across item boundaries into a ring of STAGES.  A stage = KBS consecutive k-blocks: one
+//     weight box of 128 rows x up to 128 bytes of codes (swizzled) + KBS activation tiles;
+//   * two groups of 4 dequant warps take stages alternately.  A thread owns one weight row:
+//     it reads the row's codes from shared memory, widens them to bf16 pairs in registers (exact
+//     integers) and stores them with tcgen05.st straight into TENSOR MEMORY, where they are the
+//     A operand of the MMA (M = 128 weight rows; K-major, two bf16 per 32-bit column) - no
+//     shared-memory A tile, no generic->async proxy fence;
+//   * one lane issues tcgen05.mma (A from TMEM, B = activation tile from shared memory through a
+//     128-byte-swizzle descriptor, N = token tile) accumulating in TMEM columns [0, TN);
+//   * all 8 warps run the epilogue from TMEM (one lane = one weight row): scale, bias, store;
 //   * split-K: every item stores its fp32 partial tile in a private slice of the workspace (plain
 //     stores, no zero-fill needed); the last CTA to finish a tile (a per-tile counter, reset by
-//     that CTA) sums the slices in split order - a deterministic result - and writes the
-//     output, so no memset and no second kernel are needed.
+//     that CTA) sums the slices in split order - a deterministic result - and writes the output.
 // Every mbarrier wait is bounded (see tc_common.cuh); on expiry the CTA records a code in the
 // status word, drains, frees its TMEM and returns.
 #include "tc_common.cuh"
@@ -23,98 +28,118 @@ namespace tsb {
 using namespace tc;
 namespace {
 
-constexpr int NA = 3;                  // A-tile ring depth
-constexpr int kDqWarps = 8;
+constexpr int kDqWarps = 8;                 // two groups of four
 constexpr int kThreadsQ = 64 + kDqWarps * 32;
-constexpr int kSmemBudget = 200 * 1024;
+constexpr int kSmemBudget = 208 * 1024;
+constexpr unsigned kTmemCols = 512;
+constexpr unsigned kACol0 = 128;            // TMEM column of A buffer 0; buffer 1 follows at +128
 
-// A ring stage holds KBS consecutive k-blocks: one weight box of 128 rows x (KBS*64 codes) - rows of
-// up to 128 bytes, so every row is one full-width DRAM request - and KBS activation tiles.
 template <int TN, int BITS> struct QLayout {
   static constexpr int kKbsFull = 1024 / BITS / BK;        // k-blocks in a 128-byte row of codes
-  static constexpr int KBS = TN <= 32 ? kKbsFull : (kKbsFull < 2 ? kKbsFull : 2);
+  static constexpr int kKbsCap = TN <= 32 ? 4 : 2;         // A buffer = KBS * 32 TMEM columns <= 128
+  static constexpr int KBS = kKbsFull < kKbsCap ? kKbsFull : kKbsCap;
   static constexpr int kRawRow = BK * BITS / 8;            // bytes of one weight row per k-block
-  static constexpr int kRawStageRow = KBS * kRawRow;       // bytes of one weight row per stage
+  static constexpr int kRawStageRow = KBS * kRawRow;       // bytes of one weight row per stage (32/64/128)
   static constexpr int kRaw = BM * kRawStageRow;
   static constexpr int kXTile = TN * 128;
   static constexpr int kX = KBS * kXTile;
   static constexpr int kStage = kX + kRaw;                 // multiple of 1024
-  static constexpr int kATile = BM * 128;
-  static constexpr int kNRraw = (kSmemBudget - NA * kATile) / kStage;
-  static constexpr int NR = kNRraw > 16 ? 16 : kNRraw;
+  static constexpr int kNRraw = kSmemBudget / kStage;
+  static constexpr int NR = kNRraw > 12 ? 12 : kNRraw;
   static constexpr int kBarBytes = 1024;
-  static constexpr int kBytes = NA * kATile + NR * kStage + kBarBytes + 1024;
+  static constexpr int kBytes = NR * kStage + kBarBytes + 1024;
 };
 
-// Address of 16-byte chunk `chunk` of weight row `row` inside a raw stage whose rows are RB bytes and
-// which the copy engine wrote with the RB-byte swizzle (chunk index XOR a function of the row), so
-// that threads reading the same chunk of consecutive rows hit different banks.
+__device__ __forceinline__ uint4 lds128(unsigned addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ uint2 lds64(unsigned addr) {
+  uint2 v;
+  asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];\n" : "=r"(v.x), "=r"(v.y) : "r"(addr));
+  return v;
+}
+
+// Shared address of 16-byte chunk `chunk` of weight row `row` inside a raw stage whose rows are RB
+// bytes, written by the copy engine with the RB-byte swizzle (chunk index XOR a function of the row),
+// so threads reading the same chunk of consecutive rows hit different banks.
 template <int RB>
-__device__ __forceinline__ const uint8_t* raw_chunk(const uint8_t* raw, int row, int chunk) {
+__device__ __forceinline__ unsigned raw_chunk(unsigned raw, int row, int chunk) {
   const int x = RB == 128 ? (row & 7) : (RB == 64 ? ((row >> 1) & 3) : ((row >> 2) & 1));
   return raw + row * RB + ((chunk ^ x) << 4);
 }
 
-// One dequant thread converts half a weight row of k-block `sub` of the stage: 32 codes -> 4 chunks of
-// 8 bf16 written into the 128-byte-swizzled A tile.
+// Widen the 64 codes of weight row `r`, k-block `sub` of the stage, to 32 registers of bf16 pairs:
+// register c holds columns (2c, 2c+1) of the k-block - the TMEM A-operand packing.
 template <int BITS, int RB>
-__device__ __forceinline__ void dequant_half_row(const uint8_t* __restrict__ raw, uint8_t* a_tile, int r, int sub, int half) {
+__device__ __forceinline__ void dequant_row_regs(unsigned raw, int r, int sub, unsigned (&o)[32]) {
   if (BITS == 4) {
-    const uint4 q = *reinterpret_cast<const uint4*>(raw_chunk<RB>(raw, r, sub * 2 + half));
-    const unsigned w[4] = {q.x, q.y, q.z, q.w};
 #pragma unroll
-    for (int c = 0; c < 4; ++c) {
-      const unsigned t = w[c] ^ 0x88888888u;
-      uint4 o;
-      o.x = bf16x2_sub(((t)&0x000f000fu) | 0x43004300u, 0x43084308u);
-      o.y = bf16x2_sub(((t >> 4) & 0x000f000fu) | 0x43004300u, 0x43084308u);
-      o.z = bf16x2_sub(((t >> 8) & 0x000f000fu) | 0x43004300u, 0x43084308u);
-      o.w = bf16x2_sub(((t >> 12) & 0x000f000fu) | 0x43004300u, 0x43084308u);
-      store_chunk(a_tile, r, 4 * half + c, o);
+    for (int h = 0; h < 2; ++h) {
+      const uint4 q = lds128(raw_chunk<RB>(raw, r, sub * 2 + h));
+      const unsigned w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const unsigned t = w[c] ^ 0x88888888u;              // nibble + 8; 0x4300 | u = bf16(128 + u)
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          o[h * 16 + c * 4 + j] = bf16x2_sub(((t >> (4 * j)) & 0x000f000fu) | 0x43004300u, 0x43084308u);
+      }
     }
   } else if (BITS == 2) {
-    const uint2 q = *reinterpret_cast<const uint2*>(raw_chunk<RB>(raw, r, sub) + 8 * half);
-    const unsigned w[2] = {q.x, q.y};
+    const uint4 q = lds128(raw_chunk<RB>(raw, r, sub));
+    const unsigned w[4] = {q.x, q.y, q.z, q.w};
 #pragma unroll
-    for (int g = 0; g < 2; ++g) {
-      const unsigned t = w[g] ^ 0xAAAAAAAAu;
+    for (int g = 0; g < 4; ++g) {
+      const unsigned t = w[g] ^ 0xAAAAAAAAu;                // field + 2
 #pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        uint4 o;
-        o.x = bf16x2_sub(((t >> (8 * h)) & 0x00030003u) | 0x43004300u, 0x43024302u);
-        o.y = bf16x2_sub(((t >> (8 * h + 2)) & 0x00030003u) | 0x43004300u, 0x43024302u);
-        o.z = bf16x2_sub(((t >> (8 * h + 4)) & 0x00030003u) | 0x43004300u, 0x43024302u);
-        o.w = bf16x2_sub(((t >> (8 * h + 6)) & 0x00030003u) | 0x43004300u, 0x43024302u);
-        store_chunk(a_tile, r, 4 * half + 2 * g + h, o);
-      }
+      for (int j = 0; j < 8; ++j)
+        o[g * 8 + j] = bf16x2_sub(((t >> (2 * j)) & 0x00030003u) | 0x43004300u, 0x43024302u);
     }
-  } else {  // 8-bit
+  } else {  // 8-bit, natural byte order
 #pragma unroll
-    for (int c = 0; c < 4; ++c) {
-      const uint2 q = *reinterpret_cast<const uint2*>(raw_chunk<RB>(raw, r, sub * 4 + half * 2 + (c >> 1)) + 8 * (c & 1));
-      const unsigned t0 = q.x ^ 0x80808080u, t1 = q.y ^ 0x80808080u;
-      float f[8];
+    for (int c = 0; c < 8; ++c) {
+      const uint2 q = lds64(raw_chunk<RB>(raw, r, sub * 4 + (c >> 1)) + 8 * (c & 1));
+      const unsigned t[2] = {q.x ^ 0x80808080u, q.y ^ 0x80808080u};
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        f[i] = __uint_as_float(0x4B000000u | ((t0 >> (8 * i)) & 0xffu)) - 8388736.0f;
-        f[4 + i] = __uint_as_float(0x4B000000u | ((t1 >> (8 * i)) & 0xffu)) - 8388736.0f;
+      for (int j = 0; j < 4; ++j) {
+        const unsigned tw = t[j >> 1];
+        const float f0 = __uint_as_float(0x4B000000u | ((tw >> (16 * (j & 1))) & 0xffu)) - 8388736.0f;      // 2^23 + 128
+        const float f1 = __uint_as_float(0x4B000000u | ((tw >> (16 * (j & 1) + 8)) & 0xffu)) - 8388736.0f;
+        __nv_bfloat162 p = __floats2bfloat162_rn(f0, f1);
+        o[c * 4 + j] = *reinterpret_cast<unsigned*>(&p);
       }
-      uint4 o;
-      __nv_bfloat162 p;
-      p = __floats2bfloat162_rn(f[0], f[1]); o.x = *reinterpret_cast<unsigned*>(&p);
-      p = __floats2bfloat162_rn(f[2], f[3]); o.y = *reinterpret_cast<unsigned*>(&p);
-      p = __floats2bfloat162_rn(f[4], f[5]); o.z = *reinterpret_cast<unsigned*>(&p);
-      p = __floats2bfloat162_rn(f[6], f[7]); o.w = *reinterpret_cast<unsigned*>(&p);
-      store_chunk(a_tile, r, 4 * half + c, o);
     }
   }
 }
 
+__device__ __forceinline__ void tmem_st32(unsigned taddr, const unsigned (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
+      "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};\n" ::"r"(taddr),
+      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+      "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]),
+      "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]),
+      "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory"); }
 __device__ __forceinline__ void tmem_ld8(unsigned taddr, unsigned (&r)[8]) {
   asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];\n"
                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
                : "r"(taddr)
                : "memory");
+}
+// D[tmem] (+)= A[tmem] . B[smem descriptor]; kind::f16, A K-major in tensor memory.
+__device__ __forceinline__ void umma_bf16_ts(unsigned d_tmem, unsigned a_tmem, unsigned long long bdesc, unsigned idesc,
+                                             unsigned accumulate) {
+  asm volatile(
+      "{\n.reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}\n" ::"r"(d_tmem),
+      "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
 }
 // Rendezvous of the 8 dequant/epilogue warps on an mbarrier (count 8) with a bounded wait, so a
 // warp that gave up elsewhere can never leave the others blocked.
@@ -145,18 +170,16 @@ linear_tcq_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
   constexpr int NR = L::NR;
   constexpr int KBS = L::KBS;
   constexpr unsigned TX_BYTES = (unsigned)L::kStage;
-  constexpr unsigned TMEM_COLS = TN < 32 ? 32 : TN;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-  uint8_t* a_ring = smem;                                   // NA x 16 KB
-  uint8_t* r_ring = smem + NA * L::kATile;                  // NR x {X tile, raw codes}
+  uint8_t* r_ring = smem;                                   // NR x {KBS activation tiles, raw codes}
   unsigned long long* bars = reinterpret_cast<unsigned long long*>(r_ring + NR * L::kStage);
   unsigned long long* raw_full = bars;                      // [NR] TMA landed
-  unsigned long long* raw_empty = bars + NR;                // [NR] 8 dequant warps + MMA commit
-  unsigned long long* a_ready = bars + 2 * NR;              // [NA] 8 dequant warps
-  unsigned long long* a_empty = a_ready + NA;               // [NA] MMA commit
-  unsigned long long* acc_full = a_empty + NA;              // [1]  MMA commit (accumulator complete)
-  unsigned long long* ep_bar = acc_full + 1;                // [1]  epilogue rendezvous of the 8 warps
+  unsigned long long* raw_empty = bars + NR;                // [NR] 4 dequant warps of the owning group + MMA commit
+  unsigned long long* a_ready = bars + 2 * NR;              // [2]  4 dequant warps: A buffer stored in TMEM
+  unsigned long long* a_empty = a_ready + 2;                // [2]  MMA commit: A buffer consumed
+  unsigned long long* acc_full = a_empty + 2;               // [1]  MMA commit: accumulator of the item complete
+  unsigned long long* ep_bar = acc_full + 1;                // [1]  rendezvous of the 8 warps
   unsigned* tmem_slot = reinterpret_cast<unsigned*>(ep_bar + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   volatile int* last_flag = abort_flag + 1;
@@ -164,15 +187,15 @@ linear_tcq_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < NR; ++i) { mbar_init(&raw_full[i], 1); mbar_init(&raw_empty[i], kDqWarps + 1); }
-    for (int i = 0; i < NA; ++i) { mbar_init(&a_ready[i], kDqWarps); mbar_init(&a_empty[i], 1); }
+    for (int i = 0; i < NR; ++i) { mbar_init(&raw_full[i], 1); mbar_init(&raw_empty[i], 4 + 1); }
+    for (int i = 0; i < 2; ++i) { mbar_init(&a_ready[i], 4); mbar_init(&a_empty[i], 1); }
     mbar_init(acc_full, 1);
     mbar_init(ep_bar, kDqWarps);
     *abort_flag = 0;
     *last_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
-  if (warp == 1) tmem_alloc(tmem_slot, TMEM_COLS);
+  if (warp == 1) tmem_alloc(tmem_slot, kTmemCols);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -191,7 +214,7 @@ linear_tcq_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
   if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer
     if (lane == 0) {
-      int gs = 0;                                             // global stage counter of this CTA
+      int gs = 0;                                             // stage counter of this CTA (all items)
       bool ok = true;
       for (int item = blockIdx.x; item < p.items && ok; item += gridDim.x) {
         int nt, mt, kb0, nkb;
@@ -213,76 +236,80 @@ linear_tcq_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
     // ---------------------------------------------------------------- MMA issuer
     if (lane == 0) {
       constexpr unsigned idesc = idesc_bf16(TN);
-      int g = 0, gs = 0;                                      // k-block / stage counters of this CTA
+      int gs = 0;
       bool ok = true;
       for (int item = blockIdx.x; item < p.items && ok; item += gridDim.x) {
         int nt, mt, kb0, nkb;
         decode(item, nt, mt, kb0, nkb);
-        for (int i = 0; i < nkb; ++i, ++g) {
-          const int sub = i % KBS;
-          const int s = gs % NR, a = g % NA;
-          ok = mbar_wait(&raw_full[s], (gs / NR) & 1, abort_flag, 2) && mbar_wait(&a_ready[a], (g / NA) & 1, abort_flag, 3);
+        for (int i = 0; i < nkb; i += KBS, ++gs) {
+          const int s = gs % NR, buf = gs & 1;
+          ok = mbar_wait(&raw_full[s], (gs / NR) & 1, abort_flag, 2) && mbar_wait(&a_ready[buf], (gs >> 1) & 1, abort_flag, 3);
           if (!ok) break;
           tc_fence_after();
-          const unsigned long long adesc = smem_desc_sw128(smem_u32(a_ring + a * L::kATile));
-          const unsigned long long bdesc = smem_desc_sw128(smem_u32(r_ring + s * L::kStage + sub * L::kXTile));
+          const unsigned a_tmem = tmem_base + kACol0 + buf * 128;
+          const unsigned x_base = smem_u32(r_ring + s * L::kStage);
+          const int nsub = min(KBS, nkb - i);
+          for (int j = 0; j < nsub; ++j) {
+            const unsigned long long bdesc = smem_desc_sw128(x_base + j * L::kXTile);
 #pragma unroll
-          for (int k = 0; k < BK / 16; ++k)
-            umma_bf16(tmem_base, adesc + 2 * k, bdesc + 2 * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
-          umma_commit(&a_empty[a]);
-          if (sub == KBS - 1 || i == nkb - 1) { umma_commit(&raw_empty[s]); ++gs; }
+            for (int k = 0; k < BK / 16; ++k)   // A: 8 TMEM columns per K=16; B: +32 bytes inside the swizzle atom
+              umma_bf16_ts(tmem_base, a_tmem + j * 32 + k * 8, bdesc + 2 * k, idesc, (i + j > 0 || k > 0) ? 1u : 0u);
+          }
+          umma_commit(&a_empty[buf]);
+          umma_commit(&raw_empty[s]);
         }
         if (ok) umma_commit(acc_full);
       }
     }
   } else {
     // ---------------------------------------------------------------- dequant + epilogue
-    const int td = threadIdx.x - 64;                         // 0..255
-    const int row = td & 127, half = td >> 7;
-    const int q = warp & 3;                                  // TMEM lane quarter of this warp
-    const int chalf = (warp - 2) >> 2;                       // which half of the token columns
-    int g = 0, gs = 0, it = 0, ep_uses = 0;
+    const int grp = (warp - 2) >> 2;                         // dequant group 0 / 1: stages of that parity
+    const int q = warp & 3;                                  // TMEM lane quarter this warp may access
+    const int row = q * 32 + lane;                           // weight row within the tile = TMEM lane
+    const unsigned lane_addr = tmem_base + ((unsigned)(q * 32) << 16);
+    int gs = 0, it = 0, ep_uses = 0;
     bool ok = true;
     for (int item = blockIdx.x; item < p.items && ok; item += gridDim.x, ++it) {
       int nt, mt, kb0, nkb;
       decode(item, nt, mt, kb0, nkb);
-      for (int i = 0; i < nkb; ++i, ++g) {
-        const int sub = i % KBS;
-        const int s = gs % NR, a = g % NA;
+      for (int i = 0; i < nkb; i += KBS, ++gs) {
+        if ((gs & 1) != grp) continue;
+        const int s = gs % NR, buf = gs & 1;
         ok = mbar_wait(&raw_full[s], (gs / NR) & 1, abort_flag, 4);
-        if (ok && g >= NA) ok = mbar_wait(&a_empty[a], ((g / NA) - 1) & 1, abort_flag, 5);
+        if (ok && gs >= 2) ok = mbar_wait(&a_empty[buf], ((gs >> 1) - 1) & 1, abort_flag, 5);
         if (!ok) break;
-        const uint8_t* raw = r_ring + s * L::kStage + L::kX;
-        dequant_half_row<BITS, L::kRawStageRow>(raw, a_ring + a * L::kATile, row, sub, half);
-        fence_async_proxy();
-        __syncwarp();
-        const bool stage_done = (sub == KBS - 1 || i == nkb - 1);
-        if (lane == 0) {
-          mbar_arrive(&a_ready[a]);
-          if (stage_done) mbar_arrive(&raw_empty[s]);
+        tc_fence_after();
+        const unsigned raw = smem_u32(r_ring + s * L::kStage + L::kX);
+        const int nsub = min(KBS, nkb - i);
+        for (int j = 0; j < nsub; ++j) {
+          unsigned regs[32];
+          dequant_row_regs<BITS, L::kRawStageRow>(raw, row, j, regs);
+          tmem_st32(lane_addr + kACol0 + buf * 128 + j * 32, regs);
         }
-        if (stage_done) ++gs;
+        tmem_st_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) { mbar_arrive(&a_ready[buf]); mbar_arrive(&raw_empty[s]); }
       }
       if (!ok) break;
       ok = mbar_wait(acc_full, it & 1, abort_flag, 6);
       if (!ok) break;
       tc_fence_after();
-      const int trow = q * 32 + lane;                        // TMEM lane = weight row within the tile
-      const int64_t n = (int64_t)nt * BM + trow;
+      const int64_t n = (int64_t)nt * BM + row;
       const int64_t m0 = (int64_t)mt * TN;
       const bool split = p.splits > 1;
       const float sc = (p.scale && n < p.N) ? p.scale[n] : 1.0f;
       const float bv = (p.bias && n < p.N) ? __bfloat162float(p.bias[n]) : 0.f;
-      constexpr int CH = TN / 2;                             // columns handled by this warp
+      constexpr int CH = TN / 2;                             // token columns handled by this warp
       float* slice = p.partial + (size_t)item * (TN * BM);   // [TN][128] of this item
 #pragma unroll 1
-      for (int c0 = chalf * CH; c0 < (chalf + 1) * CH; c0 += 8) {
+      for (int c0 = grp * CH; c0 < (grp + 1) * CH; c0 += 8) {
         unsigned r[8];
-        tmem_ld8(tmem_base + ((unsigned)(q * 32) << 16) + (unsigned)c0, r);
+        tmem_ld8(lane_addr + (unsigned)c0, r);
         tmem_ld_wait();
         if (split) {
 #pragma unroll
-          for (int j = 0; j < 8; ++j) __stcg(&slice[(c0 + j) * BM + trow], __uint_as_float(r[j]));
+          for (int j = 0; j < 8; ++j) __stcg(&slice[(c0 + j) * BM + row], __uint_as_float(r[j]));
         } else if (n < p.N) {
 #pragma unroll
           for (int j = 0; j < 8; ++j) {
@@ -292,11 +319,13 @@ linear_tcq_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
         }
       }
       tc_fence_before();
+      // every warp is done reading the accumulator before any warp stores the next item's A operand
+      if (!(ok = warps_rendezvous(ep_bar, ep_uses, lane, abort_flag))) break;
       if (split) {
         // last CTA of this (n tile, m tile) finalizes: sum of the slices -> y, then reset the counter
         __threadfence();
         if (!(ok = warps_rendezvous(ep_bar, ep_uses, lane, abort_flag))) break;
-        if (td == 0) {
+        if (threadIdx.x == 64) {
           const int old = atomicAdd(&p.counters[mt * p.n_tiles + nt], 1);
           *last_flag = (old == p.splits - 1);
         }
@@ -306,16 +335,22 @@ linear_tcq_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
           __threadfence();
           if (n < p.N) {
             const float* tile0 = p.partial + (size_t)(item - item % p.splits) * (TN * BM);
-            for (int c = chalf * CH; c < (chalf + 1) * CH; ++c) {
+            for (int c = grp * CH; c < (grp + 1) * CH; ++c) {
               const int64_t m = m0 + c;
-              if (m < p.M) {
-                float v = 0.f;
-                for (int sp = 0; sp < p.splits; ++sp) v += __ldcg(&tile0[(size_t)sp * (TN * BM) + c * BM + trow]);
-                p.y[m * p.N + n] = __float2bfloat16_rn(v * sc + bv);
+              if (m >= p.M) break;
+              const float* src = tile0 + c * BM + row;
+              float v = 0.f;
+              int sp = 0;
+              for (; sp + 4 <= p.splits; sp += 4) {          // four loads in flight; fixed summation order
+                const float a0 = __ldcg(src + (size_t)(sp + 0) * (TN * BM)), a1 = __ldcg(src + (size_t)(sp + 1) * (TN * BM));
+                const float a2 = __ldcg(src + (size_t)(sp + 2) * (TN * BM)), a3 = __ldcg(src + (size_t)(sp + 3) * (TN * BM));
+                v = (((v + a0) + a1) + a2) + a3;
               }
+              for (; sp < p.splits; ++sp) v += __ldcg(src + (size_t)sp * (TN * BM));
+              p.y[m * p.N + n] = __float2bfloat16_rn(v * sc + bv);
             }
           }
-          if (td == 0) p.counters[mt * p.n_tiles + nt] = 0;
+          if (threadIdx.x == 64) p.counters[mt * p.n_tiles + nt] = 0;
         }
         if (!(ok = warps_rendezvous(ep_bar, ep_uses, lane, abort_flag))) break;   // last_flag is reused by the next item
       }
@@ -329,7 +364,7 @@ linear_tcq_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
   __syncthreads();
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, TMEM_COLS);
+    tmem_dealloc(tmem_base, kTmemCols);
   }
   if (threadIdx.x == 0 && *abort_flag) atomicMax(p.status, *abort_flag);
 }
@@ -369,7 +404,8 @@ int launch_q_bits(int bits, const CUtensorMap& mw, const CUtensorMap& mx, const 
 // Inner extent (bytes) of the weight box: must equal QLayout<TN, BITS>::kRawStageRow.
 int raw_box_bytes(int tn, int bits) {
   const int full = 1024 / bits / BK;
-  const int kbs = tn <= 32 ? full : (full < 2 ? full : 2);
+  const int cap = tn <= 32 ? 4 : 2;
+  const int kbs = full < cap ? full : cap;
   return kbs * BK * bits / 8;
 }
 
