@@ -57,6 +57,11 @@ int tsb200_version(void);
 int tsb200_last_cuda_error(void);
 /* TSB200_OK when the CURRENT device can run this library (compute capability 10.0). */
 int tsb200_check_device(void);
+/* Programmatic dependent launch for the decode-step kernels (linear, rope_append, decode
+ * attention, add_rmsnorm, swiglu): when enabled, each launch may start while its predecessor on
+ * the stream drains; the kernels order their dependent memory accesses themselves.  Process-wide;
+ * returns the previous setting.  Default 0. */
+int tsb200_set_pdl(int enabled);
 
 /* ------------------------------------------------------------------------------------
  * Weight quantization, packing, reconstruction

@@ -43,6 +43,7 @@ SIGNATURES = {
     "tsb200_version": (_i32, []),
     "tsb200_last_cuda_error": (_i32, []),
     "tsb200_check_device": (_i32, []),
+    "tsb200_set_pdl": (_i32, [_i32]),
     "tsb200_packed_row_bytes": (_sz, [_i64, _i32]),
     "tsb200_quantize_weight": (_i32, [_vp, _i32, _i64, _i64, _i32, _i32, _f32, _vp, _vp, _vp, _sz, _vp]),
     "tsb200_pack_codes": (_i32, [_vp, _i64, _i64, _i32, _vp, _vp, _vp]),

@@ -3,6 +3,7 @@
 
 namespace tsb {
 int g_last_cuda_error = 0;
+int g_pdl = 0;
 
 int check_device_cached() {
   // Cached per device ordinal: 0 = unknown, 1 = ok, 2 = wrong architecture.
@@ -39,5 +40,10 @@ const char* tsb200_strerror(int status) {
 int tsb200_version(void) { return 100; }
 int tsb200_last_cuda_error(void) { return tsb::g_last_cuda_error; }
 int tsb200_check_device(void) { return tsb::check_device_cached(); }
+int tsb200_set_pdl(int enabled) {
+  const int old = tsb::g_pdl;
+  tsb::g_pdl = enabled ? 1 : 0;
+  return old;
+}
 
 }  // extern "C"

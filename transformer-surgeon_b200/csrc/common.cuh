@@ -23,6 +23,35 @@ inline int cuda_fail(cudaError_t e) {
   } while (0)
 #define TSB_LAUNCH_CHECK() TSB_CUDA(cudaPeekAtLastError())
 
+// Programmatic dependent launch (tsb200_set_pdl): kernels are launched with the programmatic
+// stream-serialization attribute, so a kernel's prologue (and its loads of constant weights) may
+// overlap the tail of its predecessor; every kernel calls pdl_wait() before it reads or writes
+// anything a predecessor may still touch.
+extern int g_pdl;
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s,
+                                 Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = g_pdl ? attr : nullptr;
+  cfg.numAttrs = g_pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
+#ifdef __CUDACC__
+// Wait until every prerequisite grid has completed and its memory is visible (no-op without PDL).
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
+// Allow the dependent grid to start launching (it still waits in pdl_wait for this grid to finish).
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
+#endif
+
 int check_device_cached();   // TSB200_OK iff current device is CC 10.0
 #define TSB_REQUIRE_DEVICE()                    \
   do {                                          \

@@ -78,6 +78,8 @@ decode_attn_mma_kernel(tsb200_kv_desc kv, const T* __restrict__ q, int64_t qs, i
   constexpr int STAGE = 2 * REC;
   constexpr int NC = D / 16;                    // k-steps of QK, m-tiles of PV
   extern __shared__ __align__(128) uint8_t smem[];
+  pdl_launch_dependents();
+  pdl_wait();     // q, the page just appended and seq_lens come from the preceding kernels
 
   const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
   const int gid = lane >> 2, tid = lane & 3;
@@ -269,8 +271,8 @@ int launch_mma(const tsb200_kv_desc& kv, const void* q, int64_t qs, int H, float
   }
   const int g = H / kv.hkv;
   dim3 grid((unsigned)(B * kv.hkv), (unsigned)S, (unsigned)((g + 7) / 8));
-  decode_attn_mma_kernel<T, D, FMT><<<grid, kWarps * 32, smem, st>>>(kv, (const T*)q, qs, H, sm_scale, max_seq_len, S, ws);
-  TSB_LAUNCH_CHECK();
+  TSB_CUDA(launch_kernel(decode_attn_mma_kernel<T, D, FMT>, grid, dim3(kWarps * 32), smem, st, kv, (const T*)q, qs, H, sm_scale,
+                         max_seq_len, S, ws));
   return TSB200_OK;
 }
 

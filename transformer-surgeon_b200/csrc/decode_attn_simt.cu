@@ -87,6 +87,8 @@ __global__ void decode_attn_simt_kernel(tsb200_kv_desc kv, const T* __restrict__
 template <typename T, int D>
 __global__ void decode_attn_reduce_kernel(const float* __restrict__ ws, int64_t BH, int S, T* __restrict__ out) {
   constexpr int EPL = D / 32;
+  pdl_launch_dependents();
+  pdl_wait();
   const int lane = threadIdx.x & 31;
   const int64_t bh = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5;
   if (bh >= BH) return;
@@ -111,8 +113,7 @@ __global__ void decode_attn_reduce_kernel(const float* __restrict__ ws, int64_t 
 template <typename T, int D>
 int launch_reduce(const float* ws, int64_t BH, int S, void* out, cudaStream_t st) {
   const int64_t blocks = (BH + 3) / 4;
-  decode_attn_reduce_kernel<T, D><<<(unsigned)blocks, 128, 0, st>>>(ws, BH, S, (T*)out);
-  TSB_LAUNCH_CHECK();
+  TSB_CUDA(launch_kernel(decode_attn_reduce_kernel<T, D>, dim3((unsigned)blocks), dim3(128), 0, st, ws, BH, S, (T*)out));
   return TSB200_OK;
 }
 template int launch_reduce<float, 64>(const float*, int64_t, int, void*, cudaStream_t);

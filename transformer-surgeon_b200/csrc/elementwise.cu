@@ -99,6 +99,8 @@ __global__ void __launch_bounds__(256)
 add_rmsnorm_hf_bf16_kernel(__nv_bfloat16* __restrict__ residual, const __nv_bfloat16* __restrict__ delta,
                            const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ y, int hidden, float eps) {
   __shared__ float sh[32];
+  pdl_launch_dependents();
+  pdl_wait();
   const int64_t row = blockIdx.x;
   const int nvec = hidden >> 3;
   uint4* r = reinterpret_cast<uint4*>(residual + row * hidden);
@@ -162,6 +164,8 @@ add_rmsnorm_hf_bf16_kernel(__nv_bfloat16* __restrict__ residual, const __nv_bflo
 template <typename T>
 __global__ void swiglu_kernel(const T* __restrict__ gate, const T* __restrict__ up, T* __restrict__ y, int64_t M, int64_t n,
                               int64_t gs, int64_t us, int64_t ys) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int64_t total = M * n;
   for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
     const int64_t m = i / n, c = i - m * n;
@@ -211,9 +215,9 @@ int tsb200_add_rmsnorm(void* residual, const void* delta, const void* w, void* y
   if (M > 0x7fffffffLL) return TSB200_ERR_UNSUPPORTED;
   if (dtype == TSB200_BF16 && variant == 0 && hidden % 8 == 0 && hidden <= 8192 && aligned(residual, 16) &&
       aligned(y, 16) && aligned(w, 16) && (!delta || aligned(delta, 16))) {
-    add_rmsnorm_hf_bf16_kernel<<<(unsigned)M, 256, 0, as_stream(stream)>>>(
-        (__nv_bfloat16*)residual, (const __nv_bfloat16*)delta, (const __nv_bfloat16*)w, (__nv_bfloat16*)y, (int)hidden, eps);
-    TSB_LAUNCH_CHECK();
+    TSB_CUDA(launch_kernel(add_rmsnorm_hf_bf16_kernel, dim3((unsigned)M), dim3(256), 0, as_stream(stream),
+                           (__nv_bfloat16*)residual, (const __nv_bfloat16*)delta, (const __nv_bfloat16*)w, (__nv_bfloat16*)y,
+                           (int)hidden, eps));
     return TSB200_OK;
   }
   if (dtype == TSB200_F32)
@@ -235,7 +239,8 @@ int tsb200_swiglu(const void* gate, const void* up, void* y, int dtype, int64_t 
   if (dtype == TSB200_F32)
     swiglu_kernel<float><<<egrid(M * n), 256, 0, as_stream(stream)>>>((const float*)gate, (const float*)up, (float*)y, M, n, gate_stride, up_stride, y_stride);
   else if (dtype == TSB200_BF16)
-    swiglu_kernel<__nv_bfloat16><<<egrid(M * n), 256, 0, as_stream(stream)>>>((const __nv_bfloat16*)gate, (const __nv_bfloat16*)up, (__nv_bfloat16*)y, M, n, gate_stride, up_stride, y_stride);
+    TSB_CUDA(launch_kernel(swiglu_kernel<__nv_bfloat16>, dim3(egrid(M * n)), dim3(256), 0, as_stream(stream),
+                           (const __nv_bfloat16*)gate, (const __nv_bfloat16*)up, (__nv_bfloat16*)y, M, n, gate_stride, up_stride, y_stride));
   else
     return TSB200_ERR_UNSUPPORTED;
   TSB_LAUNCH_CHECK();

@@ -124,6 +124,8 @@ __global__ void kv_append_kernel(tsb200_kv_desc kv, T* __restrict__ q, int64_t q
                                  int64_t vs_, int64_t B,
                                  int64_t Tn, const int32_t* __restrict__ new_lens, const float* __restrict__ rope_cos,
                                  const float* __restrict__ rope_sin, int64_t rope_rows, int64_t rec_bytes) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int lane = threadIdx.x & 31;
   const int64_t warp = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5;
   const int64_t total = B * Tn * kv.hkv;
@@ -217,16 +219,16 @@ int launch_append(const tsb200_kv_desc& kv, void* q, int64_t qs, int qheads, con
   const int64_t rec = (int64_t)tsb200_kv_record_bytes(kv.format, D);
   switch (kv.format) {
     case TSB200_KV_INT8:
-      kv_append_kernel<T, D, TSB200_KV_INT8><<<(unsigned)blocks, 256, 0, s>>>(kv, (T*)q, qs, qheads, (const T*)k, (const T*)v, ks, vs, B, Tn, new_lens, rc, rs, rr, rec);
+      TSB_CUDA(launch_kernel(kv_append_kernel<T, D, TSB200_KV_INT8>, dim3((unsigned)blocks), dim3(256), 0, s, kv, (T*)q, qs, qheads, (const T*)k, (const T*)v, ks, vs, B, Tn, new_lens, rc, rs, rr, rec));
       break;
     case TSB200_KV_FP8:
-      kv_append_kernel<T, D, TSB200_KV_FP8><<<(unsigned)blocks, 256, 0, s>>>(kv, (T*)q, qs, qheads, (const T*)k, (const T*)v, ks, vs, B, Tn, new_lens, rc, rs, rr, rec);
+      TSB_CUDA(launch_kernel(kv_append_kernel<T, D, TSB200_KV_FP8>, dim3((unsigned)blocks), dim3(256), 0, s, kv, (T*)q, qs, qheads, (const T*)k, (const T*)v, ks, vs, B, Tn, new_lens, rc, rs, rr, rec));
       break;
     case TSB200_KV_NVFP4:
-      kv_append_kernel<T, D, TSB200_KV_NVFP4><<<(unsigned)blocks, 256, 0, s>>>(kv, (T*)q, qs, qheads, (const T*)k, (const T*)v, ks, vs, B, Tn, new_lens, rc, rs, rr, rec);
+      TSB_CUDA(launch_kernel(kv_append_kernel<T, D, TSB200_KV_NVFP4>, dim3((unsigned)blocks), dim3(256), 0, s, kv, (T*)q, qs, qheads, (const T*)k, (const T*)v, ks, vs, B, Tn, new_lens, rc, rs, rr, rec));
       break;
     default:   // unquantized pages in the act dtype
-      kv_append_kernel<T, D, TSB200_KV_F32><<<(unsigned)blocks, 256, 0, s>>>(kv, (T*)q, qs, qheads, (const T*)k, (const T*)v, ks, vs, B, Tn, new_lens, rc, rs, rr, rec);
+      TSB_CUDA(launch_kernel(kv_append_kernel<T, D, TSB200_KV_F32>, dim3((unsigned)blocks), dim3(256), 0, s, kv, (T*)q, qs, qheads, (const T*)k, (const T*)v, ks, vs, B, Tn, new_lens, rc, rs, rr, rec));
   }
   TSB_LAUNCH_CHECK();
   return TSB200_OK;

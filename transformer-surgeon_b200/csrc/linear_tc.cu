@@ -144,6 +144,8 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
   __syncthreads();
   tc_fence_after();
   const unsigned tmem_base = *tmem_slot;
+  pdl_launch_dependents();
+  pdl_wait();     // activations (and the split-K buffer) belong to the preceding kernels
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer -----
@@ -258,8 +260,7 @@ int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, const TcParams& p, d
     TSB_CUDA(cudaFuncSetAttribute(linear_tc_kernel<TN, BITS>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kBytes));
     configured[dev] = true;
   }
-  linear_tc_kernel<TN, BITS><<<grid, kThreads, L::kBytes, s>>>(mw, mx, p);
-  TSB_LAUNCH_CHECK();
+  TSB_CUDA(launch_kernel(linear_tc_kernel<TN, BITS>, grid, dim3(kThreads), (size_t)L::kBytes, s, mw, mx, p));
   return TSB200_OK;
 }
 

@@ -151,6 +151,14 @@ __device__ __forceinline__ bool warps_rendezvous(unsigned long long* bar, int& u
   return ok;
 }
 
+// Optional phase trace (compile with -DTSB_TRACE): CTA 0 stores clock64 stamps in bytes 64.. of the
+// workspace header.
+#ifdef TSB_TRACE
+#define TSB_STAMP(i) do { if (blockIdx.x == 0) reinterpret_cast<long long*>(reinterpret_cast<char*>(p.status) + 64)[i] = clock64(); } while (0)
+#else
+#define TSB_STAMP(i) do { } while (0)
+#endif
+
 struct QParams {
   int64_t M, N, K;
   int kb_total, kb_per_split, splits;
@@ -185,6 +193,7 @@ linear_tcq_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
   volatile int* last_flag = abort_flag + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  pdl_launch_dependents();
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < NR; ++i) { mbar_init(&raw_full[i], 1); mbar_init(&raw_empty[i], 4 + 1); }
@@ -200,6 +209,7 @@ linear_tcq_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
   __syncthreads();
   tc_fence_after();
   const unsigned tmem_base = *tmem_slot;
+  if (threadIdx.x == 0) TSB_STAMP(0);
 
   // item -> (n tile, m tile, split); the same enumeration in every role
   auto decode = [&](int item, int& nt, int& mt, int& kb0, int& nkb) {
@@ -214,23 +224,38 @@ linear_tcq_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
   if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer
     if (lane == 0) {
-      int gs = 0;                                             // stage counter of this CTA (all items)
+      asm volatile("prefetch.tensormap [%0];\n" ::"l"(&map_w) : "memory");
+      asm volatile("prefetch.tensormap [%0];\n" ::"l"(&map_x) : "memory");
+      // Walk stages [g_begin, g_end) of this CTA's item list.  The packed weights are constants, so
+      // their boxes for the first NR stages are requested BEFORE waiting for the preceding kernel;
+      // the activation tiles of those stages follow after the wait.
       bool ok = true;
-      for (int item = blockIdx.x; item < p.items && ok; item += gridDim.x) {
-        int nt, mt, kb0, nkb;
-        decode(item, nt, mt, kb0, nkb);
-        for (int i = 0; i < nkb; i += KBS, ++gs) {
-          const int s = gs % NR;
-          if (gs >= NR && !mbar_wait(&raw_empty[s], ((gs / NR) - 1) & 1, abort_flag, 1)) { ok = false; break; }
-          uint8_t* st = r_ring + s * L::kStage;
-          mbar_expect_tx(&raw_full[s], TX_BYTES);
-          const int kcol = (kb0 + i) * BK;
+      auto walk = [&](int g_begin, int g_end, bool do_w, bool do_x, bool arm) {
+        int gs = 0;
+        for (int item = blockIdx.x; item < p.items && ok && gs < g_end; item += gridDim.x) {
+          int nt, mt, kb0, nkb;
+          decode(item, nt, mt, kb0, nkb);
+          for (int i = 0; i < nkb && gs < g_end; i += KBS, ++gs) {
+            if (gs < g_begin) continue;
+            const int s = gs % NR;
+            if (gs >= NR && !mbar_wait(&raw_empty[s], ((gs / NR) - 1) & 1, abort_flag, 1)) { ok = false; return; }
+            uint8_t* st = r_ring + s * L::kStage;
+            if (arm) mbar_expect_tx(&raw_full[s], TX_BYTES);
+            const int kcol = (kb0 + i) * BK;
+            if (do_x) {
 #pragma unroll
-          for (int j = 0; j < KBS; ++j)                       // columns beyond K are zero-filled by the copy engine
-            tma_load_2d(st + j * L::kXTile, &map_x, kcol + j * BK, mt * TN, &raw_full[s]);
-          tma_load_2d(st + L::kX, &map_w, kcol * BITS / 8, nt * BM, &raw_full[s]);
+              for (int j = 0; j < KBS; ++j)                   // columns beyond K are zero-filled by the copy engine
+                tma_load_2d(st + j * L::kXTile, &map_x, kcol + j * BK, mt * TN, &raw_full[s]);
+            }
+            if (do_w) tma_load_2d(st + L::kX, &map_w, kcol * BITS / 8, nt * BM, &raw_full[s]);
+            if (gs == 0 && do_w) TSB_STAMP(1);
+          }
         }
-      }
+      };
+      walk(0, NR, true, false, true);
+      pdl_wait();
+      walk(0, NR, false, true, false);
+      walk(NR, 0x7fffffff, true, true, true);
     }
   } else if (warp == 1) {
     // ---------------------------------------------------------------- MMA issuer
@@ -272,12 +297,17 @@ linear_tcq_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
     for (int item = blockIdx.x; item < p.items && ok; item += gridDim.x, ++it) {
       int nt, mt, kb0, nkb;
       decode(item, nt, mt, kb0, nkb);
+      // per-row epilogue constants (weights-side data): requested now, consumed after the main loop
+      const int64_t n = (int64_t)nt * BM + row;
+      const float sc = (p.scale && n < p.N) ? __ldg(&p.scale[n]) : 1.0f;
+      const float bv = (p.bias && n < p.N) ? __bfloat162float(p.bias[n]) : 0.f;
       for (int i = 0; i < nkb; i += KBS, ++gs) {
         if ((gs & 1) != grp) continue;
         const int s = gs % NR, buf = gs & 1;
         ok = mbar_wait(&raw_full[s], (gs / NR) & 1, abort_flag, 4);
         if (ok && gs >= 2) ok = mbar_wait(&a_empty[buf], ((gs >> 1) - 1) & 1, abort_flag, 5);
         if (!ok) break;
+        if (gs == 0 && threadIdx.x == 64) TSB_STAMP(2);
         tc_fence_after();
         const unsigned raw = smem_u32(r_ring + s * L::kStage + L::kX);
         const int nsub = min(KBS, nkb - i);
@@ -290,16 +320,16 @@ linear_tcq_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
         tc_fence_before();
         __syncwarp();
         if (lane == 0) { mbar_arrive(&a_ready[buf]); mbar_arrive(&raw_empty[s]); }
+        if (threadIdx.x == 64) { if (gs == 0) TSB_STAMP(3); TSB_STAMP(4); }
       }
       if (!ok) break;
       ok = mbar_wait(acc_full, it & 1, abort_flag, 6);
       if (!ok) break;
+      if (threadIdx.x == 64) TSB_STAMP(5);
       tc_fence_after();
-      const int64_t n = (int64_t)nt * BM + row;
+      if (it == 0) pdl_wait();                               // outputs / split-K scratch may still be in use upstream
       const int64_t m0 = (int64_t)mt * TN;
       const bool split = p.splits > 1;
-      const float sc = (p.scale && n < p.N) ? p.scale[n] : 1.0f;
-      const float bv = (p.bias && n < p.N) ? __bfloat162float(p.bias[n]) : 0.f;
       constexpr int CH = TN / 2;                             // token columns handled by this warp
       float* slice = p.partial + (size_t)item * (TN * BM);   // [TN][128] of this item
 #pragma unroll 1
@@ -334,20 +364,37 @@ linear_tcq_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
         if (last) {
           __threadfence();
           if (n < p.N) {
-            const float* tile0 = p.partial + (size_t)(item - item % p.splits) * (TN * BM);
-            for (int c = grp * CH; c < (grp + 1) * CH; ++c) {
-              const int64_t m = m0 + c;
-              if (m >= p.M) break;
-              const float* src = tile0 + c * BM + row;
-              float v = 0.f;
+            const float* tile0 = p.partial + (size_t)(item - item % p.splits) * (TN * BM) + row;
+            // 8 token columns at a time: the 8 loads of one split are independent (in flight together);
+            // splits are added in index order, so the result does not depend on arrival order
+            for (int c0 = grp * CH; c0 < (grp + 1) * CH; c0 += 8) {
+              float v[8];
+#pragma unroll
+              for (int j = 0; j < 8; ++j) v[j] = 0.f;
               int sp = 0;
-              for (; sp + 4 <= p.splits; sp += 4) {          // four loads in flight; fixed summation order
-                const float a0 = __ldcg(src + (size_t)(sp + 0) * (TN * BM)), a1 = __ldcg(src + (size_t)(sp + 1) * (TN * BM));
-                const float a2 = __ldcg(src + (size_t)(sp + 2) * (TN * BM)), a3 = __ldcg(src + (size_t)(sp + 3) * (TN * BM));
-                v = (((v + a0) + a1) + a2) + a3;
+              for (; sp + 4 <= p.splits; sp += 4) {          // 32 loads in flight
+                float a[4][8];
+#pragma unroll
+                for (int u = 0; u < 4; ++u)
+#pragma unroll
+                  for (int j = 0; j < 8; ++j) a[u][j] = __ldcg(tile0 + (size_t)(sp + u) * (TN * BM) + (c0 + j) * BM);
+#pragma unroll
+                for (int u = 0; u < 4; ++u)
+#pragma unroll
+                  for (int j = 0; j < 8; ++j) v[j] += a[u][j];
               }
-              for (; sp < p.splits; ++sp) v += __ldcg(src + (size_t)sp * (TN * BM));
-              p.y[m * p.N + n] = __float2bfloat16_rn(v * sc + bv);
+              for (; sp < p.splits; ++sp) {
+                float a[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) a[j] = __ldcg(tile0 + (size_t)sp * (TN * BM) + (c0 + j) * BM);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v[j] += a[j];
+              }
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                const int64_t m = m0 + c0 + j;
+                if (m < p.M) p.y[m * p.N + n] = __float2bfloat16_rn(v[j] * sc + bv);
+              }
             }
           }
           if (threadIdx.x == 64) p.counters[mt * p.n_tiles + nt] = 0;
@@ -355,6 +402,7 @@ linear_tcq_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
         if (!(ok = warps_rendezvous(ep_bar, ep_uses, lane, abort_flag))) break;   // last_flag is reused by the next item
       }
       tc_fence_after();
+      if (threadIdx.x == 64) TSB_STAMP(6);
     }
   }
   if (*abort_flag) {
@@ -366,6 +414,7 @@ linear_tcq_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
     tc_fence_after();
     tmem_dealloc(tmem_base, kTmemCols);
   }
+  if (threadIdx.x == 0) TSB_STAMP(7);
   if (threadIdx.x == 0 && *abort_flag) atomicMax(p.status, *abort_flag);
 }
 
@@ -386,8 +435,7 @@ int launch_q(const CUtensorMap& mw, const CUtensorMap& mx, const QParams& p, int
     TSB_CUDA(cudaFuncSetAttribute(linear_tcq_kernel<TN, BITS>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kBytes));
     configured[dev] = true;
   }
-  linear_tcq_kernel<TN, BITS><<<grid, kThreadsQ, L::kBytes, s>>>(mw, mx, p);
-  TSB_LAUNCH_CHECK();
+  TSB_CUDA(launch_kernel(linear_tcq_kernel<TN, BITS>, dim3(grid), dim3(kThreadsQ), (size_t)L::kBytes, s, mw, mx, p));
   return TSB200_OK;
 }
 

@@ -154,9 +154,18 @@ class CompressedDecoder:
         self.kernel_launches_per_step = n
         return self.logits
 
-    def capture(self):
+    def capture(self, pdl=True):
         """Capture one decode step in a CUDA graph (the per-token Python loop of Hugging Face's
-        `_sample` and ~15 launches per layer collapse into one graph launch)."""
+        `_sample` and ~15 launches per layer collapse into one graph launch).  With `pdl` the
+        kernels are captured with programmatic dependent launch edges: each kernel's prologue and
+        weight prefetch overlap the tail of its predecessor."""
+        old_pdl = ops.set_pdl(pdl)
+        try:
+            self._capture()
+        finally:
+            ops.set_pdl(old_pdl)
+
+    def _capture(self):
         s = torch.cuda.Stream()
         s.wait_stream(torch.cuda.current_stream())
         saved = self.seq_lens.clone()

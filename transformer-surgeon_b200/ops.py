@@ -14,6 +14,11 @@ KV_FORMATS = {"int8": KV_INT8, "fp8": KV_FP8, "nvfp4": KV_NVFP4, "fp32": KV_F32,
 PAGE = 16
 
 
+def set_pdl(enabled):
+    """Programmatic dependent launch for the decode-step kernels (process-wide); returns the old setting."""
+    return bool(_lib.load().tsb200_set_pdl(int(bool(enabled))))
+
+
 def _stream():
     return C.c_void_p(torch.cuda.current_stream().cuda_stream)
 
