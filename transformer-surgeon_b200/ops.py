@@ -171,12 +171,15 @@ class Factor:
 _workspaces = {}
 
 
-def workspace(device, nbytes):
-    """Grow-only scratch buffer per device (PyTorch owns the memory)."""
-    buf = _workspaces.get(device)
+def workspace(device, nbytes, kind="linear"):
+    """Grow-only scratch buffer per (device, kind) (PyTorch owns the memory).  Linear layers and
+    attention keep separate buffers: the head of a linear workspace holds a status word and
+    split-K counters that must stay zero between calls, attention overwrites its whole buffer."""
+    key = (device, kind)
+    buf = _workspaces.get(key)
     if buf is None or buf.numel() < nbytes:
-        buf = torch.zeros(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)   # status word starts at 0
-        _workspaces[device] = buf
+        buf = torch.zeros(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)   # status word / counters start at 0
+        _workspaces[key] = buf
     return buf
 
 
@@ -224,7 +227,7 @@ class PackedLinear:
     @staticmethod
     def device_status(ws=None, device=None):
         """Status word of a workspace (synchronises): 0, or the code of a bounded wait that ran out."""
-        ws = ws if ws is not None else _workspaces[device]
+        ws = ws if ws is not None else _workspaces[(device, "linear")]
         return int(ws[:4].view(torch.int32).item())
 
 
@@ -314,7 +317,7 @@ def paged_decode_attention(kv, q, max_seq_len, sm_scale=None, out=None, ws=None,
         out = torch.empty((B, H, d), dtype=q.dtype, device=q.device)
     nbytes = decode_attn_workspace_bytes(B, H, d, max_seq_len)
     if ws is None:
-        ws = workspace(q.device, nbytes)
+        ws = workspace(q.device, nbytes, "attention")
     if sm_scale is None:
         sm_scale = d ** -0.5
     fn = lib.tsb200_paged_decode_attn_simt if simt else lib.tsb200_paged_decode_attn
