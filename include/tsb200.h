@@ -222,6 +222,24 @@ int tsb200_paged_decode_attn_simt(const tsb200_kv_desc* kv, const void* q, void*
                                   int64_t q_batch_stride, int64_t B, int H, float sm_scale, int64_t max_seq_len,
                                   void* workspace, size_t workspace_bytes, void* stream);
 
+/* Allocation-free decode attention.  (No counterpart in the reference: the reference lets
+ * PyTorch allocate whatever it needs.)  Same contract and results as tsb200_paged_decode_attn,
+ * but the split partials are kept in a fixed array inside the library, so the call needs no
+ * workspace and performs no allocation of any kind.  It is meant for callers that cannot call
+ * cudaMalloc on their serving path (fixed-budget plugins, runtimes whose allocator must not be
+ * re-entered, code already inside a stream capture).
+ *   - capacity: tsb200_paged_decode_attn_static_capacity() bytes (8 MiB); a problem whose
+ *     tsb200_paged_decode_attn_workspace_bytes(...) exceeds it is refused with
+ *     TSB200_ERR_WORKSPACE.  Each GPU that loads the library holds the array until exit.
+ *   - the first call on a device resolves the array's device address (cudaGetSymbolAddress with
+ *     that device current); make that first call before any stream capture begins.
+ *   - all calls on a device share the array: two calls that may overlap on the GPU (different
+ *     streams) race; the array keeps the previous call's contents and nothing needs clearing. */
+size_t tsb200_paged_decode_attn_static_capacity(void);
+int tsb200_paged_decode_attn_static(const tsb200_kv_desc* kv, const void* q, void* out, int dtype,
+                                    int64_t q_batch_stride, int64_t B, int H, float sm_scale,
+                                    int64_t max_seq_len, void* stream);
+
 /* ------------------------------------------------------------------------------------
  * Small decoder ops
  * ---------------------------------------------------------------------------------- */

@@ -59,6 +59,8 @@ SIGNATURES = {
     "tsb200_paged_decode_attn_workspace_bytes": (_sz, [_i64, _i32, _i32, _i64]),
     "tsb200_paged_decode_attn": (_i32, [_KD, _vp, _vp, _i32, _i64, _i64, _i32, _f32, _i64, _vp, _sz, _vp]),
     "tsb200_paged_decode_attn_simt": (_i32, [_KD, _vp, _vp, _i32, _i64, _i64, _i32, _f32, _i64, _vp, _sz, _vp]),
+    "tsb200_paged_decode_attn_static_capacity": (_sz, []),
+    "tsb200_paged_decode_attn_static": (_i32, [_KD, _vp, _vp, _i32, _i64, _i64, _i32, _f32, _i64, _vp]),
     "tsb200_rope": (_i32, [_vp, _i32, _i64, _i64, _i64, _i32, _i32, _vp, _vp, _vp, _i64, _vp]),
     "tsb200_add_rmsnorm": (_i32, [_vp, _vp, _vp, _vp, _i32, _i64, _i64, _f32, _i32, _vp]),
     "tsb200_swiglu": (_i32, [_vp, _vp, _vp, _i32, _i64, _i64, _i64, _i64, _i64, _vp]),

@@ -307,3 +307,58 @@ extern "C" int tsb200_paged_decode_attn(const tsb200_kv_desc* kv, const void* q,
   }
 #undef TSB_GO
 }
+
+
+// ---------------------------------------------------------------------------------------------
+// Allocation-free variant.
+//
+// Some callers may not allocate device memory at all: code running inside a CUDA-graph capture or
+// under a framework that forbids cudaMalloc on its serving path, plugins handed a fixed memory
+// budget, and host runtimes whose allocator cannot be re-entered from the calling thread.  For them
+// the split partials live in the fixed array below instead of a caller-provided workspace.  Every
+// GPU that loads this library carries the array (kStaticScratchBytes) until the process exits.
+//
+// In host code `g_attn_scratch` is only a stand-in for the symbol, not a device address; the
+// address the kernels need is obtained once per device with cudaGetSymbolAddress while that device
+// is current, and that pointer is what is passed to the launches.
+namespace tsb {
+namespace {
+constexpr size_t kStaticScratchBytes = 8u << 20;     // 8 MiB: e.g. batch 64 x 32 heads x 8 splits x (2 + 128) floats
+static __device__ __align__(256) unsigned char g_attn_scratch[kStaticScratchBytes];
+
+int static_scratch_ptr(void** out) {
+  static void* ptrs[64] = {nullptr};                 // one resolved address per device ordinal
+  int dev = 0;
+  TSB_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return TSB200_ERR_DEVICE;
+  if (!ptrs[dev]) {
+    void* p = nullptr;
+    TSB_CUDA(cudaGetSymbolAddress(&p, g_attn_scratch));   // resolves the copy owned by the current device
+    if (!p) return TSB200_ERR_CUDA;
+    ptrs[dev] = p;
+  }
+  *out = ptrs[dev];
+  return TSB200_OK;
+}
+}  // namespace
+}  // namespace tsb
+
+extern "C" size_t tsb200_paged_decode_attn_static_capacity(void) { return tsb::kStaticScratchBytes; }
+
+extern "C" int tsb200_paged_decode_attn_static(const tsb200_kv_desc* kv, const void* q, void* out, int dtype,
+                                               int64_t q_batch_stride, int64_t B, int H, float sm_scale,
+                                               int64_t max_seq_len, void* stream) {
+  TSB_REQUIRE_DEVICE();
+  if (!kv || B < 0 || H <= 0) return TSB200_ERR_ARG;
+  if (B == 0) return TSB200_OK;
+  const size_t need = tsb200_paged_decode_attn_workspace_bytes(B, H, kv->head_dim, max_seq_len);
+  if (need == 0) return TSB200_ERR_ARG;
+  if (need > kStaticScratchBytes) return TSB200_ERR_WORKSPACE;   // problem too large for the built-in scratch
+  void* scratch = nullptr;
+  const int st = static_scratch_ptr(&scratch);
+  if (st != TSB200_OK) return st;
+  // Nothing in the scratch has to start at zero: every (sequence, head, split) record that the
+  // reducer reads is written by the split kernel of the same call.
+  return tsb200_paged_decode_attn(kv, q, out, dtype, q_batch_stride, B, H, sm_scale, max_seq_len, scratch, kStaticScratchBytes,
+                                  stream);
+}
