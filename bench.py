@@ -336,7 +336,7 @@ def run_ours(a):
                         "h2d_bytes_per_step": B * 8, "d2h_bytes_per_step": B * 8},
                 "gpu_launches": dec.kernel_launches_per_step * a.steps,
                 "clocks": clocks,
-                "roofline": {"kernel": "decode_attn_mma_kernel (+ split reducer)", "bound": "hbm", "achieved": achieved,
+                "roofline": {"kernel": "decode_attn_mma_kernel (split merge fused)", "bound": "hbm", "achieved": achieved,
                              "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_source": which,
                              "traffic": None, "ms_per_launch": t_attn,
                              "step_achieved": step_bytes / (ms / a.steps * 1e-3) / 1e9,

@@ -212,7 +212,9 @@ int tsb200_rope_append(const tsb200_kv_desc* kv, void* q, int q_heads, int64_t q
  * decode step, reading the quantized pages directly.
  * q, out [B, H, d] act dtype; attends over seq_lens[b] tokens (0 -> zeros).
  * max_seq_len bounds seq_lens (sizes the split grid; lengths above it are clamped).
- * q_batch_stride: elements between consecutive sequences of q (0 = H*d); out is dense. */
+ * q_batch_stride: elements between consecutive sequences of q (0 = H*d); out is dense.
+ * The first 16384 bytes of the workspace hold split counters: zero-fill them ONCE before the
+ * first use; every call leaves them zero.  One workspace must not serve overlapping calls. */
 size_t tsb200_paged_decode_attn_workspace_bytes(int64_t B, int H, int head_dim, int64_t max_seq_len);
 int tsb200_paged_decode_attn(const tsb200_kv_desc* kv, const void* q, void* out, int dtype,
                              int64_t q_batch_stride, int64_t B, int H, float sm_scale, int64_t max_seq_len,

@@ -41,7 +41,7 @@ def test_status_strings_and_sizes():
     assert lib.tsb200_kv_record_bytes(_lib.KV_FP8, 128) == 2048
     assert lib.tsb200_kv_record_bytes(_lib.KV_NVFP4, 128) == 1152
     assert lib.tsb200_kv_record_bytes(_lib.KV_NVFP4, 64) == 576
-    assert lib.tsb200_paged_decode_attn_workspace_bytes(64, 32, 128, 32768) == 64 * 32 * 64 * 130 * 4
+    assert lib.tsb200_paged_decode_attn_workspace_bytes(64, 32, 128, 32768) == 16384 + 64 * 32 * 64 * 130 * 4
 
 
 def test_record_sizes_match_oracle():

@@ -5,7 +5,10 @@
 
 namespace tsb {
 
-// Workspace: float [B][H][S][2 + d]  ->  m, l, acc[d] per (sequence, q head, split).
+// Workspace: kAttnCounterBytes of int32 counters (zero between calls; one per (sequence, kv head,
+// head chunk), used by the tensor-core kernel to let the last split merge the partials), then
+// float [B][H][S][2 + d]  ->  m, l, acc[d] per (sequence, q head, split).
+constexpr size_t kAttnCounterBytes = 16384;
 struct AttnSplit {
   int splits;
 };

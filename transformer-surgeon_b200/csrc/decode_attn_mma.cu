@@ -60,6 +60,18 @@ template <int FMT> __device__ __forceinline__ unsigned widen2(unsigned w16) {
     return *reinterpret_cast<unsigned*>(&h);
   }
 }
+// Two e4m3 codes (low 16 bits of w) -> f16x2 holding value * 2^-8, with integer instructions only:
+// sign to bit 15, exponent+mantissa shifted to f16 bits 13..7 (e4m3 exponent bias 7 vs f16 bias 15,
+// hence the 2^-8; e4m3 subnormals land on f16 subnormals, also exactly).  Used for the K operand so
+// that only half of the widening work sits on the conversion pipe; the caller folds 2^8 into its scale.
+__device__ __forceinline__ unsigned widen2_e4m3_alu(unsigned w16) {
+  const unsigned t = __byte_perm(w16, 0u, 0x1404);          // {b1, 0, b0, 0}: each code in the high byte of a half
+  return (t & 0x80008000u) | ((t >> 1) & 0x3f803f80u);
+}
+template <int FMT> __device__ __forceinline__ unsigned widen2_k(unsigned w16) {
+  return FMT == TSB200_KV_FP8 ? widen2_e4m3_alu(w16) : widen2<FMT>(w16);
+}
+
 // Row swizzle of the K record (rows of 128 bytes = 8 chunks): adjacent token rows land in
 // different halves of the bank space, rows two apart in different chunks.
 __device__ __forceinline__ int kswz(int row) { return ((row & 1) << 2) | ((row >> 1) & 3); }
@@ -71,7 +83,7 @@ template <int D> __device__ __forceinline__ int k_phys_chunk(int row, int j) {
 template <typename T, int D, int FMT>
 __global__ void __launch_bounds__(kWarps * 32)
 decode_attn_mma_kernel(tsb200_kv_desc kv, const T* __restrict__ q, int64_t qs, int H, float sm_scale, int64_t max_seq_len, int S,
-                       float* __restrict__ ws) {
+                       float* __restrict__ ws, int* __restrict__ counters, T* __restrict__ out) {
   constexpr int REC = (FMT == TSB200_KV_INT8) ? 16 * D + 64 : 16 * D;
   constexpr int CODE_CHUNKS = D;               // 16*D bytes / 16
   constexpr int REC_CHUNKS = REC / 16;
@@ -88,6 +100,8 @@ decode_attn_mma_kernel(tsb200_kv_desc kv, const T* __restrict__ q, int64_t qs, i
   const int g0 = blockIdx.z * 8, gn = min(8, g - g0);
   int len = kv.seq_lens[b];
   len = len < 0 ? 0 : (len > max_seq_len ? (int)max_seq_len : len);
+  const bool fuse_reduce = S > 0;      // S < 0: |S| splits, partials only (a reducer kernel follows)
+  S = S < 0 ? -S : S;
   int pb, pe;
   split_range(len, s, S, pb, pe);
 
@@ -107,7 +121,8 @@ decode_attn_mma_kernel(tsb200_kv_desc kv, const T* __restrict__ q, int64_t qs, i
   }
   float kscale = 1.f, vscale = 1.f;
   if (FMT == TSB200_KV_FP8) { kscale = kv.k_scale[b * kv.hkv + hk]; vscale = kv.v_scale[b * kv.hkv + hk]; }
-  const float sc = sm_scale * 1.4426950408889634f * kscale;
+  // FP8 keys are widened to value * 2^-8 (widen2_e4m3_alu): 256 restores the scale
+  const float sc = sm_scale * 1.4426950408889634f * kscale * (FMT == TSB200_KV_FP8 ? 256.0f : 1.0f);
 
   float oacc[NC][4];
 #pragma unroll
@@ -163,7 +178,7 @@ decode_attn_mma_kernel(tsb200_kv_desc kv, const T* __restrict__ q, int64_t qs, i
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         const int c = 4 * hh + i;
-        mma16816(sacc, widen2<FMT>(wa[i]), widen2<FMT>(wb[i]), widen2<FMT>(wa[i] >> 16), widen2<FMT>(wb[i] >> 16),
+        mma16816(sacc, widen2_k<FMT>(wa[i]), widen2_k<FMT>(wb[i]), widen2_k<FMT>(wa[i] >> 16), widen2_k<FMT>(wb[i] >> 16),
                  qf[c][0], qf[c][1]);
       }
     }
@@ -235,6 +250,7 @@ decode_attn_mma_kernel(tsb200_kv_desc kv, const T* __restrict__ q, int64_t qs, i
     a[(2 * tid + 1) * D + 16 * mt + gid + 8] = oacc[mt][3];
   }
   __syncthreads();
+  // merge the 4 warps; with one split the result is final, otherwise it is this split's partial
   for (int idx = threadIdx.x; idx < gn * D; idx += blockDim.x) {
     const int i = idx / D, e = idx % D;
     float mm = -INFINITY;
@@ -248,15 +264,47 @@ decode_attn_mma_kernel(tsb200_kv_desc kv, const T* __restrict__ q, int64_t qs, i
       ll += sm_l[ww * 8 + i] * c;
       a += sm_acc[((size_t)ww * 8 + i) * D + e] * c;
     }
-    float* o = ws + (((int64_t)b * H + hk * g + g0 + i) * S + s) * (2 + D);
-    if (e == 0) { o[0] = mm * 0.6931471805599453f; o[1] = ll; }   // natural-log domain for the reducer
-    o[2 + e] = a * vscale;
+    const int64_t bh = (int64_t)b * H + hk * g + g0 + i;
+    if (S == 1 && fuse_reduce) {
+      out[bh * D + e] = from_f32<T>(ll > 0.f ? a * vscale / ll : 0.f);
+    } else {
+      float* o = ws + (bh * S + s) * (2 + D);
+      if (e == 0) { o[0] = mm * 0.6931471805599453f; o[1] = ll; }   // natural-log domain (shared with the reducer kernel)
+      o[2 + e] = a * vscale;
+    }
   }
+  if (S == 1 || !fuse_reduce) return;
+  // The last CTA of this (sequence, kv head, head chunk) to finish merges the S partials in split
+  // order and resets the counter, so no separate reduction launch is needed.
+  __shared__ int s_last;
+  __threadfence();
+  __syncthreads();
+  int* ctr = counters + ((int64_t)blockIdx.x * gridDim.z + blockIdx.z);
+  if (threadIdx.x == 0) s_last = (atomicAdd(ctr, 1) == S - 1);
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  for (int idx = threadIdx.x; idx < gn * D; idx += blockDim.x) {
+    const int i = idx / D, e = idx % D;
+    const int64_t bh = (int64_t)b * H + hk * g + g0 + i;
+    const float* pr = ws + bh * S * (2 + D);
+    float mm = -INFINITY;
+    for (int sp = 0; sp < S; ++sp) mm = fmaxf(mm, __ldcg(pr + sp * (2 + D)));
+    float ll = 0.f, a = 0.f;
+    for (int sp = 0; sp < S; ++sp) {
+      const float ms = __ldcg(pr + sp * (2 + D));
+      const float c = ms == -INFINITY ? 0.f : __expf(ms - mm);
+      ll += __ldcg(pr + sp * (2 + D) + 1) * c;
+      a += __ldcg(pr + sp * (2 + D) + 2 + e) * c;
+    }
+    out[bh * D + e] = from_f32<T>(ll > 0.f ? a / ll : 0.f);
+  }
+  if (threadIdx.x == 0) *ctr = 0;
 }
 
 template <typename T, int D, int FMT>
 int launch_mma(const tsb200_kv_desc& kv, const void* q, int64_t qs, int H, float sm_scale, int64_t max_seq_len, int S, int64_t B,
-               float* ws, cudaStream_t st) {
+               float* ws, int* counters, void* out, cudaStream_t st) {
   constexpr int REC = (FMT == TSB200_KV_INT8) ? 16 * D + 64 : 16 * D;
   constexpr size_t pipe = (size_t)kWarps * kStages * 2 * REC;
   constexpr size_t merge = (size_t)(kWarps * 16 + kWarps * 8 * D) * sizeof(float);
@@ -272,7 +320,7 @@ int launch_mma(const tsb200_kv_desc& kv, const void* q, int64_t qs, int H, float
   const int g = H / kv.hkv;
   dim3 grid((unsigned)(B * kv.hkv), (unsigned)S, (unsigned)((g + 7) / 8));
   TSB_CUDA(launch_kernel(decode_attn_mma_kernel<T, D, FMT>, grid, dim3(kWarps * 32), smem, st, kv, (const T*)q, qs, H, sm_scale,
-                         max_seq_len, S, ws));
+                         max_seq_len, S, ws, counters, (T*)out));
   return TSB200_OK;
 }
 
@@ -294,10 +342,17 @@ extern "C" int tsb200_paged_decode_attn(const tsb200_kv_desc* kv, const void* q,
     return tsb200_paged_decode_attn_simt(kv, q, out, dtype, q_batch_stride, B, H, sm_scale, max_seq_len, workspace, workspace_bytes, stream);
   cudaStream_t s = as_stream(stream);
   const int S = choose_splits(B, kv->hkv, max_seq_len);
-  float* ws = (float*)workspace;
+  int* counters = (int*)workspace;                               // zero between calls
+  float* ws = (float*)((char*)workspace + kAttnCounterBytes);
   const int D = kv->head_dim;
+  const int64_t n_ctr = B * kv->hkv * ((H / kv->hkv + 7) / 8);
+  const bool fused = n_ctr * (int64_t)sizeof(int) <= (int64_t)kAttnCounterBytes;   // else: separate reduction launch
   int r;
-#define TSB_GO(TT, DD, FF) r = launch_mma<TT, DD, FF>(*kv, q, qs, H, sm_scale, max_seq_len, S, B, ws, s); if (r != TSB200_OK) return r; return launch_reduce<TT, DD>(ws, B * H, S, out, s)
+#define TSB_GO(TT, DD, FF)                                                                                              \
+  if (fused) return launch_mma<TT, DD, FF>(*kv, q, qs, H, sm_scale, max_seq_len, S, B, ws, counters, out, s);        \
+  r = launch_mma<TT, DD, FF>(*kv, q, qs, H, sm_scale, max_seq_len, -S, B, ws, counters, out, s);                      \
+  if (r != TSB200_OK) return r;                                                                                         \
+  return launch_reduce<TT, DD>(ws, B * H, S, out, s)
   if (dtype == TSB200_F32) {
     if (D == 64) { if (kv->format == TSB200_KV_INT8) { TSB_GO(float, 64, TSB200_KV_INT8); } else { TSB_GO(float, 64, TSB200_KV_FP8); } }
     else { if (kv->format == TSB200_KV_INT8) { TSB_GO(float, 128, TSB200_KV_INT8); } else { TSB_GO(float, 128, TSB200_KV_FP8); } }

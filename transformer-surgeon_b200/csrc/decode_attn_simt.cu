@@ -148,7 +148,7 @@ size_t tsb200_paged_decode_attn_workspace_bytes(int64_t B, int H, int head_dim, 
   int64_t pages = (max_seq_len + 15) / 16;
   int64_t smax = pages / 4 > 0 ? pages / 4 : 1;
   if (smax > 64) smax = 64;
-  return (size_t)(B * H * smax * (2 + head_dim)) * sizeof(float);
+  return kAttnCounterBytes + (size_t)(B * H * smax * (2 + head_dim)) * sizeof(float);
 }
 
 int tsb200_paged_decode_attn_simt(const tsb200_kv_desc* kv, const void* q, void* out, int dtype, int64_t q_batch_stride, int64_t B, int H,
@@ -165,7 +165,7 @@ int tsb200_paged_decode_attn_simt(const tsb200_kv_desc* kv, const void* q, void*
   const int g = H / kv->hkv;
   const int64_t rec = (int64_t)tsb200_kv_record_bytes(kv->format, kv->head_dim);
   dim3 grid((unsigned)(B * kv->hkv), (unsigned)S, (unsigned)((g + 7) / 8));
-  float* ws = (float*)workspace;
+  float* ws = (float*)((char*)workspace + kAttnCounterBytes);
 #define TSB_GO(TT, DD)                                                                                       \
   decode_attn_simt_kernel<TT, DD><<<grid, 128, 0, s>>>(*kv, (const TT*)q, qs, H, sm_scale, max_seq_len, S, rec, ws); \
   TSB_LAUNCH_CHECK();                                                                                        \
