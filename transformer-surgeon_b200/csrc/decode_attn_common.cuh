@@ -2,6 +2,7 @@
 // (m, l, acc) workspace layout and the cross-split reduction.
 #pragma once
 #include "common.cuh"
+#include <cstdlib>
 
 namespace tsb {
 
@@ -14,6 +15,9 @@ struct AttnSplit {
 };
 
 inline int choose_splits(int64_t B, int hkv, int64_t max_seq_len) {
+#ifdef TSB_TUNE
+  if (const char* e = getenv("TSB_ATTN_SPLITS")) return atoi(e);
+#endif
   const int64_t base = B * hkv;
   const int64_t pages = (max_seq_len + 15) / 16;
   int64_t s = (148 * 8 + base - 1) / (base > 0 ? base : 1);

@@ -16,6 +16,9 @@
 namespace tsb {
 
 template <typename T, int D> int launch_reduce(const float* ws, int64_t BH, int S, void* out, cudaStream_t st);
+template <typename T>
+int launch_attn_fp8(const tsb200_kv_desc& kv, const void* q, int64_t qs, int H, float sm_scale, int64_t max_seq_len, int S,
+                    int64_t B, float* ws, int* counters, void* out, cudaStream_t st);
 int validate_attn_args(const tsb200_kv_desc* kv, const void* q, void* out, int dtype, int64_t B, int H,
                        int64_t max_seq_len, void* workspace, size_t workspace_bytes, bool& noop);
 
@@ -68,8 +71,11 @@ __device__ __forceinline__ unsigned widen2_e4m3_alu(unsigned w16) {
   const unsigned t = __byte_perm(w16, 0u, 0x1404);          // {b1, 0, b0, 0}: each code in the high byte of a half
   return (t & 0x80008000u) | ((t >> 1) & 0x3f803f80u);
 }
+#ifndef TSB_ATTN_ALU_WIDEN
+#define TSB_ATTN_ALU_WIDEN 1
+#endif
 template <int FMT> __device__ __forceinline__ unsigned widen2_k(unsigned w16) {
-  return FMT == TSB200_KV_FP8 ? widen2_e4m3_alu(w16) : widen2<FMT>(w16);
+  return (FMT == TSB200_KV_FP8 && TSB_ATTN_ALU_WIDEN) ? widen2_e4m3_alu(w16) : widen2<FMT>(w16);
 }
 
 // Row swizzle of the K record (rows of 128 bytes = 8 chunks): adjacent token rows land in
@@ -122,7 +128,7 @@ decode_attn_mma_kernel(tsb200_kv_desc kv, const T* __restrict__ q, int64_t qs, i
   float kscale = 1.f, vscale = 1.f;
   if (FMT == TSB200_KV_FP8) { kscale = kv.k_scale[b * kv.hkv + hk]; vscale = kv.v_scale[b * kv.hkv + hk]; }
   // FP8 keys are widened to value * 2^-8 (widen2_e4m3_alu): 256 restores the scale
-  const float sc = sm_scale * 1.4426950408889634f * kscale * (FMT == TSB200_KV_FP8 ? 256.0f : 1.0f);
+  const float sc = sm_scale * 1.4426950408889634f * kscale * ((FMT == TSB200_KV_FP8 && TSB_ATTN_ALU_WIDEN) ? 256.0f : 1.0f);
 
   float oacc[NC][4];
 #pragma unroll
@@ -348,6 +354,14 @@ extern "C" int tsb200_paged_decode_attn(const tsb200_kv_desc* kv, const void* q,
   const int64_t n_ctr = B * kv->hkv * ((H / kv->hkv + 7) / 8);
   const bool fused = n_ctr * (int64_t)sizeof(int) <= (int64_t)kAttnCounterBytes;   // else: separate reduction launch
   int r;
+  if (kv->format == TSB200_KV_FP8 && D == 128 && H / kv->hkv <= 4) {
+    // e4m3 pages go to the tensor cores as FP8 (decode_attn_fp8.cu)
+    int* ctr = fused ? counters : nullptr;
+    if (dtype == TSB200_F32) r = launch_attn_fp8<float>(*kv, q, qs, H, sm_scale, max_seq_len, S, B, ws, ctr, out, s);
+    else r = launch_attn_fp8<__nv_bfloat16>(*kv, q, qs, H, sm_scale, max_seq_len, S, B, ws, ctr, out, s);
+    if (r != TSB200_OK || fused) return r;
+    return dtype == TSB200_F32 ? launch_reduce<float, 128>(ws, B * H, S, out, s) : launch_reduce<__nv_bfloat16, 128>(ws, B * H, S, out, s);
+  }
 #define TSB_GO(TT, DD, FF)                                                                                              \
   if (fused) return launch_mma<TT, DD, FF>(*kv, q, qs, H, sm_scale, max_seq_len, S, B, ws, counters, out, s);        \
   r = launch_mma<TT, DD, FF>(*kv, q, qs, H, sm_scale, max_seq_len, -S, B, ws, counters, out, s);                      \
