@@ -28,6 +28,23 @@ inline int choose_splits(int64_t B, int hkv, int64_t max_seq_len) {
   return (int)s;
 }
 
+// Split count of the fp8-MMA kernel: its per-CTA set-up (query expansion) is amortised over at
+// least 128 pages per split; more splits only when the (sequence, kv head) grid underfills the SMs.
+inline int choose_splits_fp8(int64_t B, int hkv, int64_t max_seq_len) {
+#ifdef TSB_TUNE
+  if (const char* e = getenv("TSB_ATTN_SPLITS")) return atoi(e);
+#endif
+  const int64_t base = B * hkv;
+  const int64_t pages = (max_seq_len + 15) / 16;
+  int64_t s = (148 * 2 + base - 1) / (base > 0 ? base : 1);
+  if (base >= 148) s = 1;
+  const int64_t cap = pages / 128 > 0 ? pages / 128 : 1;
+  if (s > cap) s = cap;
+  if (s < 1) s = 1;
+  if (s > 64) s = 64;
+  return (int)s;
+}
+
 // Pages [begin, end) of sequence with `len` tokens handled by split s of S.
 __device__ __forceinline__ void split_range(int len, int s, int S, int& begin, int& end) {
   const int pages = (len + 15) >> 4;

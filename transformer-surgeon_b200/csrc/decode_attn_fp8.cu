@@ -10,7 +10,7 @@
 //   S^T[token, col] = K_page[16 x 128] . Qexp^T          4 k-steps x 2 n-tiles per page
 //   O^T[dim, col]  += V^T_pagepair[128 x 32] . Pexp^T    8 m-tiles x 2 n-tiles per PAIR of pages
 // The three column sums are added in fp32 afterwards.  One CTA = (sequence, kv head, split); its 4
-// warps take page pairs round-robin; each warp streams its pairs through a private 3-stage ring
+// warps take page pairs round-robin; each warp streams its pairs through a private 2-stage ring
 // filled by cp.async.bulk (one lane, four 2 KB copies per stage) completing on an mbarrier.
 // Every mbarrier wait is bounded; on expiry the warp stops consuming pages and records a status.
 #include "tc_common.cuh"
@@ -29,7 +29,7 @@ using tc::mbar_try_wait;
 using tc::smem_u32;
 
 constexpr int kWarps = 4;
-constexpr int kStages = 3;
+constexpr int kStages = 2;
 constexpr int D = 128;
 constexpr int REC = 16 * D;                 // bytes of one K or V record
 constexpr int STAGE = 4 * REC;              // K_A, V_A, K_B, V_B
@@ -88,41 +88,42 @@ decode_attn_fp8_kernel(tsb200_kv_desc kv, const T* __restrict__ q, int64_t qs, i
   // column n of n-tile nt: head 2*nt + (n >> 2), term n & 3 (hi, mid, lo, zero); this lane supplies
   // column n = gid.  k-slots of QK step c (c = 0..3): lane `tid` covers dims 16*(tid + 4*(c>>1)) +
   // 8*(c&1) + [0, 8): b0 = the first four, b1 = the last four.
+  // The expansion is computed once per CTA (warp h handles head h: 32 lanes x 4 dims) into shared
+  // memory as words hi | mid << 8 | lo << 16, then every lane gathers the bytes of its own column.
   unsigned qf[2][4][2];
   float qamax[2];                                            // of the heads this lane tracks: 2*nt + (tid >> 1)
   {
-    float am[4];
+    unsigned* qexp = reinterpret_cast<unsigned*>(smem + (size_t)kWarps * WARP_SMEM);   // [4 heads][128 dims]
+    float* qam = reinterpret_cast<float*>(qexp + 4 * D);                               // [4]
+    {
+      float v[4] = {0.f, 0.f, 0.f, 0.f};
+      if (w < g) {
+        const T* qp = q + (int64_t)b * qs + (int64_t)(hk * g + w) * D + lane * 4;
 #pragma unroll
-    for (int h = 0; h < 4; ++h) {
-      float m = 0.f;
-      if (h < g) {
-        const T* qp = q + (int64_t)b * qs + (int64_t)(hk * g + h) * D + lane * 4;
-#pragma unroll
-        for (int i = 0; i < 4; ++i) m = fmaxf(m, fabsf(to_f32<T>(qp[i])));
+        for (int i = 0; i < 4; ++i) v[i] = to_f32<T>(qp[i]);
       }
-      am[h] = warp_max(m);
+      const float a = warp_max(fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3]))));
+      const float qsc = a > 0.f ? 256.0f / a : 0.f;
+      uint4 e;
+      e.x = split3(v[0] * qsc); e.y = split3(v[1] * qsc); e.z = split3(v[2] * qsc); e.w = split3(v[3] * qsc);
+      *reinterpret_cast<uint4*>(&qexp[w * D + lane * 4]) = e;
+      if (lane == 0) qam[w] = a;
     }
+    __syncthreads();
+    const unsigned part = gid & 3;
+    const unsigned sel = part | ((4u + part) << 4);          // byte `part` of two words -> bytes 0, 1
 #pragma unroll
     for (int nt = 0; nt < 2; ++nt) {
-      const int hq = 2 * nt + (gid >> 2), part = gid & 3;
-      const float a = hq == 0 ? am[0] : (hq == 1 ? am[1] : (hq == 2 ? am[2] : am[3]));
-      const float qsc = a > 0.f ? 256.0f / a : 0.f;
-      const bool valid = hq < g;
-      const T* qp = q + (int64_t)b * qs + (int64_t)(hk * g + (valid ? hq : 0)) * D;
+      const int hq = 2 * nt + (gid >> 2);
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         const int base = 16 * (tid + 4 * (c >> 1)) + 8 * (c & 1);
-        unsigned r[2] = {0u, 0u};
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const unsigned wd = valid ? split3(to_f32<T>(qp[base + i]) * qsc) : 0u;
-          r[i >> 2] |= ((wd >> (8 * part)) & 0xffu) << (8 * (i & 3));
-        }
-        qf[nt][c][0] = r[0];
-        qf[nt][c][1] = r[1];
+        const uint4 w0 = *reinterpret_cast<const uint4*>(&qexp[hq * D + base]);
+        const uint4 w1 = *reinterpret_cast<const uint4*>(&qexp[hq * D + base + 4]);
+        qf[nt][c][0] = __byte_perm(__byte_perm(w0.x, w0.y, sel), __byte_perm(w0.z, w0.w, sel), 0x5410);
+        qf[nt][c][1] = __byte_perm(__byte_perm(w1.x, w1.y, sel), __byte_perm(w1.z, w1.w, sel), 0x5410);
       }
-      const int ht = 2 * nt + (tid >> 1);
-      qamax[nt] = ht == 0 ? am[0] : (ht == 1 ? am[1] : (ht == 2 ? am[2] : am[3]));
+      qamax[nt] = qam[2 * nt + (tid >> 1)];
     }
   }
   const float kscale = kv.k_scale[b * kv.hkv + hk], vscale = kv.v_scale[b * kv.hkv + hk];
@@ -377,7 +378,7 @@ decode_attn_fp8_kernel(tsb200_kv_desc kv, const T* __restrict__ q, int64_t qs, i
 template <typename T>
 int launch_attn_fp8(const tsb200_kv_desc& kv, const void* q, int64_t qs, int H, float sm_scale, int64_t max_seq_len, int S,
                     int64_t B, float* ws, int* counters, void* out, cudaStream_t st) {
-  constexpr size_t pipe = (size_t)kWarps * WARP_SMEM;
+  constexpr size_t pipe = (size_t)kWarps * WARP_SMEM + 4 * D * 4 + 64;   // rings + expanded q
   constexpr size_t merge = (size_t)(kWarps * 16 + kWarps * 8 * D) * sizeof(float);
   constexpr size_t smem = pipe > merge ? pipe : merge;
   static bool configured[64] = {false};

@@ -357,10 +357,11 @@ extern "C" int tsb200_paged_decode_attn(const tsb200_kv_desc* kv, const void* q,
   if (kv->format == TSB200_KV_FP8 && D == 128 && H / kv->hkv <= 4) {
     // e4m3 pages go to the tensor cores as FP8 (decode_attn_fp8.cu)
     int* ctr = fused ? counters : nullptr;
-    if (dtype == TSB200_F32) r = launch_attn_fp8<float>(*kv, q, qs, H, sm_scale, max_seq_len, S, B, ws, ctr, out, s);
-    else r = launch_attn_fp8<__nv_bfloat16>(*kv, q, qs, H, sm_scale, max_seq_len, S, B, ws, ctr, out, s);
+    const int S8 = choose_splits_fp8(B, kv->hkv, max_seq_len);   // never more than choose_splits(): the workspace fits
+    if (dtype == TSB200_F32) r = launch_attn_fp8<float>(*kv, q, qs, H, sm_scale, max_seq_len, S8, B, ws, ctr, out, s);
+    else r = launch_attn_fp8<__nv_bfloat16>(*kv, q, qs, H, sm_scale, max_seq_len, S8, B, ws, ctr, out, s);
     if (r != TSB200_OK || fused) return r;
-    return dtype == TSB200_F32 ? launch_reduce<float, 128>(ws, B * H, S, out, s) : launch_reduce<__nv_bfloat16, 128>(ws, B * H, S, out, s);
+    return dtype == TSB200_F32 ? launch_reduce<float, 128>(ws, B * H, S8, out, s) : launch_reduce<__nv_bfloat16, 128>(ws, B * H, S8, out, s);
   }
 #define TSB_GO(TT, DD, FF)                                                                                              \
   if (fused) return launch_mma<TT, DD, FF>(*kv, q, qs, H, sm_scale, max_seq_len, S, B, ws, counters, out, s);        \
