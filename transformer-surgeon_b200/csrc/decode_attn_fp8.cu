@@ -58,6 +58,21 @@ __device__ __forceinline__ unsigned split3(float x) {
   const unsigned lo = to_e4m3(r);
   return hi | (mid << 8) | (lo << 16);
 }
+// fp32 value rounded to 4 significant bits (what an e4m3 code holds in its normal range), with
+// integer instructions: add half an ulp of the 3-bit mantissa, clear the 20 low mantissa bits.
+__device__ __forceinline__ float round_4bits(float x) { return __uint_as_float((__float_as_uint(x) + 0x00080000u) & 0xfff00000u); }
+// Two values at once: the codes come from the packed conversion (one instruction per term for both
+// values), the residuals from round_4bits on the FMA/ALU pipes.  Below 2^-6 the code is a subnormal
+// and the residual is off by < 2^-10: far below the last term's resolution.
+__device__ __forceinline__ void split3x2(float x0, float x1, unsigned& w0, unsigned& w1) {
+  const unsigned hi = (unsigned)__nv_cvt_float2_to_fp8x2(make_float2(x0, x1), __NV_SATFINITE, __NV_E4M3);
+  const float r0 = x0 - round_4bits(x0), r1 = x1 - round_4bits(x1);
+  const unsigned mid = (unsigned)__nv_cvt_float2_to_fp8x2(make_float2(r0, r1), __NV_SATFINITE, __NV_E4M3);
+  const float s0 = r0 - round_4bits(r0), s1 = r1 - round_4bits(r1);
+  const unsigned lo = (unsigned)__nv_cvt_float2_to_fp8x2(make_float2(s0, s1), __NV_SATFINITE, __NV_E4M3);
+  w0 = (hi & 0xffu) | ((mid & 0xffu) << 8) | ((lo & 0xffu) << 16);
+  w1 = ((hi >> 8) & 0xffu) | (mid & 0xff00u) | ((lo & 0xff00u) << 8);
+}
 
 template <typename T>
 __global__ void __launch_bounds__(kWarps * 32)
@@ -236,8 +251,10 @@ decode_attn_fp8_kernel(tsb200_kv_desc kv, const T* __restrict__ q, int64_t qs, i
       const float p0 = exp2f(sv[X][nt][0] - m_run[nt]), p1 = exp2f(sv[X][nt][1] - m_run[nt]);
       psum[nt] = p0 + p1;
       const int head = 2 * nt + (tid >> 1);
-      pbuf[(X * 4 + head) * 16 + gid] = split3(p0 * 256.0f);
-      pbuf[(X * 4 + head) * 16 + gid + 8] = split3(p1 * 256.0f);
+      unsigned w0, w1;
+      split3x2(p0 * 256.0f, p1 * 256.0f, w0, w1);
+      pbuf[(X * 4 + head) * 16 + gid] = w0;
+      pbuf[(X * 4 + head) * 16 + gid + 8] = w1;
       l_run[nt] = l_run[nt] * corr[nt] + psum[nt];
     }
     __syncwarp();
