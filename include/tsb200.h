@@ -138,6 +138,18 @@ int tsb200_linear(const tsb200_linear_desc* d, const void* x, void* y, int64_t M
 int tsb200_linear_simt(const tsb200_linear_desc* d, const void* x, void* y, int64_t M,
                        void* workspace, size_t workspace_bytes, void* stream);
 
+/* Gated MLP block: y = down(silu(gate(x)) * up(x)).
+ * Replaces: blocks/mlp.py:171-185 (MLPGated.forward: up_proj, gate_proj, activation * up, down_proj)
+ * with SiLU as the activation (the Qwen2 / Llama choice).  gate and up map in -> inter, down maps
+ * inter -> out; x [M, in] -> y [M, out].  When the layers are packed alike the whole block is one
+ * launch; otherwise it is composed from tsb200_linear and tsb200_swiglu.  The workspace must be
+ * zero-filled once before its first use and must not serve overlapping calls. */
+size_t tsb200_mlp_gated_workspace_bytes(const tsb200_linear_desc* gate, const tsb200_linear_desc* up,
+                                        const tsb200_linear_desc* down, int64_t M);
+int tsb200_mlp_gated(const tsb200_linear_desc* gate, const tsb200_linear_desc* up,
+                     const tsb200_linear_desc* down, const void* x, void* y, int64_t M,
+                     void* workspace, size_t workspace_bytes, void* stream);
+
 /* ------------------------------------------------------------------------------------
  * Quantized paged KV cache
  * The reference's cache is a dense fixed-size row store written at clamp(pos_id)

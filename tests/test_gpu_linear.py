@@ -110,3 +110,50 @@ def test_linearity_and_leading_shape(cuda):
     y2 = lin((2.0 * xa).reshape(2, 3, 512)).reshape(6, 128)
     torch.testing.assert_close(2.0 * y1, y2, rtol=1e-5, atol=1e-5)
     assert lin(xa[:0]).shape == (0, 128)
+
+
+@pytest.mark.parametrize("name", ["bf16", "fp32"])
+@pytest.mark.parametrize("p", [8, 4, None])
+@pytest.mark.parametrize("M,K,I,r,N", [(32, 512, 7168, 256, 512), (12, 512, 7168, 0, 384), (32, 256, 640, 64, 256), (5, 256, 640, 64, 256)])
+def test_gated_mlp_block(cuda, name, p, M, K, I, r, N):
+    """MLPGated.forward (blocks/mlp.py:171-185): fused one-launch path (wide intermediate, bf16, 9<=M<=64)
+    and the composed path, against the oracle's silu(gate)*up -> down in fp32 from the dequantized factors."""
+    from transformer_surgeon_b200 import ops
+    from oracle import attention as oatt
+    dt = DT[name]
+    g = torch.Generator().manual_seed(7)
+    x = torch.randn(M, K, generator=g).to(dt)
+
+    def layer(out, inn, rank, bias):
+        U = (torch.randn(out, rank or inn, generator=g) * (0.5 / (rank or inn) ** 0.5)).to(dt)
+        V = (torch.randn(rank, inn, generator=g) * (1.0 / inn ** 0.5)).to(dt) if rank else None
+        b = (torch.randn(out, generator=g) * 0.1).to(dt) if bias else None
+        if p is None:
+            fu, fv = ops.Factor.dense(U.to(cuda)), (ops.Factor.dense(V.to(cuda)) if rank else None)
+        else:
+            fu, fv = ops.Factor.quantize(U.to(cuda), p), (ops.Factor.quantize(V.to(cuda), p) if rank else None)
+        lin = ops.PackedLinear(fu, fv, None if b is None else b.to(cuda), dt)
+        Ud = fu.reconstruct(dt).float().cpu()
+        Vd = fv.reconstruct(dt).float().cpu() if rank else None
+        return lin, (Ud, Vd, None if b is None else b.float())
+
+    gate, gw = layer(I, K, r, True)
+    up, uw = layer(I, K, r, False)
+    down, dw = layer(N, I, r, True)
+
+    def ref_lin(t, w):
+        U, V, b = w
+        h = t @ V.T if V is not None else t
+        y = h @ U.T
+        return y + b if b is not None else y
+
+    ref = ref_lin(oatt.swiglu(ref_lin(x.float(), gw), ref_lin(x.float(), uw)), dw)
+    mlp = ops.GatedMLP(gate, up, down)
+    y = mlp(x.to(cuda))
+    y2 = mlp(x.to(cuda))
+    assert torch.equal(y, y2)                                   # deterministic split-K, clean workspace
+    assert rel_err(y.cpu(), ref) < (2e-2 if name == "bf16" else 1e-4), rel_err(y.cpu(), ref)
+    # identical to composing the public pieces
+    yc = down(ops.swiglu(gate(x.to(cuda)), up(x.to(cuda))))
+    assert rel_err(y, yc) < (1e-2 if name == "bf16" else 1e-5)
+    assert ops.PackedLinear.device_status(ws=ops.workspace(cuda, 1, "mlp")) == 0

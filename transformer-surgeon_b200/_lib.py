@@ -52,6 +52,8 @@ SIGNATURES = {
     "tsb200_linear_workspace_bytes": (_sz, [_LD, _i64]),
     "tsb200_linear": (_i32, [_LD, _vp, _vp, _i64, _vp, _sz, _vp]),
     "tsb200_linear_simt": (_i32, [_LD, _vp, _vp, _i64, _vp, _sz, _vp]),
+    "tsb200_mlp_gated_workspace_bytes": (_sz, [_LD, _LD, _LD, _i64]),
+    "tsb200_mlp_gated": (_i32, [_LD, _LD, _LD, _vp, _vp, _i64, _vp, _sz, _vp]),
     "tsb200_kv_record_bytes": (_sz, [_i32, _i32]),
     "tsb200_kv_fp8_scales": (_i32, [_vp, _vp, _i32, _i64, _i64, _i32, _i32, _vp, _vp, _vp, _i64, _vp, _vp, _vp]),
     "tsb200_kv_append": (_i32, [_KD, _vp, _vp, _i32, _i64, _i64, _i64, _i64, _vp, _vp, _vp, _i64, _vp]),

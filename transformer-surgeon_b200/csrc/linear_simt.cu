@@ -193,8 +193,7 @@ size_t tsb200_linear_workspace_bytes(const tsb200_linear_desc* d, int64_t M) {
   const int64_t ku = d->rank > 0 ? d->rank : d->in_features;
   const size_t s_u = tc::plan_gemm(M, d->out_features, ku).slice_bytes;
   const size_t s_v = d->rank > 0 ? tc::plan_gemm(M, d->rank, d->in_features).slice_bytes : 0;
-  if (s_u > scratch) scratch = s_u;
-  if (s_v > scratch) scratch = s_v;
+  if (s_u + s_v > scratch) scratch = s_u + s_v;     // the fused V -> U launch keeps both phases' slices apart
   return kWsHeaderBytes + h + (scratch + 255) / 256 * 256;
 }
 

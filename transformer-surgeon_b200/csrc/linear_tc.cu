@@ -353,6 +353,16 @@ int linear_tc(const tsb200_linear_desc* d, const void* x, void* y, int64_t M, vo
     return bits == 16 ? gemm_tc(W, bits, scale, bias, in, out, M, K, N, partial, status, s)
                       : gemm_tcq(W, bits, scale, bias, in, out, M, K, N, partial, counters, status, s);
   };
+  if (d->rank > 0 && d->u_bits == d->v_bits && d->u_bits <= 8) {
+    // both factors packed alike: V then U as two phases of ONE launch (grid barrier in between);
+    // the rank-r intermediate is produced and consumed through L2
+    PhaseSpec ps[2];
+    ps[0].nsub = 1; ps[0].gated = 0;
+    ps[0].g[0] = GemmSpec{d->v, d->v_scale, nullptr, x, h, d->rank, d->in_features};
+    ps[1].nsub = 1; ps[1].gated = 0;
+    ps[1].g[0] = GemmSpec{d->u, d->u_scale, d->bias, h, y, d->out_features, d->rank};
+    return run_program_tcq(ps, 2, d->u_bits, M, (uint8_t*)partial, counters, (int*)(ws + kWsGridBar), status, s);
+  }
   const void* in = x;
   if (d->rank > 0) {
     int st = gemm(d->v, d->v_bits, d->v_scale, nullptr, x, h, d->in_features, d->rank);

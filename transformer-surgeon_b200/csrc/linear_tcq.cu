@@ -20,8 +20,13 @@
 //   * split-K: every item stores its fp32 partial tile in a private slice of the workspace (plain
 //     stores, no zero-fill needed); the last CTA to finish a tile (a per-tile counter, reset by
 //     that CTA) sums the slices in split order - a deterministic result - and writes the output.
-// Every mbarrier wait is bounded (see tc_common.cuh); on expiry the CTA records a code in the
-// status word, drains, frees its TMEM and returns.
+//   * a launch executes a PROGRAM of up to 4 phases separated by grid-wide barriers (all CTAs are
+//     co-resident: grid <= #SMs, one CTA per SM, cooperative launch): the V and U factors of a
+//     low-rank layer, or the whole gated MLP (gate|up V, gate|up U with SiLU(g)*u in the epilogue,
+//     down V, down U), run in ONE launch; the rank-r intermediates never leave L2, and the
+//     producer already streams the next phase's weights while the barrier is pending.
+// Every mbarrier / grid-barrier wait is bounded (see tc_common.cuh); on expiry the CTA records a
+// code in the status word, drains, frees its TMEM and returns.
 #include "tc_common.cuh"
 
 namespace tsb {
@@ -151,29 +156,59 @@ __device__ __forceinline__ bool warps_rendezvous(unsigned long long* bar, int& u
   return ok;
 }
 
-// Optional phase trace (compile with -DTSB_TRACE): CTA 0 stores clock64 stamps in bytes 64.. of the
+
+// Optional phase trace (compile with -DTSB_TRACE): CTA 0 stores clock64 stamps in bytes 128.. of the
 // workspace header.
 #ifdef TSB_TRACE
-#define TSB_STAMP(i) do { if (blockIdx.x == 0) reinterpret_cast<long long*>(reinterpret_cast<char*>(p.status) + 64)[i] = clock64(); } while (0)
+#define TSB_STAMP(i) do { if (blockIdx.x == 0) reinterpret_cast<long long*>(reinterpret_cast<char*>(prog.status) + 128)[i] = clock64(); } while (0)
 #else
 #define TSB_STAMP(i) do { } while (0)
 #endif
 
-struct QParams {
-  int64_t M, N, K;
-  int kb_total, kb_per_split, splits;
-  int n_tiles, m_tiles, items;
-  const float* scale;
-  const __nv_bfloat16* bias;
-  __nv_bfloat16* y;
-  float* partial;      // split-K: fp32 slices [items][TN][128], written before they are read
-  int* counters;       // split-K: zero-filled int32 [n_tiles * m_tiles], left zero
-  int* status;
+constexpr int kMaxPhases = 4;
+
+struct SubGemm {                 // one packed weight matrix and its operands
+  CUtensorMap map_w;             // uint8 [N, row_bytes], box 128 rows x stage-row bytes, swizzled
+  CUtensorMap map_x;             // bf16 [M, K], box TN rows x 64, 128-byte swizzle
+  const float* scale;            // [N]
+  const __nv_bfloat16* bias;     // [N] or null
+  __nv_bfloat16* y;              // [M, N]
 };
+struct Phase {
+  SubGemm sub[2];
+  int nsub;                      // 1, or 2 matrices of identical shape sharing the plan
+  int gated;                     // 1: an item computes sub[0] (gate) and sub[1] (up) tiles and stores
+                                 //    silu(gate) * up to sub[0].y; requires splits == 1 and TN <= 64
+  int64_t N, K;
+  int kb_total, kb_per_split, splits;
+  int n_tiles, m_tiles, items_per_sub, items;
+  float* partial;                // split-K: fp32 slices [items][TN][128] of this phase
+  int* counters;                 // split-K: zero-filled int32 [nsub * n_tiles * m_tiles], left zero
+};
+struct Program {
+  int64_t M;
+  int n_phases;
+  int* status;                   // workspace header: [0] status word
+  int* grid_bar;                 // kMaxPhases barrier counters + 1 exit counter, zero between launches
+  Phase ph[kMaxPhases];
+};
+
+// Bounded wait for `*ctr >= target` (another CTA's release increments).  False = gave up.
+__device__ __forceinline__ bool grid_wait(const int* ctr, int target, volatile int* abort_flag) {
+  for (unsigned i = 0; i < (1u << 22); ++i) {
+    int v;
+    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];\n" : "=r"(v) : "l"(ctr) : "memory");
+    if (v >= target) return true;
+    if ((i & 63u) == 63u && *abort_flag) return false;
+    __nanosleep(64);
+  }
+  *abort_flag = 9;
+  return false;
+}
 
 template <int TN, int BITS>
 __global__ void __launch_bounds__(kThreadsQ, 1)
-linear_tcq_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, QParams p) {
+linear_tcq_kernel(const __grid_constant__ Program prog) {
   using L = QLayout<TN, BITS>;
   constexpr int NR = L::NR;
   constexpr int KBS = L::KBS;
@@ -186,7 +221,7 @@ linear_tcq_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
   unsigned long long* raw_empty = bars + NR;                // [NR] 4 dequant warps of the owning group + MMA commit
   unsigned long long* a_ready = bars + 2 * NR;              // [2]  4 dequant warps: A buffer stored in TMEM
   unsigned long long* a_empty = a_ready + 2;                // [2]  MMA commit: A buffer consumed
-  unsigned long long* acc_full = a_empty + 2;               // [1]  MMA commit: accumulator of the item complete
+  unsigned long long* acc_full = a_empty + 2;               // [1]  MMA commit: accumulator(s) of the item complete
   unsigned long long* ep_bar = acc_full + 1;                // [1]  rendezvous of the 8 warps
   unsigned* tmem_slot = reinterpret_cast<unsigned*>(ep_bar + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -211,51 +246,78 @@ linear_tcq_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
   const unsigned tmem_base = *tmem_slot;
   if (threadIdx.x == 0) TSB_STAMP(0);
 
-  // item -> (n tile, m tile, split); the same enumeration in every role
-  auto decode = [&](int item, int& nt, int& mt, int& kb0, int& nkb) {
-    const int sp = item % p.splits;
-    const int t = item / p.splits;
-    nt = t % p.n_tiles;
-    mt = t / p.n_tiles;
-    kb0 = sp * p.kb_per_split;
-    nkb = min(p.kb_per_split, p.kb_total - kb0);
+  // Work enumeration, identical in every role.  Phase -> items (round-robin over CTAs) -> passes
+  // (one per matrix the item touches: 2 for a gated item) -> stages of KBS k-blocks.
+  struct Item { int sub, nt, mt, kb0, nkb; };
+  auto decode = [&](const Phase& ph, int item) {
+    Item it;
+    int local = item;
+    it.sub = 0;
+    if (!ph.gated && ph.nsub == 2 && item >= ph.items_per_sub) { it.sub = 1; local = item - ph.items_per_sub; }
+    const int sp = local % ph.splits;
+    const int t = local / ph.splits;
+    it.nt = t % ph.n_tiles;
+    it.mt = t / ph.n_tiles;
+    it.kb0 = sp * ph.kb_per_split;
+    it.nkb = min(ph.kb_per_split, ph.kb_total - it.kb0);
+    return it;
   };
 
   if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer
     if (lane == 0) {
-      asm volatile("prefetch.tensormap [%0];\n" ::"l"(&map_w) : "memory");
-      asm volatile("prefetch.tensormap [%0];\n" ::"l"(&map_x) : "memory");
-      // Walk stages [g_begin, g_end) of this CTA's item list.  The packed weights are constants, so
-      // their boxes for the first NR stages are requested BEFORE waiting for the preceding kernel;
-      // the activation tiles of those stages follow after the wait.
+      for (int p = 0; p < prog.n_phases; ++p)
+        for (int j = 0; j < prog.ph[p].nsub; ++j) {
+          asm volatile("prefetch.tensormap [%0];\n" ::"l"(&prog.ph[p].sub[j].map_w) : "memory");
+          asm volatile("prefetch.tensormap [%0];\n" ::"l"(&prog.ph[p].sub[j].map_x) : "memory");
+        }
+      // The packed weights are constants: for the first NR stages of a phase their boxes are
+      // requested BEFORE the phase's activations exist (before the wait on the preceding kernel
+      // for phase 0, before the grid barrier for later phases); the activation tiles follow.
       bool ok = true;
-      auto walk = [&](int g_begin, int g_end, bool do_w, bool do_x, bool arm) {
-        int gs = 0;
-        for (int item = blockIdx.x; item < p.items && ok && gs < g_end; item += gridDim.x) {
-          int nt, mt, kb0, nkb;
-          decode(item, nt, mt, kb0, nkb);
-          for (int i = 0; i < nkb && gs < g_end; i += KBS, ++gs) {
-            if (gs < g_begin) continue;
-            const int s = gs % NR;
-            if (gs >= NR && !mbar_wait(&raw_empty[s], ((gs / NR) - 1) & 1, abort_flag, 1)) { ok = false; return; }
-            uint8_t* st = r_ring + s * L::kStage;
-            if (arm) mbar_expect_tx(&raw_full[s], TX_BYTES);
-            const int kcol = (kb0 + i) * BK;
-            if (do_x) {
+      int gs_phase0 = 0;                                      // stage counter at the start of the phase
+      auto walk = [&](const Phase& ph, int rel_begin, int rel_end, bool do_w, bool do_x, bool arm) -> int {
+        int gs = gs_phase0;                                   // absolute stage counter
+        for (int item = blockIdx.x; item < ph.items && ok; item += gridDim.x) {
+          const Item it = decode(ph, item);
+          const int passes = ph.gated ? 2 : 1;
+          for (int ps = 0; ps < passes; ++ps) {
+            const SubGemm& sg = ph.sub[ph.gated ? ps : it.sub];
+            for (int i = 0; i < it.nkb; i += KBS, ++gs) {
+              const int rel = gs - gs_phase0;
+              if (rel >= rel_end) return gs;
+              if (rel < rel_begin) continue;
+              const int s = gs % NR;
+              if (arm && gs >= NR && !mbar_wait(&raw_empty[s], ((gs / NR) - 1) & 1, abort_flag, 1)) { ok = false; return gs; }
+              uint8_t* st = r_ring + s * L::kStage;
+              if (arm) mbar_expect_tx(&raw_full[s], TX_BYTES);
+              const int kcol = (it.kb0 + i) * BK;
+              if (do_x) {
 #pragma unroll
-              for (int j = 0; j < KBS; ++j)                   // columns beyond K are zero-filled by the copy engine
-                tma_load_2d(st + j * L::kXTile, &map_x, kcol + j * BK, mt * TN, &raw_full[s]);
+                for (int j = 0; j < KBS; ++j)                 // columns beyond K are zero-filled by the copy engine
+                  tma_load_2d(st + j * L::kXTile, &sg.map_x, kcol + j * BK, it.mt * TN, &raw_full[s]);
+              }
+              if (do_w) tma_load_2d(st + L::kX, &sg.map_w, kcol * BITS / 8, it.nt * BM, &raw_full[s]);
+              if (gs == 0 && do_w) TSB_STAMP(1);
             }
-            if (do_w) tma_load_2d(st + L::kX, &map_w, kcol * BITS / 8, nt * BM, &raw_full[s]);
-            if (gs == 0 && do_w) TSB_STAMP(1);
           }
         }
+        return gs;
       };
-      walk(0, NR, true, false, true);
-      pdl_wait();
-      walk(0, NR, false, true, false);
-      walk(NR, 0x7fffffff, true, true, true);
+      for (int p = 0; p < prog.n_phases && ok; ++p) {
+        const Phase& ph = prog.ph[p];
+        walk(ph, 0, NR, true, false, true);
+        if (p == 0) {
+          pdl_wait();
+        } else {
+          ok = ok && grid_wait(&prog.grid_bar[p - 1], (int)gridDim.x, abort_flag);
+          asm volatile("fence.proxy.async;\n" ::: "memory");  // other CTAs' stores -> visible to the copy engine
+        }
+        if (!ok) break;
+        walk(ph, 0, NR, false, true, false);
+        gs_phase0 = walk(ph, NR, 0x7fffffff, true, true, true);
+        if (gs_phase0 < 0) break;
+      }
     }
   } else if (warp == 1) {
     // ---------------------------------------------------------------- MMA issuer
@@ -263,27 +325,33 @@ linear_tcq_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
       constexpr unsigned idesc = idesc_bf16(TN);
       int gs = 0;
       bool ok = true;
-      for (int item = blockIdx.x; item < p.items && ok; item += gridDim.x) {
-        int nt, mt, kb0, nkb;
-        decode(item, nt, mt, kb0, nkb);
-        for (int i = 0; i < nkb; i += KBS, ++gs) {
-          const int s = gs % NR, buf = gs & 1;
-          ok = mbar_wait(&raw_full[s], (gs / NR) & 1, abort_flag, 2) && mbar_wait(&a_ready[buf], (gs >> 1) & 1, abort_flag, 3);
-          if (!ok) break;
-          tc_fence_after();
-          const unsigned a_tmem = tmem_base + kACol0 + buf * 128;
-          const unsigned x_base = smem_u32(r_ring + s * L::kStage);
-          const int nsub = min(KBS, nkb - i);
-          for (int j = 0; j < nsub; ++j) {
-            const unsigned long long bdesc = smem_desc_sw128(x_base + j * L::kXTile);
+      for (int p = 0; p < prog.n_phases && ok; ++p) {
+        const Phase& ph = prog.ph[p];
+        for (int item = blockIdx.x; item < ph.items && ok; item += gridDim.x) {
+          const Item it = decode(ph, item);
+          const int passes = ph.gated ? 2 : 1;
+          for (int ps = 0; ps < passes && ok; ++ps) {
+            const unsigned d_tmem = tmem_base + ps * TN;      // gated: gate -> columns [0, TN), up -> [TN, 2 TN)
+            for (int i = 0; i < it.nkb; i += KBS, ++gs) {
+              const int s = gs % NR, buf = gs & 1;
+              ok = mbar_wait(&raw_full[s], (gs / NR) & 1, abort_flag, 2) && mbar_wait(&a_ready[buf], (gs >> 1) & 1, abort_flag, 3);
+              if (!ok) break;
+              tc_fence_after();
+              const unsigned a_tmem = tmem_base + kACol0 + buf * 128;
+              const unsigned x_base = smem_u32(r_ring + s * L::kStage);
+              const int nsub = min(KBS, it.nkb - i);
+              for (int j = 0; j < nsub; ++j) {
+                const unsigned long long bdesc = smem_desc_sw128(x_base + j * L::kXTile);
 #pragma unroll
-            for (int k = 0; k < BK / 16; ++k)   // A: 8 TMEM columns per K=16; B: +32 bytes inside the swizzle atom
-              umma_bf16_ts(tmem_base, a_tmem + j * 32 + k * 8, bdesc + 2 * k, idesc, (i + j > 0 || k > 0) ? 1u : 0u);
+                for (int k = 0; k < BK / 16; ++k)   // A: 8 TMEM columns per K=16; B: +32 bytes inside the swizzle atom
+                  umma_bf16_ts(d_tmem, a_tmem + j * 32 + k * 8, bdesc + 2 * k, idesc, (i + j > 0 || k > 0) ? 1u : 0u);
+              }
+              umma_commit(&a_empty[buf]);
+              umma_commit(&raw_empty[s]);
+            }
           }
-          umma_commit(&a_empty[buf]);
-          umma_commit(&raw_empty[s]);
+          if (ok) umma_commit(acc_full);
         }
-        if (ok) umma_commit(acc_full);
       }
     }
   } else {
@@ -292,117 +360,156 @@ linear_tcq_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
     const int q = warp & 3;                                  // TMEM lane quarter this warp may access
     const int row = q * 32 + lane;                           // weight row within the tile = TMEM lane
     const unsigned lane_addr = tmem_base + ((unsigned)(q * 32) << 16);
-    int gs = 0, it = 0, ep_uses = 0;
+    int gs = 0, it_count = 0, ep_uses = 0;
     bool ok = true;
-    for (int item = blockIdx.x; item < p.items && ok; item += gridDim.x, ++it) {
-      int nt, mt, kb0, nkb;
-      decode(item, nt, mt, kb0, nkb);
-      // per-row epilogue constants (weights-side data): requested now, consumed after the main loop
-      const int64_t n = (int64_t)nt * BM + row;
-      const float sc = (p.scale && n < p.N) ? __ldg(&p.scale[n]) : 1.0f;
-      const float bv = (p.bias && n < p.N) ? __bfloat162float(p.bias[n]) : 0.f;
-      for (int i = 0; i < nkb; i += KBS, ++gs) {
-        if ((gs & 1) != grp) continue;
-        const int s = gs % NR, buf = gs & 1;
-        ok = mbar_wait(&raw_full[s], (gs / NR) & 1, abort_flag, 4);
-        if (ok && gs >= 2) ok = mbar_wait(&a_empty[buf], ((gs >> 1) - 1) & 1, abort_flag, 5);
-        if (!ok) break;
-        if (gs == 0 && threadIdx.x == 64) TSB_STAMP(2);
-        tc_fence_after();
-        const unsigned raw = smem_u32(r_ring + s * L::kStage + L::kX);
-        const int nsub = min(KBS, nkb - i);
-        for (int j = 0; j < nsub; ++j) {
-          unsigned regs[32];
-          dequant_row_regs<BITS, L::kRawStageRow>(raw, row, j, regs);
-          tmem_st32(lane_addr + kACol0 + buf * 128 + j * 32, regs);
+    bool waited = false;
+    for (int p = 0; p < prog.n_phases && ok; ++p) {
+      const Phase& ph = prog.ph[p];
+      for (int item = blockIdx.x; item < ph.items && ok; item += gridDim.x, ++it_count) {
+        const Item it = decode(ph, item);
+        const int passes = ph.gated ? 2 : 1;
+        // per-row epilogue constants (weights-side data): requested now, consumed after the main loop
+        const int64_t n = (int64_t)it.nt * BM + row;
+        const SubGemm& sg0 = ph.sub[ph.gated ? 0 : it.sub];
+        const float sc0 = n < ph.N ? __ldg(&sg0.scale[n]) : 1.0f;
+        const float bv0 = (sg0.bias && n < ph.N) ? __bfloat162float(sg0.bias[n]) : 0.f;
+        float sc1 = 1.0f, bv1 = 0.f;
+        if (ph.gated) {
+          sc1 = n < ph.N ? __ldg(&ph.sub[1].scale[n]) : 1.0f;
+          bv1 = (ph.sub[1].bias && n < ph.N) ? __bfloat162float(ph.sub[1].bias[n]) : 0.f;
         }
-        tmem_st_wait();
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) { mbar_arrive(&a_ready[buf]); mbar_arrive(&raw_empty[s]); }
-        if (threadIdx.x == 64) { if (gs == 0) TSB_STAMP(3); TSB_STAMP(4); }
-      }
-      if (!ok) break;
-      ok = mbar_wait(acc_full, it & 1, abort_flag, 6);
-      if (!ok) break;
-      if (threadIdx.x == 64) TSB_STAMP(5);
-      tc_fence_after();
-      if (it == 0) pdl_wait();                               // outputs / split-K scratch may still be in use upstream
-      const int64_t m0 = (int64_t)mt * TN;
-      const bool split = p.splits > 1;
-      constexpr int CH = TN / 2;                             // token columns handled by this warp
-      float* slice = p.partial + (size_t)item * (TN * BM);   // [TN][128] of this item
-#pragma unroll 1
-      for (int c0 = grp * CH; c0 < (grp + 1) * CH; c0 += 8) {
-        unsigned r[8];
-        tmem_ld8(lane_addr + (unsigned)c0, r);
-        tmem_ld_wait();
-        if (split) {
-#pragma unroll
-          for (int j = 0; j < 8; ++j) __stcg(&slice[(c0 + j) * BM + row], __uint_as_float(r[j]));
-        } else if (n < p.N) {
-#pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            const int64_t m = m0 + c0 + j;
-            if (m < p.M) p.y[m * p.N + n] = __float2bfloat16_rn(__uint_as_float(r[j]) * sc + bv);
+        for (int ps = 0; ps < passes && ok; ++ps) {
+          for (int i = 0; i < it.nkb; i += KBS, ++gs) {
+            if ((gs & 1) != grp) continue;
+            const int s = gs % NR, buf = gs & 1;
+            ok = mbar_wait(&raw_full[s], (gs / NR) & 1, abort_flag, 4);
+            if (ok && gs >= 2) ok = mbar_wait(&a_empty[buf], ((gs >> 1) - 1) & 1, abort_flag, 5);
+            if (!ok) break;
+            if (gs == 0 && threadIdx.x == 64) TSB_STAMP(2);
+            tc_fence_after();
+            const unsigned raw = smem_u32(r_ring + s * L::kStage + L::kX);
+            const int nsub = min(KBS, it.nkb - i);
+            for (int j = 0; j < nsub; ++j) {
+              unsigned regs[32];
+              dequant_row_regs<BITS, L::kRawStageRow>(raw, row, j, regs);
+              tmem_st32(lane_addr + kACol0 + buf * 128 + j * 32, regs);
+            }
+            tmem_st_wait();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) { mbar_arrive(&a_ready[buf]); mbar_arrive(&raw_empty[s]); }
+            if (threadIdx.x == 64) { if (gs == 0) TSB_STAMP(3); TSB_STAMP(4); }
           }
         }
-      }
-      tc_fence_before();
-      // every warp is done reading the accumulator before any warp stores the next item's A operand
-      if (!(ok = warps_rendezvous(ep_bar, ep_uses, lane, abort_flag))) break;
-      if (split) {
-        // last CTA of this (n tile, m tile) finalizes: sum of the slices -> y, then reset the counter
-        __threadfence();
-        if (!(ok = warps_rendezvous(ep_bar, ep_uses, lane, abort_flag))) break;
-        if (threadIdx.x == 64) {
-          const int old = atomicAdd(&p.counters[mt * p.n_tiles + nt], 1);
-          *last_flag = (old == p.splits - 1);
-        }
-        if (!(ok = warps_rendezvous(ep_bar, ep_uses, lane, abort_flag))) break;
-        const bool last = *last_flag != 0;
-        if (last) {
-          __threadfence();
-          if (n < p.N) {
-            const float* tile0 = p.partial + (size_t)(item - item % p.splits) * (TN * BM) + row;
-            // 8 token columns at a time: the 8 loads of one split are independent (in flight together);
-            // splits are added in index order, so the result does not depend on arrival order
-            for (int c0 = grp * CH; c0 < (grp + 1) * CH; c0 += 8) {
-              float v[8];
-#pragma unroll
-              for (int j = 0; j < 8; ++j) v[j] = 0.f;
-              int sp = 0;
-              for (; sp + 4 <= p.splits; sp += 4) {          // 32 loads in flight
-                float a[4][8];
-#pragma unroll
-                for (int u = 0; u < 4; ++u)
-#pragma unroll
-                  for (int j = 0; j < 8; ++j) a[u][j] = __ldcg(tile0 + (size_t)(sp + u) * (TN * BM) + (c0 + j) * BM);
-#pragma unroll
-                for (int u = 0; u < 4; ++u)
-#pragma unroll
-                  for (int j = 0; j < 8; ++j) v[j] += a[u][j];
-              }
-              for (; sp < p.splits; ++sp) {
-                float a[8];
-#pragma unroll
-                for (int j = 0; j < 8; ++j) a[j] = __ldcg(tile0 + (size_t)sp * (TN * BM) + (c0 + j) * BM);
-#pragma unroll
-                for (int j = 0; j < 8; ++j) v[j] += a[j];
-              }
+        if (!ok) break;
+        ok = mbar_wait(acc_full, it_count & 1, abort_flag, 6);
+        if (!ok) break;
+        if (threadIdx.x == 64) TSB_STAMP(5);
+        tc_fence_after();
+        if (!waited) { pdl_wait(); waited = true; }          // outputs / scratch may still be in use upstream
+        const int64_t m0 = (int64_t)it.mt * TN;
+        const bool split = ph.splits > 1;
+        constexpr int CH = TN / 2;                           // token columns handled by this warp
+        float* slice = ph.partial + (size_t)item * (TN * BM);
+        __nv_bfloat16* y = sg0.y;
+#pragma unroll 1
+        for (int c0 = grp * CH; c0 < (grp + 1) * CH; c0 += 8) {
+          unsigned r[8];
+          tmem_ld8(lane_addr + (unsigned)c0, r);
+          if (ph.gated) {
+            unsigned r2[8];
+            tmem_ld8(lane_addr + (unsigned)(TN + c0), r2);
+            tmem_ld_wait();
+            if (n < ph.N) {
 #pragma unroll
               for (int j = 0; j < 8; ++j) {
                 const int64_t m = m0 + c0 + j;
-                if (m < p.M) p.y[m * p.N + n] = __float2bfloat16_rn(v[j] * sc + bv);
+                if (m < prog.M) {
+                  // same rounding points as separate gate / up / SiLU*up kernels (blocks/mlp.py:181-183)
+                  const float g = __bfloat162float(__float2bfloat16_rn(__uint_as_float(r[j]) * sc0 + bv0));
+                  const float u = __bfloat162float(__float2bfloat16_rn(__uint_as_float(r2[j]) * sc1 + bv1));
+                  const float a = __bfloat162float(__float2bfloat16_rn(g / (1.0f + expf(-g))));
+                  y[m * ph.N + n] = __float2bfloat16_rn(__fmul_rn(a, u));
+                }
+              }
+            }
+          } else {
+            tmem_ld_wait();
+            if (split) {
+#pragma unroll
+              for (int j = 0; j < 8; ++j) __stcg(&slice[(c0 + j) * BM + row], __uint_as_float(r[j]));
+            } else if (n < ph.N) {
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                const int64_t m = m0 + c0 + j;
+                if (m < prog.M) y[m * ph.N + n] = __float2bfloat16_rn(__uint_as_float(r[j]) * sc0 + bv0);
               }
             }
           }
-          if (threadIdx.x == 64) p.counters[mt * p.n_tiles + nt] = 0;
         }
-        if (!(ok = warps_rendezvous(ep_bar, ep_uses, lane, abort_flag))) break;   // last_flag is reused by the next item
+        tc_fence_before();
+        // every warp is done reading the accumulator before any warp stores the next item's A operand
+        if (!(ok = warps_rendezvous(ep_bar, ep_uses, lane, abort_flag))) break;
+        if (split) {
+          // last CTA of this (matrix, n tile, m tile) finalizes: sum of the slices -> y, then resets the counter
+          int* ctr = &ph.counters[(it.sub * ph.m_tiles + it.mt) * ph.n_tiles + it.nt];
+          __threadfence();
+          if (!(ok = warps_rendezvous(ep_bar, ep_uses, lane, abort_flag))) break;
+          if (threadIdx.x == 64) *last_flag = (atomicAdd(ctr, 1) == ph.splits - 1);
+          if (!(ok = warps_rendezvous(ep_bar, ep_uses, lane, abort_flag))) break;
+          const bool last = *last_flag != 0;
+          if (last) {
+            __threadfence();
+            if (n < ph.N) {
+              const float* tile0 = ph.partial + (size_t)(item - item % ph.splits) * (TN * BM) + row;
+              // 8 token columns at a time, 4 splits in flight; splits are added in index order, so the
+              // result does not depend on arrival order
+              for (int c0 = grp * CH; c0 < (grp + 1) * CH; c0 += 8) {
+                float v[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v[j] = 0.f;
+                int sp = 0;
+                for (; sp + 4 <= ph.splits; sp += 4) {
+                  float a[4][8];
+#pragma unroll
+                  for (int u = 0; u < 4; ++u)
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) a[u][j] = __ldcg(tile0 + (size_t)(sp + u) * (TN * BM) + (c0 + j) * BM);
+#pragma unroll
+                  for (int u = 0; u < 4; ++u)
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) v[j] += a[u][j];
+                }
+                for (; sp < ph.splits; ++sp) {
+                  float a[8];
+#pragma unroll
+                  for (int j = 0; j < 8; ++j) a[j] = __ldcg(tile0 + (size_t)sp * (TN * BM) + (c0 + j) * BM);
+#pragma unroll
+                  for (int j = 0; j < 8; ++j) v[j] += a[j];
+                }
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                  const int64_t m = m0 + c0 + j;
+                  if (m < prog.M) y[m * ph.N + n] = __float2bfloat16_rn(v[j] * sc0 + bv0);
+                }
+              }
+            }
+            if (threadIdx.x == 64) *ctr = 0;
+          }
+          if (!(ok = warps_rendezvous(ep_bar, ep_uses, lane, abort_flag))) break;   // last_flag is reused by the next item
+        }
+        tc_fence_after();
+        if (threadIdx.x == 64) TSB_STAMP(6);
       }
-      tc_fence_after();
-      if (threadIdx.x == 64) TSB_STAMP(6);
+      if (!ok) break;
+      // ---- end of phase: publish this CTA's outputs, then signal the grid barrier ------------------
+      if (p + 1 < prog.n_phases) {
+        if (!waited) { pdl_wait(); waited = true; }
+        asm volatile("fence.proxy.async;\n" ::: "memory");    // generic stores -> visible to other CTAs' copy engines
+        __threadfence();
+        if (!(ok = warps_rendezvous(ep_bar, ep_uses, lane, abort_flag))) break;
+        if (threadIdx.x == 64) atomicAdd(&prog.grid_bar[p], 1);
+      }
     }
   }
   if (*abort_flag) {
@@ -414,8 +521,17 @@ linear_tcq_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
     tc_fence_after();
     tmem_dealloc(tmem_base, kTmemCols);
   }
-  if (threadIdx.x == 0) TSB_STAMP(7);
-  if (threadIdx.x == 0 && *abort_flag) atomicMax(p.status, *abort_flag);
+  if (threadIdx.x == 0) {
+    TSB_STAMP(7);
+    if (*abort_flag) atomicMax(prog.status, *abort_flag);
+    if (prog.n_phases > 1) {
+      // the last CTA to leave resets the grid-barrier counters for the next launch
+      __threadfence();
+      if (atomicAdd(&prog.grid_bar[kMaxPhases], 1) == (int)gridDim.x - 1) {
+        for (int i = 0; i <= kMaxPhases; ++i) prog.grid_bar[i] = 0;
+      }
+    }
+  }
 }
 
 }  // namespace
@@ -425,7 +541,7 @@ namespace tsb {
 namespace {
 
 template <int TN, int BITS>
-int launch_q(const CUtensorMap& mw, const CUtensorMap& mx, const QParams& p, int grid, cudaStream_t s) {
+int launch_q(const Program& prog, int grid, cudaStream_t s) {
   using L = QLayout<TN, BITS>;
   static bool configured[64] = {false};
   int dev = 0;
@@ -435,16 +551,41 @@ int launch_q(const CUtensorMap& mw, const CUtensorMap& mx, const QParams& p, int
     TSB_CUDA(cudaFuncSetAttribute(linear_tcq_kernel<TN, BITS>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kBytes));
     configured[dev] = true;
   }
-  TSB_CUDA(launch_kernel(linear_tcq_kernel<TN, BITS>, dim3(grid), dim3(kThreadsQ), (size_t)L::kBytes, s, mw, mx, p));
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)grid);
+  cfg.blockDim = dim3(kThreadsQ);
+  cfg.dynamicSmemBytes = (size_t)L::kBytes;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[2];
+  int na = 0;
+  if (prog.n_phases > 1) {     // grid barriers: every CTA must be resident at once
+    attr[na].id = cudaLaunchAttributeCooperative;
+    attr[na].val.cooperative = 1;
+    ++na;
+  }
+  if (g_pdl) {
+    attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[na].val.programmaticStreamSerializationAllowed = 1;
+    ++na;
+  }
+  cfg.attrs = attr;
+  cfg.numAttrs = na;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, linear_tcq_kernel<TN, BITS>, prog);
+  if (e != cudaSuccess && na == 2) {   // the two attributes are not accepted together: keep co-residency
+    (void)cudaGetLastError();
+    cfg.numAttrs = 1;
+    e = cudaLaunchKernelEx(&cfg, linear_tcq_kernel<TN, BITS>, prog);
+  }
+  TSB_CUDA(e);
   return TSB200_OK;
 }
 
 template <int TN>
-int launch_q_bits(int bits, const CUtensorMap& mw, const CUtensorMap& mx, const QParams& p, int grid, cudaStream_t s) {
+int launch_q_bits(int bits, const Program& prog, int grid, cudaStream_t s) {
   switch (bits) {
-    case 2: return launch_q<TN, 2>(mw, mx, p, grid, s);
-    case 4: return launch_q<TN, 4>(mw, mx, p, grid, s);
-    case 8: return launch_q<TN, 8>(mw, mx, p, grid, s);
+    case 2: return launch_q<TN, 2>(prog, grid, s);
+    case 4: return launch_q<TN, 4>(prog, grid, s);
+    case 8: return launch_q<TN, 8>(prog, grid, s);
     default: return TSB200_ERR_UNSUPPORTED;
   }
 }
@@ -469,37 +610,86 @@ int num_sms() {
   return sms[dev];
 }
 
+bool fill_sub(SubGemm& sg, const GemmSpec& g, int64_t M, int tn, int bits) {
+  const uint64_t rb = tsb200_packed_row_bytes(g.K, bits);
+  const int box = raw_box_bytes(tn, bits);
+  const CUtensorMapSwizzle sw = box == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : (box == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B);
+  if (!make_map(&sg.map_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, g.W, rb, (uint64_t)g.N, rb, (uint32_t)box, BM, sw)) return false;
+  if (!make_map(&sg.map_x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, g.x, (uint64_t)g.K, (uint64_t)M, (uint64_t)g.K * 2, BK, (uint32_t)tn,
+                CU_TENSOR_MAP_SWIZZLE_128B))
+    return false;
+  sg.scale = g.scale;
+  sg.bias = (const __nv_bfloat16*)g.bias;
+  sg.y = (__nv_bfloat16*)g.y;
+  return true;
+}
+
 }  // namespace
+
+size_t phase_scratch_bytes(int64_t M, int64_t N, int64_t K, int nsub, bool gated) {
+  return plan_gemm(M, N, K, nsub, gated).slice_bytes;
+}
+
+// Run a program of phases in one launch.  All matrices packed at `bits`; bf16 activations.
+// scratch: split-K slices (sum over phases of phase_scratch_bytes); counters / grid_bar / status:
+// the zero-filled workspace header.
+int run_program_tcq(const PhaseSpec* specs, int n_phases, int bits, int64_t M, uint8_t* scratch, int* counters, int* grid_bar,
+                    int* status, cudaStream_t s) {
+  if (n_phases < 1 || n_phases > kMaxPhases) return TSB200_ERR_ARG;
+  Program prog;
+  prog.M = M;
+  prog.n_phases = n_phases;
+  prog.status = status;
+  prog.grid_bar = grid_bar;
+  int tn = 0, max_items = 0, ctr_off = 0;
+  size_t sc_off = 0;
+  for (int p = 0; p < n_phases; ++p) {
+    const PhaseSpec& ps = specs[p];
+    Phase& ph = prog.ph[p];
+    const GemmPlan g = plan_gemm(M, ps.g[0].N, ps.g[0].K, ps.gated ? 1 : ps.nsub, ps.gated != 0);
+    if (p == 0) tn = g.tn;
+    if (ps.gated && (g.tn > 64 || ps.nsub != 2)) return TSB200_ERR_UNSUPPORTED;
+    ph.nsub = ps.nsub;
+    ph.gated = ps.gated;
+    ph.N = ps.g[0].N;
+    ph.K = ps.g[0].K;
+    ph.kb_total = g.kb_total;
+    ph.kb_per_split = g.kb_per_split;
+    ph.splits = g.splits;
+    ph.n_tiles = g.n_tiles;
+    ph.m_tiles = g.m_tiles;
+    ph.items = g.items;
+    ph.items_per_sub = ps.gated ? g.items : g.items / ps.nsub;
+    for (int j = 0; j < ps.nsub; ++j) {
+      if (ps.g[j].N != ph.N || ps.g[j].K != ph.K) return TSB200_ERR_ARG;
+      if (!fill_sub(ph.sub[j], ps.g[j], M, g.tn, bits)) return TSB200_ERR_CUDA;
+    }
+    const int tiles = ps.nsub * g.n_tiles * g.m_tiles;
+    if (g.splits > 1 && ctr_off + tiles > kMaxCounters) return TSB200_ERR_UNSUPPORTED;
+    ph.counters = counters + ctr_off;
+    ph.partial = (float*)(scratch + sc_off);
+    if (g.splits > 1) { ctr_off += tiles; sc_off += g.slice_bytes; }
+    if (g.items > max_items) max_items = g.items;
+  }
+  const int sms = num_sms();
+  const int grid = max_items < sms ? max_items : sms;
+  switch (tn) {
+    case 16: return launch_q_bits<16>(bits, prog, grid, s);
+    case 32: return launch_q_bits<32>(bits, prog, grid, s);
+    case 64: return launch_q_bits<64>(bits, prog, grid, s);
+    default: return launch_q_bits<128>(bits, prog, grid, s);
+  }
+}
 
 // y[M, N] = x[M, K] . Wq[N, K]^T * scale + bias; Wq packed at `bits` in {2, 4, 8}; bf16 in/out.
 // partial: split-K slice scratch (plan_gemm().slice_bytes); counters: zero-filled, left zero.
 int gemm_tcq(const void* W, int bits, const float* scale, const void* bias, const void* x, void* y, int64_t M, int64_t K,
              int64_t N, float* partial, int* counters, int* status, cudaStream_t s) {
-  const GemmPlan g = plan_gemm(M, N, K);
-  const int tn = g.tn;
-  CUtensorMap mw, mx;
-  const uint64_t rb = tsb200_packed_row_bytes(K, bits);
-  if (!make_map(&mw, CU_TENSOR_MAP_DATA_TYPE_UINT8, W, rb, (uint64_t)N, rb, (uint32_t)raw_box_bytes(tn, bits), BM,
-                raw_box_bytes(tn, bits) == 128 ? CU_TENSOR_MAP_SWIZZLE_128B
-                                               : (raw_box_bytes(tn, bits) == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B)))
-    return TSB200_ERR_CUDA;
-  if (!make_map(&mx, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, x, (uint64_t)K, (uint64_t)M, (uint64_t)K * 2, BK, (uint32_t)tn, CU_TENSOR_MAP_SWIZZLE_128B))
-    return TSB200_ERR_CUDA;
-  const int sms = num_sms();
-  if ((int64_t)g.n_tiles * g.m_tiles * g.splits > 0x3fffffffLL) return TSB200_ERR_UNSUPPORTED;
-  QParams p;
-  p.M = M; p.N = N; p.K = K;
-  p.kb_total = g.kb_total; p.kb_per_split = g.kb_per_split; p.splits = g.splits;
-  p.n_tiles = g.n_tiles; p.m_tiles = g.m_tiles; p.items = g.items;
-  p.scale = scale; p.bias = (const __nv_bfloat16*)bias; p.y = (__nv_bfloat16*)y;
-  p.partial = partial; p.counters = counters; p.status = status;
-  const int grid = p.items < sms ? p.items : sms;
-  switch (tn) {
-    case 16: return launch_q_bits<16>(bits, mw, mx, p, grid, s);
-    case 32: return launch_q_bits<32>(bits, mw, mx, p, grid, s);
-    case 64: return launch_q_bits<64>(bits, mw, mx, p, grid, s);
-    default: return launch_q_bits<128>(bits, mw, mx, p, grid, s);
-  }
+  PhaseSpec ps;
+  ps.nsub = 1;
+  ps.gated = 0;
+  ps.g[0] = GemmSpec{W, scale, bias, x, y, N, K};
+  return run_program_tcq(&ps, 1, bits, M, (uint8_t*)partial, counters, (int*)((uint8_t*)status + kWsGridBar), status, s);
 }
 
 }  // namespace tsb

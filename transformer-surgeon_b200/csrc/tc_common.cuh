@@ -11,7 +11,9 @@ constexpr int BM = 128;            // weight rows per tile = MMA M
 constexpr int BK = 64;             // k per k-block: one 128-byte swizzle atom of bf16
 constexpr unsigned kSpinLimit = 1u << 20;   // try_wait attempts before a bounded wait gives up
 
-// Workspace header shared by the linear kernels: status word, then split-K tile counters.
+// Workspace header shared by the linear kernels: status word (byte 0), grid-barrier counters of the
+// multi-phase kernel (byte 64..), then split-K tile counters.
+constexpr size_t kWsGridBar = 64;
 constexpr size_t kWsCounters = 256;
 constexpr int kMaxCounters = 4096;
 constexpr size_t kWsHeader = kWsCounters + kMaxCounters * sizeof(int);
@@ -24,14 +26,16 @@ struct GemmPlan {
   int tn, kb_total, kb_per_split, splits, n_tiles, m_tiles, items;
   size_t slice_bytes;      // split-K scratch: one fp32 [tn][128] slice per item (0 when splits == 1)
 };
-inline GemmPlan plan_gemm(int64_t M, int64_t N, int64_t K) {
+// nsub: number of equally shaped matrices sharing the launch (their tiles add up); no_split: keep
+// every tile's K range whole (needed when the epilogue combines two accumulators).
+inline GemmPlan plan_gemm(int64_t M, int64_t N, int64_t K, int nsub = 1, bool no_split = false) {
   GemmPlan g;
   g.tn = M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : 128));
   g.kb_total = (int)((K + BK - 1) / BK);
   const int64_t n_tiles = (N + BM - 1) / BM, m_tiles = (M + g.tn - 1) / g.tn;
-  const int64_t base = n_tiles * m_tiles;
+  const int64_t base = n_tiles * m_tiles * nsub;
   int splits = 1;
-  if (base > 0 && base < kPlanSMs * 3 / 4 && base <= kMaxCounters) {
+  if (!no_split && base > 0 && base < kPlanSMs * 3 / 4 && base <= kMaxCounters) {
     // fill the SMs once (prefer a single, nearly full wave); each split keeps >= 4 k-blocks
     const int lo = (int)(kPlanSMs / base), hi = (int)((kPlanSMs + base - 1) / base);
     splits = (base * lo >= kPlanSMs * 3 / 4) ? lo : hi;
@@ -43,7 +47,7 @@ inline GemmPlan plan_gemm(int64_t M, int64_t N, int64_t K) {
   g.splits = (g.kb_total + g.kb_per_split - 1) / g.kb_per_split;
   g.n_tiles = (int)n_tiles;
   g.m_tiles = (int)m_tiles;
-  g.items = (int)(base * g.splits);
+  g.items = (int)(base * g.splits);       // over all nsub matrices
   g.slice_bytes = g.splits > 1 ? (size_t)g.items * g.tn * BM * sizeof(float) : 0;
   return g;
 }
@@ -176,4 +180,25 @@ inline bool make_map(CUtensorMap* map, CUtensorMapDataType dt, const void* base,
 }
 
 }  // namespace tc
+
+// Host-side description of one matrix product y[M, N] = x[M, K] . W[N, K]^T * scale + bias.
+struct GemmSpec {
+  const void* W;
+  const float* scale;
+  const void* bias;
+  const void* x;
+  void* y;
+  int64_t N, K;
+};
+// One phase of a multi-phase launch: 1 matrix, 2 independent matrices of the same shape, or
+// (gated) a gate / up pair whose epilogue stores silu(gate) * up into g[0].y.
+struct PhaseSpec {
+  GemmSpec g[2];
+  int nsub;
+  int gated;
+};
+int run_program_tcq(const PhaseSpec* specs, int n_phases, int bits, int64_t M, uint8_t* scratch, int* counters, int* grid_bar,
+                    int* status, cudaStream_t s);
+size_t phase_scratch_bytes(int64_t M, int64_t N, int64_t K, int nsub, bool gated);
+
 }  // namespace tsb

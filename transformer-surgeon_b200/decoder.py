@@ -45,6 +45,7 @@ class LayerWeights:
     def __init__(self, ln1, ln2, o, gate, up, down, qkv=None, q=None, k=None, v=None):
         self.ln1, self.ln2, self.o, self.gate, self.up, self.down = ln1, ln2, o, gate, up, down
         self.qkv, self.q, self.k, self.v = qkv, q, k, v
+        self.mlp = ops.GatedMLP(gate, up, down)
 
 
 def fuse_rows(factors, biases, act_dtype):
@@ -98,9 +99,6 @@ class CompressedDecoder:
         self.vb = torch.empty((B, Hkv * d), dtype=dt, device=device)
         self.attn = torch.empty((B, H * d), dtype=dt, device=device)
         self.delta = torch.empty((B, c.hidden), dtype=dt, device=device)
-        self.gate = torch.empty((B, c.intermediate), dtype=dt, device=device)
-        self.up = torch.empty((B, c.intermediate), dtype=dt, device=device)
-        self.act = torch.empty((B, c.intermediate), dtype=dt, device=device)
         self.logits = torch.empty((B, c.vocab), dtype=dt, device=device)
         self.next_tokens = torch.zeros(B, dtype=torch.int64, device=device)
         lin_ws = 256
@@ -110,6 +108,7 @@ class CompressedDecoder:
                     lin_ws = max(lin_ws, lin.workspace_bytes(B))
         lin_ws = max(lin_ws, lm_head.workspace_bytes(B))
         self.lin_ws = torch.zeros(lin_ws, dtype=torch.uint8, device=device)
+        self.mlp_ws = torch.zeros(max(L.mlp.workspace_bytes(B) for L in layers), dtype=torch.uint8, device=device)
         self.attn_ws = torch.zeros(ops.decode_attn_workspace_bytes(B, H, d, max_seq_len), dtype=torch.uint8, device=device)
         self.graph = None
         self.kernel_launches_per_step = 0
@@ -142,11 +141,7 @@ class CompressedDecoder:
                                        ws=self.attn_ws, seq_lens=self.seq_lens); n += 2
             L.o(self.attn, out=self.delta, ws=self.lin_ws); n += 1
             ops.add_rmsnorm(self.resid, self.delta, L.ln2, c.rms_eps, c.norm_variant, out=self.xn); n += 1
-            L.gate(self.xn, out=self.gate, ws=self.lin_ws)
-            L.up(self.xn, out=self.up, ws=self.lin_ws)
-            n += 2 * (2 if L.gate.rank else 1)
-            ops.swiglu(self.gate, self.up, out=self.act); n += 1
-            L.down(self.act, out=self.delta, ws=self.lin_ws); n += 2 if L.down.rank else 1
+            L.mlp(self.xn, out=self.delta, ws=self.mlp_ws); n += 1
             delta = self.delta
         ops.add_rmsnorm(self.resid, delta, self.final_norm, c.rms_eps, c.norm_variant, out=self.xn); n += 1
         self.lm_head(self.xn, out=self.logits, ws=self.lin_ws); n += 1

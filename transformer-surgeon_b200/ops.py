@@ -231,6 +231,31 @@ class PackedLinear:
         return int(ws[:4].view(torch.int32).item())
 
 
+class GatedMLP:
+    """down(silu(gate(x)) * up(x)): MLPGated.forward (blocks/mlp.py:171-185) on three PackedLinear."""
+
+    def __init__(self, gate, up, down):
+        self.gate, self.up, self.down = gate, up, down
+
+    def workspace_bytes(self, M):
+        return int(_lib.load().tsb200_mlp_gated_workspace_bytes(C.byref(self.gate.desc), C.byref(self.up.desc),
+                                                                C.byref(self.down.desc), M))
+
+    def __call__(self, x, out=None, ws=None):
+        lib = _lib.load()
+        x = _cuda(x, "x")
+        lead = x.shape[:-1]
+        x2 = x.reshape(-1, x.shape[-1])
+        M = x2.shape[0]
+        if out is None:
+            out = torch.empty((M, self.down.out_features), dtype=x.dtype, device=x.device)
+        if ws is None:
+            ws = workspace(x.device, self.workspace_bytes(M), "mlp")
+        check(lib.tsb200_mlp_gated(C.byref(self.gate.desc), C.byref(self.up.desc), C.byref(self.down.desc), _p(x2),
+                                   _p(out), M, _p(ws), ws.numel(), _stream()), "tsb200_mlp_gated")
+        return out.reshape(*lead, self.down.out_features)
+
+
 # ---------------------------------------------------------------- KV cache ---------
 def kv_record_bytes(fmt, head_dim):
     return int(_lib.load().tsb200_kv_record_bytes(fmt, head_dim))
