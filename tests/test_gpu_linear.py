@@ -151,7 +151,10 @@ def test_gated_mlp_block(cuda, name, p, M, K, I, r, N):
     mlp = ops.GatedMLP(gate, up, down)
     y = mlp(x.to(cuda))
     y2 = mlp(x.to(cuda))
-    assert torch.equal(y, y2)                                   # deterministic split-K, clean workspace
+    if p is None:       # dense factors: the bf16 kernel adds its K splits with fp32 atomics (order varies)
+        assert rel_err(y, y2) < 1e-2
+    else:               # packed factors: deterministic split-K, workspace left clean
+        assert torch.equal(y, y2)
     assert rel_err(y.cpu(), ref) < (2e-2 if name == "bf16" else 1e-4), rel_err(y.cpu(), ref)
     # identical to composing the public pieces
     yc = down(ops.swiglu(gate(x.to(cuda)), up(x.to(cuda))))

@@ -32,16 +32,13 @@ bool fusable(const tsb200_linear_desc* g, const tsb200_linear_desc* u, const tsb
 }
 }  // namespace
 
-extern "C" {
-
-size_t tsb200_mlp_gated_workspace_bytes(const tsb200_linear_desc* gate, const tsb200_linear_desc* up,
-                                        const tsb200_linear_desc* down, int64_t M) {
-  if (!gate || !up || !down || M <= 0) return tc::kWsHeader;
-  const size_t elt = gate->act_dtype == TSB200_F32 ? 4 : 2;
-  const size_t inter = (size_t)gate->out_features;
-  size_t b = tc::kWsHeader;
-  b += 3 * align256((size_t)M * inter * elt);                       // gate out, up out / act
-  b += 3 * align256((size_t)M * (size_t)(gate->rank > down->rank ? gate->rank : down->rank) * elt);
+// Workspace layout: [region 0 | gate out | up out | act | h0 | h1 | h2].  Region 0 starts with the
+// zero-between-calls header (status, grid barrier, split-K counters) and continues with scratch that
+// needs no initialisation: split-K slices (fused path) or the body of the nested tsb200_linear
+// workspace (composed path).  Keeping the header at offset 0 in both paths makes one workspace
+// reusable across differently shaped blocks.
+static size_t region0_bytes(const tsb200_linear_desc* gate, const tsb200_linear_desc* up, const tsb200_linear_desc* down,
+                            int64_t M) {
   size_t scratch = 0;
   if (gate->rank > 0) scratch += phase_scratch_bytes(M, gate->rank, gate->in_features, 2, false);
   if (down->rank > 0) {
@@ -50,11 +47,25 @@ size_t tsb200_mlp_gated_workspace_bytes(const tsb200_linear_desc* gate, const ts
   } else {
     scratch += phase_scratch_bytes(M, down->out_features, down->in_features, 1, false);
   }
-  size_t lin = tsb200_linear_workspace_bytes(gate, M);
-  const size_t l2 = tsb200_linear_workspace_bytes(up, M), l3 = tsb200_linear_workspace_bytes(down, M);
-  if (l2 > lin) lin = l2;
-  if (l3 > lin) lin = l3;
-  return b + align256(scratch > lin ? scratch : lin) + 256;
+  size_t r0 = tc::kWsHeader + scratch;
+  const size_t l1 = tsb200_linear_workspace_bytes(gate, M), l2 = tsb200_linear_workspace_bytes(up, M),
+               l3 = tsb200_linear_workspace_bytes(down, M);
+  if (l1 > r0) r0 = l1;
+  if (l2 > r0) r0 = l2;
+  if (l3 > r0) r0 = l3;
+  return align256(r0);
+}
+
+extern "C" {
+
+size_t tsb200_mlp_gated_workspace_bytes(const tsb200_linear_desc* gate, const tsb200_linear_desc* up,
+                                        const tsb200_linear_desc* down, int64_t M) {
+  if (!gate || !up || !down || M <= 0) return tc::kWsHeader;
+  const size_t elt = gate->act_dtype == TSB200_F32 ? 4 : 2;
+  size_t b = region0_bytes(gate, up, down, M);
+  b += 3 * align256((size_t)M * (size_t)gate->out_features * elt);
+  b += 3 * align256((size_t)M * (size_t)(gate->rank > down->rank ? gate->rank : down->rank) * elt);
+  return b + 256;
 }
 
 int tsb200_mlp_gated(const tsb200_linear_desc* gate, const tsb200_linear_desc* up, const tsb200_linear_desc* down,
@@ -71,15 +82,15 @@ int tsb200_mlp_gated(const tsb200_linear_desc* gate, const tsb200_linear_desc* u
   cudaStream_t s = as_stream(stream);
   uint8_t* ws = (uint8_t*)workspace;
   const size_t elt = gate->act_dtype == TSB200_F32 ? 4 : 2;
+  const size_t r0 = region0_bytes(gate, up, down, M);
   const size_t inter_b = align256((size_t)M * (size_t)gate->out_features * elt);
   const size_t r_b = align256((size_t)M * (size_t)(gate->rank > down->rank ? gate->rank : down->rank) * elt);
-  uint8_t* buf_g = ws + tc::kWsHeader;          // gate out (composed path) / act (fused path)
+  uint8_t* buf_g = ws + r0;                     // gate out (composed path) / act (fused path)
   uint8_t* buf_u = buf_g + inter_b;
   uint8_t* buf_a = buf_u + inter_b;
   uint8_t* h0 = buf_a + inter_b;
   uint8_t* h1 = h0 + r_b;
   uint8_t* h2 = h1 + r_b;
-  uint8_t* tail = h2 + r_b;                     // split-K scratch (fused) or nested linear workspace (composed)
 
   if (fusable(gate, up, down, M)) {
     PhaseSpec ps[4];
@@ -111,19 +122,19 @@ int tsb200_mlp_gated(const tsb200_linear_desc* gate, const tsb200_linear_desc* u
       ps[n].g[0] = GemmSpec{down->u, down->u_scale, down->bias, buf_g, y, down->out_features, down->in_features};
       ++n;
     }
-    const int st = run_program_tcq(ps, n, gate->u_bits, M, tail, (int*)(ws + tc::kWsCounters), (int*)(ws + tc::kWsGridBar), (int*)ws, s);
+    const int st = run_program_tcq(ps, n, gate->u_bits, M, ws + tc::kWsHeader, (int*)(ws + tc::kWsCounters),
+                                   (int*)(ws + tc::kWsGridBar), (int*)ws, s);
     if (st != TSB200_ERR_UNSUPPORTED) return st;
   }
-  // composed path: three linear calls and the SwiGLU kernel; `tail` is their (zero-headed) workspace
-  const size_t tail_bytes = workspace_bytes - (size_t)(tail - ws);
-  int st = tsb200_linear(gate, x, buf_g, M, tail, tail_bytes, stream);
+  // composed path: three linear calls and the SwiGLU kernel; region 0 is their workspace
+  int st = tsb200_linear(gate, x, buf_g, M, ws, r0, stream);
   if (st != TSB200_OK) return st;
-  st = tsb200_linear(up, x, buf_u, M, tail, tail_bytes, stream);
+  st = tsb200_linear(up, x, buf_u, M, ws, r0, stream);
   if (st != TSB200_OK) return st;
   const int64_t inter = gate->out_features;
   st = tsb200_swiglu(buf_g, buf_u, buf_a, gate->act_dtype, M, inter, inter, inter, inter, stream);
   if (st != TSB200_OK) return st;
-  return tsb200_linear(down, buf_a, y, M, tail, tail_bytes, stream);
+  return tsb200_linear(down, buf_a, y, M, ws, r0, stream);
 }
 
 }  // extern "C"
