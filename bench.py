@@ -44,6 +44,12 @@ def parse():
     ap.add_argument("--rank", type=int, default=1024, help="LRD rank of the MLP linears")
     ap.add_argument("--wbits", type=int, default=4)
     ap.add_argument("--kv", default="fp8")
+    ap.add_argument("--sweep", default=None, choices=["linear", "attention"],
+                    help="op-level sweeps (BASELINE.json configs[1] / configs[2]) instead of the decode step; "
+                         "prints one JSON line per case")
+    ap.add_argument("--sweep-m", default="1,16,128,2048", help="token counts of the linear sweep")
+    ap.add_argument("--sweep-ctx", default="4096,16384,32768", help="contexts of the attention sweep")
+    ap.add_argument("--sweep-batch", type=int, default=64)
     return ap.parse_args()
 
 
@@ -353,9 +359,112 @@ def run_ours(a):
         dist.destroy_process_group()
 
 
+def _graph_time_us(fn, copies, reps=5):
+    """Average time of fn(i), i = 0..copies-1, replayed from one CUDA graph (CUDA events)."""
+    import torch
+    for i in range(min(2, copies)):
+        fn(i)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        for i in range(copies):
+            fn(i)
+    g.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        g.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) * 1000.0 / (reps * copies)
+
+
+def sweep_linear(a):
+    """configs[1]: x [M, 4096] bf16, W 4096x4096 factored at r in {256, 1024}, factors at 8 / 4 bits and
+    binary; time of LinearCompressed.forward per call, TFLOP/s and GB/s against the measured peaks."""
+    import torch
+    from transformer_surgeon_b200 import ops
+    dev = torch.device("cuda", 0)
+    g = torch.Generator(device=dev).manual_seed(2)
+    peak_bw, _ = peaks()
+    for r in (256, 1024):
+        for p in (8, 4, "binary"):
+            n_copies = 8          # distinct weight copies: 8 x (r x 8192 codes) > L2 only for the larger cases; stated per line
+            lins = []
+            for _ in range(n_copies):
+                U = (torch.randn((4096, r), generator=g, device=dev) * 0.02).bfloat16()
+                V = (torch.randn((r, 4096), generator=g, device=dev) * 0.02).bfloat16()
+                lins.append(ops.PackedLinear(ops.Factor.quantize(U, p), ops.Factor.quantize(V, p), None, torch.bfloat16))
+            bits = lins[0].u.bits
+            for M in [int(v) for v in a.sweep_m.split(",")]:
+                x = torch.randn((M, 4096), generator=g, device=dev).bfloat16()
+                y = torch.empty((M, 4096), dtype=torch.bfloat16, device=dev)
+                ws = torch.zeros(lins[0].workspace_bytes(M), dtype=torch.uint8, device=dev)
+                us = _graph_time_us(lambda i: lins[i](x, out=y, ws=ws), n_copies)
+                flops = 2.0 * M * r * 8192
+                byts = r * 8192 * bits / 8 + (4096 + r) * 4 + 2 * M * 4096 * 2
+                print(json.dumps({"sweep": "linear", "M": M, "rank": r, "precision": p, "container_bits": bits,
+                                  "us_per_call": us, "tflops": flops / us / 1e6, "gbs": byts / us / 1e3,
+                                  "frac_hbm": byts / us / 1e3 / peak_bw, "frac_tensor_burst": flops / us / 1e6 / 1671.9,
+                                  "weights_mb_cycled": n_copies * r * 8192 * bits / 8 / 1e6}))
+
+
+def sweep_attention(a):
+    """configs[2]: 32 q heads / 8 kv heads / d 128, batch 64, page 16, seeded random block table, K/V
+    N(0,1) with 4 outlier channels per head (x20); decode attention and single-token append per format."""
+    import torch
+    from transformer_surgeon_b200 import ops
+    dev = torch.device("cuda", 0)
+    g = torch.Generator(device=dev).manual_seed(3)
+    peak_bw, _ = peaks()
+    B, H, Hkv, d = a.sweep_batch, 32, 8, 128
+    outl = torch.ones((Hkv, d), device=dev)
+    for h in range(Hkv):
+        outl[h, torch.randperm(d, generator=g, device=dev)[:4]] = 20.0
+    for L in [int(v) for v in a.sweep_ctx.split(",")]:
+        for fmt in ("int8", "fp8", "nvfp4"):
+            pages = L // 16 + 1
+            rec = ops.kv_record_bytes(ops.KV_FORMATS[fmt], d)
+            layers = max(1, min(4, int(3e9 // (B * pages * Hkv * rec * 2))))     # a few GB on the device at most
+            kvs = []
+            seq = torch.zeros(B, dtype=torch.int32, device=dev)
+            bt = torch.randperm(B * pages, generator=g, device=dev).to(torch.int32).reshape(B, pages)
+            for _ in range(layers):
+                kv = ops.PagedKV(fmt, B * pages, Hkv, d, bt, seq, dev)
+                if fmt == "fp8":
+                    kv.k_scale.fill_(110.0 / 448)
+                    kv.v_scale.fill_(110.0 / 448)
+                seq.zero_()
+                for t0 in range(0, L, 1024):
+                    n = min(1024, L - t0)
+                    k = (torch.randn((B, n, Hkv, d), generator=g, device=dev) * outl).bfloat16()
+                    v = (torch.randn((B, n, Hkv, d), generator=g, device=dev) * outl).bfloat16()
+                    kv.append(k, v)
+                    seq += n
+                kvs.append(kv)
+            q = torch.randn((B, H, d), generator=g, device=dev).bfloat16()
+            out = torch.empty_like(q)
+            ws = torch.zeros(ops.decode_attn_workspace_bytes(B, H, d, L + 16), dtype=torch.uint8, device=dev)
+            us = _graph_time_us(lambda i: ops.paged_decode_attention(kvs[i], q, L + 16, out=out, ws=ws), layers, reps=4)
+            byts = B * (L // 16) * Hkv * rec * 2 + B * (L // 16) * 4 + 2 * B * H * d * 2
+            k1 = torch.randn((B, 1, Hkv, d), generator=g, device=dev).bfloat16()
+            us_app = _graph_time_us(lambda i: kvs[i].append(k1, k1), layers, reps=4)
+            app_bytes = B * 2 * Hkv * d * (2 + rec / (16.0 * d))
+            print(json.dumps({"sweep": "attention", "format": fmt, "batch": B, "context": L, "decode_us": us,
+                              "decode_gbs": byts / us / 1e3, "decode_frac_hbm": byts / us / 1e3 / peak_bw,
+                              "pages_mb": byts / 1e6, "append_us": us_app, "append_gbs": app_bytes / us_app / 1e3,
+                              "layers_cycled": layers}))
+            del kvs
+
+
 if __name__ == "__main__":
     args = parse()
-    if args.impl == "reference":
+    if args.sweep:
+        import torch
+        torch.cuda.set_device(0)
+        (sweep_linear if args.sweep == "linear" else sweep_attention)(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)

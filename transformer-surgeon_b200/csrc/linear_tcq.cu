@@ -428,7 +428,7 @@ linear_tcq_kernel(const __grid_constant__ Program prog) {
                   // same rounding points as separate gate / up / SiLU*up kernels (blocks/mlp.py:181-183)
                   const float g = __bfloat162float(__float2bfloat16_rn(__uint_as_float(r[j]) * sc0 + bv0));
                   const float u = __bfloat162float(__float2bfloat16_rn(__uint_as_float(r2[j]) * sc1 + bv1));
-                  const float a = __bfloat162float(__float2bfloat16_rn(g / (1.0f + expf(-g))));
+                  const float a = __bfloat162float(__float2bfloat16_rn(__fdividef(g, 1.0f + __expf(-g))));
                   y[m * ph.N + n] = __float2bfloat16_rn(__fmul_rn(a, u));
                 }
               }
