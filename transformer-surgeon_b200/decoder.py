@@ -35,6 +35,8 @@ class DecoderConfig:
     dtype: torch.dtype = torch.bfloat16
     kv_format: str = "fp8"         # int8 | fp8 | nvfp4 | fp32 | bf16
     max_positions: int = 4096
+    tp_world: int = 1              # tensor-parallel group size (1 = none); num_heads / num_kv_heads are GLOBAL
+    tp_rank: int = 0
 
 
 class LayerWeights:
@@ -73,20 +75,26 @@ def rope_tables(head_dim, theta, max_positions, device):
 
 
 class CompressedDecoder:
-    def __init__(self, cfg, embed, layers, final_norm, lm_head, batch, max_seq_len, device):
+    def __init__(self, cfg, embed, layers, final_norm, lm_head, batch, max_seq_len, device, tp_group=None):
         self.cfg, self.embed, self.layers, self.final_norm, self.lm_head = cfg, embed, layers, final_norm, lm_head
         self.B, self.max_seq_len, self.device = batch, max_seq_len, device
+        self.tp_group = tp_group
         c = cfg
+        if c.tp_world > 1:
+            if c.num_heads % c.tp_world or c.num_kv_heads % c.tp_world:
+                raise ValueError("heads must split evenly over the tensor-parallel ranks")
+            layers = self.layers = [self._shard_layer(L, c) for L in layers]
+        self.H_local, self.Hkv_local = c.num_heads // c.tp_world, c.num_kv_heads // c.tp_world
         self.pages_per_seq = (max_seq_len + ops.PAGE - 1) // ops.PAGE
         num_pages = batch * self.pages_per_seq
         # sequence-major ascending page allocation: reproducible block tables
         self.block_table = torch.arange(num_pages, dtype=torch.int32, device=device).reshape(batch, self.pages_per_seq)
         self.seq_lens = torch.zeros(batch, dtype=torch.int32, device=device)    # tokens in cache (after this step's append)
         self.write_pos = torch.zeros(batch, dtype=torch.int32, device=device)   # position of the token being appended
-        self.kv = [ops.PagedKV(c.kv_format, num_pages, c.num_kv_heads, c.head_dim, self.block_table, self.seq_lens, device)
+        self.kv = [ops.PagedKV(c.kv_format, num_pages, self.Hkv_local, c.head_dim, self.block_table, self.seq_lens, device)
                    for _ in range(c.num_layers)]
         self.cos, self.sin = rope_tables(c.head_dim, c.rope_theta, c.max_positions, device)
-        H, Hkv, d = c.num_heads, c.num_kv_heads, c.head_dim
+        H, Hkv, d = self.H_local, self.Hkv_local, c.head_dim
         dt = c.dtype
         B = batch
         # persistent activation buffers (stable addresses -> the step can be captured in a CUDA graph)
@@ -113,10 +121,28 @@ class CompressedDecoder:
         self.graph = None
         self.kernel_launches_per_step = 0
 
+    @staticmethod
+    def _shard_layer(L, c):
+        """Tensor-parallel shard of one layer: q/k/v/gate/up column-parallel, o/down row-parallel."""
+        from . import tensor_parallel as tp
+        w, r, d = c.tp_world, c.tp_rank, c.head_dim
+        if L.qkv is not None:
+            raise ValueError("build tensor-parallel engines with separate q/k/v projections (fuse_qkv=False)")
+        q, k, v = (tp.column_parallel(x, w, r, d) for x in (L.q, L.k, L.v))
+        qkv = None
+        if not (q.rank or k.rank or v.rank):
+            qkv = fuse_rows([q.u, k.u, v.u], [q.bias, k.bias, v.bias], c.dtype)
+        return LayerWeights(L.ln1, L.ln2, tp.row_parallel(L.o, w, r, d), tp.column_parallel(L.gate, w, r),
+                            tp.column_parallel(L.up, w, r), tp.row_parallel(L.down, w, r), qkv=qkv,
+                            q=None if qkv else q, k=None if qkv else k, v=None if qkv else v)
+
     # ------------------------------------------------------------------ one decode step
     def _step_kernels(self):
         c = self.cfg
-        B, H, Hkv, d = self.B, c.num_heads, c.num_kv_heads, c.head_dim
+        B, H, Hkv, d = self.B, self.H_local, self.Hkv_local, c.head_dim
+        tp_on = c.tp_world > 1
+        if tp_on:
+            from .tensor_parallel import all_reduce_sum
         n = 0
         torch.index_select(self.embed, 0, self.tokens, out=self.resid)
         self.write_pos.copy_(self.seq_lens)
@@ -140,8 +166,12 @@ class CompressedDecoder:
             ops.paged_decode_attention(self.kv[li], q4[:, 0], self.max_seq_len, out=self.attn.view(B, H, d),
                                        ws=self.attn_ws, seq_lens=self.seq_lens); n += 2
             L.o(self.attn, out=self.delta, ws=self.lin_ws); n += 1
+            if tp_on:
+                all_reduce_sum(self.delta, self.tp_group)       # row-parallel o_proj: sum of the partial outputs
             ops.add_rmsnorm(self.resid, self.delta, L.ln2, c.rms_eps, c.norm_variant, out=self.xn); n += 1
             L.mlp(self.xn, out=self.delta, ws=self.mlp_ws); n += 1
+            if tp_on:
+                all_reduce_sum(self.delta, self.tp_group)       # row-parallel down_proj
             delta = self.delta
         ops.add_rmsnorm(self.resid, delta, self.final_norm, c.rms_eps, c.norm_variant, out=self.xn); n += 1
         self.lm_head(self.xn, out=self.logits, ws=self.lin_ws); n += 1

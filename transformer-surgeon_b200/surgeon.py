@@ -53,7 +53,7 @@ def pack_linear(weight, v_weight=None, bias=None, quant=None, dtype=None, device
 
 
 def decoder_from_state_dict(sd, cfg, compression_config=None, batch=1, max_seq_len=256, device="cuda",
-                            prefix="model.", fuse_qkv=True):
+                            prefix="model.", fuse_qkv=True, tp_group=None):
     """sd: state dict of a Qwen2/Llama `*ForCausalLMCompress` (keys `model.layers.N.<linear>.weight`,
     `.linear_V.weight`, `.bias`, norms, `model.embed_tokens.weight`, `lm_head.weight`)."""
     dt = cfg.dtype
@@ -70,7 +70,7 @@ def decoder_from_state_dict(sd, cfg, compression_config=None, batch=1, max_seq_l
         L = {name: lin(base + name) for name in BLOCK_LINEARS}
         q, k, v = L["self_attn.q_proj"], L["self_attn.k_proj"], L["self_attn.v_proj"]
         qkv = None
-        if fuse_qkv and not (q.rank or k.rank or v.rank):
+        if fuse_qkv and cfg.tp_world == 1 and not (q.rank or k.rank or v.rank):
             qkv = fuse_rows([q.u, k.u, v.u], [q.bias, k.bias, v.bias], dt)
         ln1 = sd[base + "input_layernorm.weight"].to(device=dev, dtype=dt).contiguous()
         ln2 = sd[base + "post_attention_layernorm.weight"].to(device=dev, dtype=dt).contiguous()
@@ -82,7 +82,7 @@ def decoder_from_state_dict(sd, cfg, compression_config=None, batch=1, max_seq_l
     lm_head = pack_linear(sd[head_key], sd.get("lm_head.linear_V.weight"), sd.get("lm_head.bias"),
                           _quant_of(compression_config, "lm_head"), dt, dev)
     norm = sd[prefix + "norm.weight"].to(device=dev, dtype=dt).contiguous()
-    return CompressedDecoder(cfg, embed, layers, norm, lm_head, batch, max_seq_len, dev)
+    return CompressedDecoder(cfg, embed, layers, norm, lm_head, batch, max_seq_len, dev, tp_group=tp_group)
 
 
 def decoder_config_from_hf(config, kv_format="fp8", dtype=None, max_positions=None):
