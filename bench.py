@@ -44,6 +44,9 @@ def parse():
     ap.add_argument("--rank", type=int, default=1024, help="LRD rank of the MLP linears")
     ap.add_argument("--wbits", type=int, default=4)
     ap.add_argument("--kv", default="fp8")
+    ap.add_argument("--parallel", default="replica", choices=["replica", "tp"],
+                    help="N > 1: independent replicas (sequences sharded, no collective; the default the scaling run uses) "
+                         "or tensor-parallel linears with an NCCL all-reduce (one batch shared by all ranks)")
     ap.add_argument("--sweep", default=None, choices=["linear", "attention"],
                     help="op-level sweeps (BASELINE.json configs[1] / configs[2]) instead of the decode step; "
                          "prints one JSON line per case")
@@ -109,14 +112,14 @@ def algorithmic_bytes(a, context):
     return a.layers * (attn_w + mlp_w + kv) + lm, a.batch * context * 2 * Hkv * d * kv_elem
 
 
-def build_engine(a, device, seed):
+def build_engine(a, device, seed, tp_world=1, tp_rank=0):
     import torch
     from transformer_surgeon_b200 import ops
     from transformer_surgeon_b200.decoder import CompressedDecoder, DecoderConfig, LayerWeights, fuse_rows
     c = dict(LLAMA3_8B)
     c["num_layers"] = a.layers
     max_seq = a.context + a.steps + a.warmup + 16
-    cfg = DecoderConfig(dtype=torch.bfloat16, kv_format=a.kv, max_positions=max_seq + 16, **c)
+    cfg = DecoderConfig(dtype=torch.bfloat16, kv_format=a.kv, max_positions=max_seq + 16, tp_world=tp_world, tp_rank=tp_rank, **c)
     g = torch.Generator(device=device).manual_seed(seed)
     dt = torch.bfloat16
     H, Hkv, d, hid, inter = cfg.num_heads, cfg.num_kv_heads, cfg.head_dim, cfg.hidden, cfg.intermediate
@@ -132,16 +135,23 @@ def build_engine(a, device, seed):
 
     layers = []
     for _ in range(a.layers):
-        qkv = fuse_rows([qfactor(H * d, hid, 0.02), qfactor(Hkv * d, hid, 0.02), qfactor(Hkv * d, hid, 0.02)], [None] * 3, dt)
+        fq, fk, fv = qfactor(H * d, hid, 0.02), qfactor(Hkv * d, hid, 0.02), qfactor(Hkv * d, hid, 0.02)
         o = ops.PackedLinear(qfactor(hid, H * d, 0.02), None, None, dt)
         ones = torch.ones(hid, dtype=dt, device=device)
-        layers.append(LayerWeights(ones, ones.clone(), o, lrd(inter, hid), lrd(inter, hid), lrd(hid, inter), qkv=qkv))
+        if tp_world > 1:     # the engine shards q/k/v/o/gate/up/down itself (and fuses the local q|k|v again)
+            mk = lambda f: ops.PackedLinear(f, None, None, dt)
+            layers.append(LayerWeights(ones, ones.clone(), o, lrd(inter, hid), lrd(inter, hid), lrd(hid, inter),
+                                       q=mk(fq), k=mk(fk), v=mk(fv)))
+        else:
+            layers.append(LayerWeights(ones, ones.clone(), o, lrd(inter, hid), lrd(inter, hid), lrd(hid, inter),
+                                       qkv=fuse_rows([fq, fk, fv], [None] * 3, dt)))
     embed = rnd(cfg.vocab, hid, 0.02)
     lm_head = ops.PackedLinear(ops.Factor.dense(rnd(cfg.vocab, hid, 0.02)), None, None, dt)
     dec = CompressedDecoder(cfg, embed, layers, torch.ones(hid, dtype=dt, device=device), lm_head, a.batch, max_seq, device)
     # synthetic prompt KV of the benchmark's shape: N(0,1) with 4 outlier channels per head (x20)
     B = a.batch
     chunk = 512
+    Hkv = dec.Hkv_local
     outl = torch.ones((Hkv, d), device=device)
     for h in range(Hkv):
         outl[h, torch.randperm(d, generator=g, device=device)[:4]] = 20.0
@@ -275,10 +285,12 @@ def run_ours(a):
     import __graft_entry__ as ge
     if not os.path.exists(os.path.join(ROOT, "transformer-surgeon_b200", "libtsb200.so")):
         ge.build()
-    dec = build_engine(a, device, seed=1 + rank)
+    tp = a.parallel == "tp" and world > 1
+    dec = build_engine(a, device, seed=1 if tp else 1 + rank, tp_world=world if tp else 1, tp_rank=rank if tp else 0)
     dec.capture()
     B = a.batch
-    tok_host = torch.randint(0, dec.cfg.vocab, (B,), dtype=torch.int64).pin_memory()
+    tgen = torch.Generator().manual_seed(7 if tp else 7 + rank)     # tensor parallel: every rank feeds the same tokens
+    tok_host = torch.randint(0, dec.cfg.vocab, (B,), generator=tgen, dtype=torch.int64).pin_memory()
     out_host = torch.empty(B, dtype=torch.int64).pin_memory()
 
     def barrier():
@@ -329,16 +341,18 @@ def run_ours(a):
         step_bytes, attn_bytes = algorithmic_bytes(a, ctx_mid)
         attn_alg = algorithmic_bytes(a, int(dec.seq_lens[0].item()))[1]
         achieved = attn_alg / (t_attn * 1e-3) / 1e9
-        tps = world * B * a.steps / (ms * 1e-3)
+        seqs = B if tp else world * B                  # tensor parallel: one batch shared by all ranks
+        tps = seqs * a.steps / (ms * 1e-3)
         line = {"metric": METRIC, "value": tps, "unit": "tokens/s", "n_gpus": world, "steps": a.steps, "warmup": a.warmup,
-                "ms_per_step": ms / a.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+                "ms_per_step": ms / a.steps, "higher_is_better": True, "scaling": "strong" if tp else "weak", "vs_baseline": None,
                 "dtype": "bf16", "data": "synthetic",
                 "config": {"workload": "llama3-8b-arch decode: %d layers, MLP LRD r=%d, W%d per-channel, %s paged KV, "
                            "batch %d/GPU, context %d->%d" % (a.layers, a.rank, a.wbits, a.kv, B, ctx0, ctx0 + a.steps),
-                           "sharding": "replicas, %d sequences per GPU, no collective" % B,
+                           "sharding": ("tensor parallel x%d: heads / MLP columns split, 2 NCCL all-reduces per layer, batch %d shared" % (world, B))
+                           if tp else "replicas, %d sequences per GPU, no collective" % B,
                            "l2": "inputs larger than L2 (%.1f GB read per step)" % (step_bytes / 1e9),
                            "cuda_graph": True},
-                "e2e": {"value": world * B * a.steps / (ms_e2e * 1e-3), "unit": "tokens/s",
+                "e2e": {"value": seqs * a.steps / (ms_e2e * 1e-3), "unit": "tokens/s",
                         "h2d_bytes_per_step": B * 8, "d2h_bytes_per_step": B * 8},
                 "gpu_launches": dec.kernel_launches_per_step * a.steps,
                 "clocks": clocks,
