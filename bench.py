@@ -178,7 +178,7 @@ def time_attention_kernel(dec, a, reps=5):
     import torch
     from transformer_surgeon_b200 import ops
     c = dec.cfg
-    q = torch.randn((dec.B, c.num_heads, c.head_dim), device=dec.device).to(c.dtype)
+    q = torch.randn((dec.B, dec.H_local, c.head_dim), device=dec.device).to(c.dtype)
     out = torch.empty_like(q)
     for kv in dec.kv[:2]:
         ops.paged_decode_attention(kv, q, dec.max_seq_len, out=out, ws=dec.attn_ws)
