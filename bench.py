@@ -373,6 +373,13 @@ def run_ours(a):
             line["cpu_baseline"] = {"value": None, "error": repr(ex)}
         print(json.dumps(line))
     if world > 1:
+        if tp:
+            # the captured step holds NCCL work: drop the graph and leave without tearing the communicator
+            # down (destroying the group with a live graph has been seen to block at exit)
+            dec.graph = None
+            torch.cuda.synchronize()
+            sys.stdout.flush()
+            os._exit(0)
         dist.destroy_process_group()
 
 
