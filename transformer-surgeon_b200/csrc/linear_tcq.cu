@@ -157,13 +157,24 @@ __device__ __forceinline__ bool warps_rendezvous(unsigned long long* bar, int& u
 }
 
 
-// Optional phase trace (compile with -DTSB_TRACE): CTA 0 stores clock64 stamps in bytes 128.. of the
-// workspace header.
+// Optional phase trace (compile with -DTSB_TRACE): CTA 0 stores clock64 stamps in the last 512 bytes
+// of the workspace header (split counters that far up are not in use at traced sizes).
 #ifdef TSB_TRACE
-#define TSB_STAMP(i) do { if (blockIdx.x == 0) reinterpret_cast<long long*>(reinterpret_cast<char*>(prog.status) + 128)[i] = clock64(); } while (0)
+__device__ long long g_trace[160 * 32 * 2];     // per CTA: 32 slots of {clock64, globaltimer}
+__device__ __forceinline__ void trace_stamp(int i) {
+  if (blockIdx.x < 160 && i < 32) {
+    unsigned long long gt;
+    asm volatile("mov.u64 %0, %globaltimer;\n" : "=l"(gt));
+    g_trace[(blockIdx.x * 32 + i) * 2] = clock64();
+    g_trace[(blockIdx.x * 32 + i) * 2 + 1] = (long long)gt;
+  }
+}
+#define TSB_STAMP(i) do { if (blockIdx.x == 0) reinterpret_cast<long long*>(reinterpret_cast<char*>(prog.status) + kWsHeader - 512)[i] = clock64(); trace_stamp(i); } while (0)
 #else
 #define TSB_STAMP(i) do { } while (0)
 #endif
+// per-phase stamps of CTA 0: slot 8 + 4 * phase + k
+#define TSB_STAMP_P(p, k) TSB_STAMP(8 + 4 * (p) + (k))
 
 constexpr int kMaxPhases = 4;
 
@@ -184,6 +195,9 @@ struct Phase {
   int n_tiles, m_tiles, items_per_sub, items;
   float* partial;                // split-K: fp32 slices [items][TN][128] of this phase
   int* counters;                 // split-K: zero-filled int32 [nsub * n_tiles * m_tiles], left zero
+  int scatter;                   // split-K: 1 = every CTA holds at most one item of the phase and all CTAs are
+                                 //    co-resident, so the CTAs of a tile wait for one another and each sums its
+                                 //    share of the tile's columns; 0 = the last CTA to arrive sums the whole tile
 };
 struct Program {
   int64_t M;
@@ -212,14 +226,14 @@ linear_tcq_kernel(const __grid_constant__ Program prog) {
   using L = QLayout<TN, BITS>;
   constexpr int NR = L::NR;
   constexpr int KBS = L::KBS;
-  constexpr unsigned TX_BYTES = (unsigned)L::kStage;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint8_t* r_ring = smem;                                   // NR x {KBS activation tiles, raw codes}
   unsigned long long* bars = reinterpret_cast<unsigned long long*>(r_ring + NR * L::kStage);
-  unsigned long long* raw_full = bars;                      // [NR] TMA landed
-  unsigned long long* raw_empty = bars + NR;                // [NR] 4 dequant warps of the owning group + MMA commit
-  unsigned long long* a_ready = bars + 2 * NR;              // [2]  4 dequant warps: A buffer stored in TMEM
+  unsigned long long* w_full = bars;                        // [NR] weight box landed (the dequant warps wait on it)
+  unsigned long long* x_full = bars + NR;                   // [NR] activation tiles landed (the MMA lane waits on it)
+  unsigned long long* raw_empty = bars + 2 * NR;            // [NR] 4 dequant warps of the owning group + MMA commit
+  unsigned long long* a_ready = bars + 3 * NR;              // [2]  4 dequant warps: A buffer stored in TMEM
   unsigned long long* a_empty = a_ready + 2;                // [2]  MMA commit: A buffer consumed
   unsigned long long* acc_full = a_empty + 2;               // [1]  MMA commit: accumulator(s) of the item complete
   unsigned long long* ep_bar = acc_full + 1;                // [1]  rendezvous of the 8 warps
@@ -231,7 +245,7 @@ linear_tcq_kernel(const __grid_constant__ Program prog) {
   pdl_launch_dependents();
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < NR; ++i) { mbar_init(&raw_full[i], 1); mbar_init(&raw_empty[i], 4 + 1); }
+    for (int i = 0; i < NR; ++i) { mbar_init(&w_full[i], 1); mbar_init(&x_full[i], 1); mbar_init(&raw_empty[i], 4 + 1); }
     for (int i = 0; i < 2; ++i) { mbar_init(&a_ready[i], 4); mbar_init(&a_empty[i], 1); }
     mbar_init(acc_full, 1);
     mbar_init(ep_bar, kDqWarps);
@@ -266,17 +280,23 @@ linear_tcq_kernel(const __grid_constant__ Program prog) {
   if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer
     if (lane == 0) {
-      for (int p = 0; p < prog.n_phases; ++p)
-        for (int j = 0; j < prog.ph[p].nsub; ++j) {
-          asm volatile("prefetch.tensormap [%0];\n" ::"l"(&prog.ph[p].sub[j].map_w) : "memory");
-          asm volatile("prefetch.tensormap [%0];\n" ::"l"(&prog.ph[p].sub[j].map_x) : "memory");
-        }
+      // descriptor prefetches cost ~130 cycles each on this lane: a phase's descriptors are requested
+      // right after the first weight boxes of the phase BEFORE it are in flight
+      auto prefetch_maps = [&](int p) {
+        if (p < prog.n_phases)
+          for (int j = 0; j < prog.ph[p].nsub; ++j) {
+            asm volatile("prefetch.tensormap [%0];\n" ::"l"(&prog.ph[p].sub[j].map_w) : "memory");
+            asm volatile("prefetch.tensormap [%0];\n" ::"l"(&prog.ph[p].sub[j].map_x) : "memory");
+          }
+      };
       // The packed weights are constants: for the first NR stages of a phase their boxes are
       // requested BEFORE the phase's activations exist (before the wait on the preceding kernel
-      // for phase 0, before the grid barrier for later phases); the activation tiles follow.
+      // for phase 0, before the grid barrier for later phases); the activation tiles follow.  The
+      // two kinds of data complete separate barriers, so the dequant warps already fill both A
+      // buffers of the next phase while the barrier is pending.
       bool ok = true;
       int gs_phase0 = 0;                                      // stage counter at the start of the phase
-      auto walk = [&](const Phase& ph, int rel_begin, int rel_end, bool do_w, bool do_x, bool arm) -> int {
+      auto walk = [&](const Phase& ph, int rel_begin, int rel_end, bool do_w, bool do_x) -> int {
         int gs = gs_phase0;                                   // absolute stage counter
         for (int item = blockIdx.x; item < ph.items && ok; item += gridDim.x) {
           const Item it = decode(ph, item);
@@ -288,16 +308,19 @@ linear_tcq_kernel(const __grid_constant__ Program prog) {
               if (rel >= rel_end) return gs;
               if (rel < rel_begin) continue;
               const int s = gs % NR;
-              if (arm && gs >= NR && !mbar_wait(&raw_empty[s], ((gs / NR) - 1) & 1, abort_flag, 1)) { ok = false; return gs; }
               uint8_t* st = r_ring + s * L::kStage;
-              if (arm) mbar_expect_tx(&raw_full[s], TX_BYTES);
               const int kcol = (it.kb0 + i) * BK;
+              if (do_w) {                                     // the stage is free once its previous user is done
+                if (gs >= NR && !mbar_wait(&raw_empty[s], ((gs / NR) - 1) & 1, abort_flag, 1)) { ok = false; return gs; }
+                mbar_expect_tx(&w_full[s], (unsigned)L::kRaw);
+                tma_load_2d(st + L::kX, &sg.map_w, kcol * BITS / 8, it.nt * BM, &w_full[s]);
+              }
               if (do_x) {
+                mbar_expect_tx(&x_full[s], (unsigned)L::kX);
 #pragma unroll
                 for (int j = 0; j < KBS; ++j)                 // columns beyond K are zero-filled by the copy engine
-                  tma_load_2d(st + j * L::kXTile, &sg.map_x, kcol + j * BK, it.mt * TN, &raw_full[s]);
+                  tma_load_2d(st + j * L::kXTile, &sg.map_x, kcol + j * BK, it.mt * TN, &x_full[s]);
               }
-              if (do_w) tma_load_2d(st + L::kX, &sg.map_w, kcol * BITS / 8, it.nt * BM, &raw_full[s]);
               if (gs == 0 && do_w) TSB_STAMP(1);
             }
           }
@@ -306,7 +329,9 @@ linear_tcq_kernel(const __grid_constant__ Program prog) {
       };
       for (int p = 0; p < prog.n_phases && ok; ++p) {
         const Phase& ph = prog.ph[p];
-        walk(ph, 0, NR, true, false, true);
+        walk(ph, 0, NR, true, false);
+        TSB_STAMP_P(p, 0);
+        prefetch_maps(p + 1);
         if (p == 0) {
           pdl_wait();
         } else {
@@ -314,8 +339,9 @@ linear_tcq_kernel(const __grid_constant__ Program prog) {
           asm volatile("fence.proxy.async;\n" ::: "memory");  // other CTAs' stores -> visible to the copy engine
         }
         if (!ok) break;
-        walk(ph, 0, NR, false, true, false);
-        gs_phase0 = walk(ph, NR, 0x7fffffff, true, true, true);
+        TSB_STAMP_P(p, 1);
+        walk(ph, 0, NR, false, true);
+        gs_phase0 = walk(ph, NR, 0x7fffffff, true, true);
         if (gs_phase0 < 0) break;
       }
     }
@@ -334,7 +360,7 @@ linear_tcq_kernel(const __grid_constant__ Program prog) {
             const unsigned d_tmem = tmem_base + ps * TN;      // gated: gate -> columns [0, TN), up -> [TN, 2 TN)
             for (int i = 0; i < it.nkb; i += KBS, ++gs) {
               const int s = gs % NR, buf = gs & 1;
-              ok = mbar_wait(&raw_full[s], (gs / NR) & 1, abort_flag, 2) && mbar_wait(&a_ready[buf], (gs >> 1) & 1, abort_flag, 3);
+              ok = mbar_wait(&x_full[s], (gs / NR) & 1, abort_flag, 2) && mbar_wait(&a_ready[buf], (gs >> 1) & 1, abort_flag, 3);
               if (!ok) break;
               tc_fence_after();
               const unsigned a_tmem = tmem_base + kACol0 + buf * 128;
@@ -382,7 +408,7 @@ linear_tcq_kernel(const __grid_constant__ Program prog) {
           for (int i = 0; i < it.nkb; i += KBS, ++gs) {
             if ((gs & 1) != grp) continue;
             const int s = gs % NR, buf = gs & 1;
-            ok = mbar_wait(&raw_full[s], (gs / NR) & 1, abort_flag, 4);
+            ok = mbar_wait(&w_full[s], (gs / NR) & 1, abort_flag, 4);
             if (ok && gs >= 2) ok = mbar_wait(&a_empty[buf], ((gs >> 1) - 1) & 1, abort_flag, 5);
             if (!ok) break;
             if (gs == 0 && threadIdx.x == 64) TSB_STAMP(2);
@@ -398,7 +424,7 @@ linear_tcq_kernel(const __grid_constant__ Program prog) {
             tc_fence_before();
             __syncwarp();
             if (lane == 0) { mbar_arrive(&a_ready[buf]); mbar_arrive(&raw_empty[s]); }
-            if (threadIdx.x == 64) { if (gs == 0) TSB_STAMP(3); TSB_STAMP(4); }
+            if (threadIdx.x == 64) { if (gs == 0) TSB_STAMP(3); if (item == blockIdx.x && ps == 0 && i == 0) TSB_STAMP_P(p, 2); }
           }
         }
         if (!ok) break;
@@ -450,7 +476,43 @@ linear_tcq_kernel(const __grid_constant__ Program prog) {
         tc_fence_before();
         // every warp is done reading the accumulator before any warp stores the next item's A operand
         if (!(ok = warps_rendezvous(ep_bar, ep_uses, lane, abort_flag))) break;
-        if (split) {
+        if (split && ph.scatter) {
+          // The CTAs of this (matrix, n tile, m tile) meet at the tile's counter; CTA `sp` then sums token
+          // columns sp, sp + splits, ... over all slices in split order (the order the single-finalizer
+          // path uses), with every load of a column in flight at once.  The counter counts arrivals, then
+          // departures; the last CTA to leave resets it.
+          int* ctr = &ph.counters[(it.sub * ph.m_tiles + it.mt) * ph.n_tiles + it.nt];
+          __threadfence();
+          if (!(ok = warps_rendezvous(ep_bar, ep_uses, lane, abort_flag))) break;
+          if (threadIdx.x == 64) {
+            atomicAdd(ctr, 1);
+            grid_wait(ctr, ph.splits, abort_flag);             // failure raises the abort flag
+          }
+          if (!(ok = warps_rendezvous(ep_bar, ep_uses, lane, abort_flag))) break;
+          if (*abort_flag) { ok = false; break; }
+          __threadfence();
+          const int sp = item % ph.splits;
+          if (n < ph.N) {
+            const float* tile0 = ph.partial + (size_t)(item - sp) * (TN * BM) + row;
+            for (int c = sp + grp * ph.splits; c < TN; c += 2 * ph.splits) {
+              const int64_t m = m0 + c;
+              if (m >= prog.M) break;
+              float v = 0.f;
+              for (int s0 = 0; s0 < ph.splits; s0 += 8) {
+                float a[8];
+#pragma unroll
+                for (int u = 0; u < 8; ++u)
+                  if (s0 + u < ph.splits) a[u] = __ldcg(tile0 + (size_t)(s0 + u) * (TN * BM) + c * BM);
+#pragma unroll
+                for (int u = 0; u < 8; ++u)
+                  if (s0 + u < ph.splits) v += a[u];
+              }
+              y[m * ph.N + n] = __float2bfloat16_rn(v * sc0 + bv0);
+            }
+          }
+          if (!(ok = warps_rendezvous(ep_bar, ep_uses, lane, abort_flag))) break;   // this CTA's slice reads are done
+          if (threadIdx.x == 64 && atomicAdd(ctr, 1) == 2 * ph.splits - 1) *ctr = 0;
+        } else if (split) {
           // last CTA of this (matrix, n tile, m tile) finalizes: sum of the slices -> y, then resets the counter
           int* ctr = &ph.counters[(it.sub * ph.m_tiles + it.mt) * ph.n_tiles + it.nt];
           __threadfence();
@@ -502,6 +564,7 @@ linear_tcq_kernel(const __grid_constant__ Program prog) {
         if (threadIdx.x == 64) TSB_STAMP(6);
       }
       if (!ok) break;
+      if (threadIdx.x == 64) TSB_STAMP_P(p, 3);
       // ---- end of phase: publish this CTA's outputs, then signal the grid barrier ------------------
       if (p + 1 < prog.n_phases) {
         if (!waited) { pdl_wait(); waited = true; }
@@ -541,7 +604,7 @@ namespace tsb {
 namespace {
 
 template <int TN, int BITS>
-int launch_q(const Program& prog, int grid, cudaStream_t s) {
+int launch_q(const Program& prog, int grid, bool coresident, cudaStream_t s) {
   using L = QLayout<TN, BITS>;
   static bool configured[64] = {false};
   int dev = 0;
@@ -558,7 +621,7 @@ int launch_q(const Program& prog, int grid, cudaStream_t s) {
   cfg.stream = s;
   cudaLaunchAttribute attr[2];
   int na = 0;
-  if (prog.n_phases > 1) {     // grid barriers: every CTA must be resident at once
+  if (coresident) {            // grid barriers / tile rendezvous: every CTA must be resident at once
     attr[na].id = cudaLaunchAttributeCooperative;
     attr[na].val.cooperative = 1;
     ++na;
@@ -581,11 +644,11 @@ int launch_q(const Program& prog, int grid, cudaStream_t s) {
 }
 
 template <int TN>
-int launch_q_bits(int bits, const Program& prog, int grid, cudaStream_t s) {
+int launch_q_bits(int bits, const Program& prog, int grid, bool coresident, cudaStream_t s) {
   switch (bits) {
-    case 2: return launch_q<TN, 2>(prog, grid, s);
-    case 4: return launch_q<TN, 4>(prog, grid, s);
-    case 8: return launch_q<TN, 8>(prog, grid, s);
+    case 2: return launch_q<TN, 2>(prog, grid, coresident, s);
+    case 4: return launch_q<TN, 4>(prog, grid, coresident, s);
+    case 8: return launch_q<TN, 8>(prog, grid, coresident, s);
     default: return TSB200_ERR_UNSUPPORTED;
   }
 }
@@ -673,11 +736,17 @@ int run_program_tcq(const PhaseSpec* specs, int n_phases, int bits, int64_t M, u
   }
   const int sms = num_sms();
   const int grid = max_items < sms ? max_items : sms;
+  bool coresident = n_phases > 1;
+  for (int p = 0; p < n_phases; ++p) {
+    Phase& ph = prog.ph[p];
+    ph.scatter = (ph.splits > 1 && ph.items <= grid) ? 1 : 0;
+    coresident = coresident || ph.scatter;
+  }
   switch (tn) {
-    case 16: return launch_q_bits<16>(bits, prog, grid, s);
-    case 32: return launch_q_bits<32>(bits, prog, grid, s);
-    case 64: return launch_q_bits<64>(bits, prog, grid, s);
-    default: return launch_q_bits<128>(bits, prog, grid, s);
+    case 16: return launch_q_bits<16>(bits, prog, grid, coresident, s);
+    case 32: return launch_q_bits<32>(bits, prog, grid, coresident, s);
+    case 64: return launch_q_bits<64>(bits, prog, grid, coresident, s);
+    default: return launch_q_bits<128>(bits, prog, grid, coresident, s);
   }
 }
 
@@ -693,3 +762,9 @@ int gemm_tcq(const void* W, int bits, const float* scale, const void* bias, cons
 }
 
 }  // namespace tsb
+
+#ifdef TSB_TRACE
+extern "C" int tsb200_trace_read(void* host, size_t nbytes) {
+  return (int)cudaMemcpyFromSymbol(host, tsb::g_trace, nbytes < sizeof(tsb::g_trace) ? nbytes : sizeof(tsb::g_trace));
+}
+#endif
