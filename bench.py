@@ -29,6 +29,12 @@ if ROOT not in sys.path:
 
 LLAMA3_8B = dict(num_layers=32, hidden=4096, num_heads=32, num_kv_heads=8, head_dim=128, intermediate=14336,
                  vocab=128256, rope_theta=5e5, rms_eps=1e-5)
+# Kernel that serves each KV format, and dram__bytes_read.sum + dram__bytes_write.sum per algorithmic
+# byte from an ncu capture of that kernel (profiles/decode_attn_fp8_mma_b32_ctx4096.md: 269.83 MB +
+# 4.09 MB against 268.4 MB algorithmic; profiles/decode_attn_mma_f16widen_fp8_b32_ctx4096.md for the
+# f16-widening kernel).  The traffic of these kernels grows in proportion to the KV bytes.
+ATTN_KERNEL = {"fp8": "decode_attn_fp8_kernel (split merge fused)", "int8": "decode_attn_mma_kernel (split merge fused)"}
+NCU_DRAM_PER_ALG_BYTE = {"fp8": (269.83 + 4.09) / 268.4}
 METRIC = "decode tokens/s (Llama-3-8B LRD+W4+FP8-KV)"
 
 
@@ -359,9 +365,11 @@ def run_ours(a):
                         "h2d_bytes_per_step": B * 8, "d2h_bytes_per_step": B * 8},
                 "gpu_launches": dec.kernel_launches_per_step * a.steps,
                 "clocks": clocks,
-                "roofline": {"kernel": "decode_attn_mma_kernel (split merge fused)", "bound": "hbm", "achieved": achieved,
+                "roofline": {"kernel": ATTN_KERNEL.get(a.kv, "decode_attn_simt_kernel"), "bound": "hbm", "achieved": achieved,
                              "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_source": which,
-                             "traffic": None, "ms_per_launch": t_attn,
+                             "traffic": (attn_alg * NCU_DRAM_PER_ALG_BYTE[a.kv]) if a.kv in NCU_DRAM_PER_ALG_BYTE else None,
+                             "traffic_source": "dram bytes of one ncu capture (batch 32 x context 4096) scaled by algorithmic bytes",
+                             "ms_per_launch": t_attn,
                              "step_achieved": step_bytes / (ms / a.steps * 1e-3) / 1e9,
                              "step_frac": step_bytes / (ms / a.steps * 1e-3) / 1e9 / peak}}
         try:
