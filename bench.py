@@ -339,7 +339,7 @@ def run_ours(a):
     dec.seq_lens.copy_(saved)
     # per-kernel timing captures a second CUDA graph; kept out of the tensor-parallel mode, whose ranks
     # must stay in lockstep on the NCCL communicator
-    t_attn = time_attention_kernel(dec, a) if not tp else float("nan")
+    t_attn = time_attention_kernel(dec, a) if not tp else None   # tensor parallel: the kernel is not timed alone
     if world > 1:
         t = torch.tensor([ms, ms_e2e], device=device)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -349,7 +349,7 @@ def run_ours(a):
         ctx_mid = ctx0 + a.steps // 2
         step_bytes, attn_bytes = algorithmic_bytes(a, ctx_mid)
         attn_alg = algorithmic_bytes(a, int(dec.seq_lens[0].item()))[1]
-        achieved = attn_alg / (t_attn * 1e-3) / 1e9
+        achieved = attn_alg / (t_attn * 1e-3) / 1e9 if t_attn else None
         seqs = B if tp else world * B                  # tensor parallel: one batch shared by all ranks
         tps = seqs * a.steps / (ms * 1e-3)
         line = {"metric": METRIC, "value": tps, "unit": "tokens/s", "n_gpus": world, "steps": a.steps, "warmup": a.warmup,
@@ -366,7 +366,7 @@ def run_ours(a):
                 "gpu_launches": dec.kernel_launches_per_step * a.steps,
                 "clocks": clocks,
                 "roofline": {"kernel": ATTN_KERNEL.get(a.kv, "decode_attn_simt_kernel"), "bound": "hbm", "achieved": achieved,
-                             "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_source": which,
+                             "peak": peak, "unit": "GB/s", "frac": achieved / peak if achieved else None, "peak_source": which,
                              "traffic": (attn_alg * NCU_DRAM_PER_ALG_BYTE[a.kv]) if a.kv in NCU_DRAM_PER_ALG_BYTE else None,
                              "traffic_source": "dram bytes of one ncu capture (batch 32 x context 4096) scaled by algorithmic bytes",
                              "ms_per_launch": t_attn,
