@@ -1,4 +1,4 @@
-// Split-K paged decode attention on tensor cores (int8 and FP8-e4m3 pages).
+// Split-K paged decode attention on tensor cores (int8, FP8-e4m3 and NVFP4 pages).
 //
 // Replaces transformersurgeon/blocks/mha.py:9-103 (attention(): GQA, softmax, @V) for the
 // decode step.  One CTA = one (sequence, kv head, split); its 4 warps take pages
@@ -9,7 +9,10 @@
 //     online softmax over tokens per head       (warp shuffles over the token lanes)
 //     O^T[dim, head]  += V^T_page . P^T         (8 x mma.m16n8k16)
 // so the whole GQA group (<= 8 query heads) shares one read of the page.  Codes are
-// widened to f16 in registers (exact for e4m3 and int8); scales are applied in fp32.
+// widened to f16 in registers (exact for e4m3 and int8); scales are applied in fp32.  NVFP4 pages:
+// an e2m1 code times its e4m3 block scale is exact in f16 (2 x 4 significant bits), so K goes to
+// the MMA as code * scale; for V the block scale of a token is folded into that token's softmax
+// weight (one product per 16-dim block and token instead of one per element).
 // Partials (m, l, acc) go to the workspace; decode_attn_reduce_kernel merges splits.
 #include "decode_attn_common.cuh"
 
@@ -85,13 +88,37 @@ __device__ __forceinline__ int kswz(int row) { return ((row & 1) << 2) | ((row >
 template <int D> __device__ __forceinline__ int k_phys_chunk(int row, int j) {
   return row * (D / 16) + (D == 128 ? (j ^ kswz(row)) : j);
 }
+// NVFP4 K rows are D/2 bytes (D/32 chunks): rows four apart would meet in the same banks, so the
+// 32-byte half of the row is flipped for every other group of four rows.
+template <int D> __device__ __forceinline__ int k4_phys_chunk(int row, int j) {
+  return row * (D / 32) + (D == 128 ? (j ^ (((row >> 2) & 1) << 1)) : j);
+}
+// e2m1 codes n_A and n_{A+4} of the 8 in a 32-bit word (16 bits apart, so one shift serves both) ->
+// f16x2 holding value * 2^-14, with integer instructions only: the sign goes to bit 15 and the
+// three magnitude bits (2 exponent, 1 mantissa; bias 1 against f16's 15) to f16 bits 11..9; code
+// 0.5 lands on an f16 subnormal, also exactly.  The conversion instructions are far slower.
+template <int A> __device__ __forceinline__ unsigned e2m1_pair_alu(unsigned w) {
+  const unsigned x = w << (12 - 4 * A);
+  return (x & 0x80008000u) | ((x >> 3) & 0x0E000E00u);
+}
+// e4m3 codes in bytes 1 and 3 of t -> f16x2 of value * 2^-8 (see widen2_e4m3_alu)
+__device__ __forceinline__ unsigned e4m3_hi_bytes_alu(unsigned t) { return (t & 0x80008000u) | ((t >> 1) & 0x3f803f80u); }
+__device__ __forceinline__ unsigned hmul2_u(unsigned a, unsigned b) {
+  __half2 h = __hmul2(*reinterpret_cast<__half2*>(&a), *reinterpret_cast<__half2*>(&b));
+  return *reinterpret_cast<unsigned*>(&h);
+}
+template <int FMT, int D> struct RecBytes {
+  static constexpr int value = FMT == TSB200_KV_INT8 ? 16 * D + 64 : (FMT == TSB200_KV_NVFP4 ? 9 * D : 16 * D);
+};
 
 template <typename T, int D, int FMT>
 __global__ void __launch_bounds__(kWarps * 32)
 decode_attn_mma_kernel(tsb200_kv_desc kv, const T* __restrict__ q, int64_t qs, int H, float sm_scale, int64_t max_seq_len, int S,
                        float* __restrict__ ws, int* __restrict__ counters, T* __restrict__ out) {
-  constexpr int REC = (FMT == TSB200_KV_INT8) ? 16 * D + 64 : 16 * D;
-  constexpr int CODE_CHUNKS = D;               // 16*D bytes / 16
+  constexpr bool FP4 = FMT == TSB200_KV_NVFP4;
+  constexpr int REC = RecBytes<FMT, D>::value;
+  constexpr int CODE_CHUNKS = FP4 ? D / 2 : D; // 16-byte chunks of K codes (placed with the row swizzle)
+  constexpr int ROW_CHUNKS = FP4 ? D / 32 : D / 16;
   constexpr int REC_CHUNKS = REC / 16;
   constexpr int STAGE = 2 * REC;
   constexpr int NC = D / 16;                    // k-steps of QK, m-tiles of PV
@@ -118,9 +145,13 @@ decode_attn_mma_kernel(tsb200_kv_desc kv, const T* __restrict__ q, int64_t qs, i
     const T* qp = q + (int64_t)b * qs + (int64_t)(hk * g + g0 + (valid ? gid : 0)) * D;
 #pragma unroll
     for (int c = 0; c < NC; ++c) {
-      const int base = 16 * (tid + 4 * (c >> 2)) + 4 * (c & 3);
+      // int8 / fp8: the step's k-slots are 4 consecutive dims; NVFP4: dims (x, x + 4) and (x + 1, x + 5),
+      // the pairs that e2m1_pair_alu extracts from a word of 8 codes
+      const int base = FMT == TSB200_KV_NVFP4 ? 16 * (tid + 4 * (c >> 2)) + 8 * ((c & 3) >> 1) + 2 * (c & 1)
+                                              : 16 * (tid + 4 * (c >> 2)) + 4 * (c & 3);
+      constexpr int o1 = FMT == TSB200_KV_NVFP4 ? 4 : 1, o2 = FMT == TSB200_KV_NVFP4 ? 1 : 2, o3 = FMT == TSB200_KV_NVFP4 ? 5 : 3;
       float f0 = 0.f, f1 = 0.f, f2 = 0.f, f3 = 0.f;
-      if (valid) { f0 = to_f32<T>(qp[base]); f1 = to_f32<T>(qp[base + 1]); f2 = to_f32<T>(qp[base + 2]); f3 = to_f32<T>(qp[base + 3]); }
+      if (valid) { f0 = to_f32<T>(qp[base]); f1 = to_f32<T>(qp[base + o1]); f2 = to_f32<T>(qp[base + o2]); f3 = to_f32<T>(qp[base + o3]); }
       qf[c][0] = pack_h2(f0, f1);
       qf[c][1] = pack_h2(f2, f3);
     }
@@ -128,7 +159,10 @@ decode_attn_mma_kernel(tsb200_kv_desc kv, const T* __restrict__ q, int64_t qs, i
   float kscale = 1.f, vscale = 1.f;
   if (FMT == TSB200_KV_FP8) { kscale = kv.k_scale[b * kv.hkv + hk]; vscale = kv.v_scale[b * kv.hkv + hk]; }
   // FP8 keys are widened to value * 2^-8 (widen2_e4m3_alu): 256 restores the scale
-  const float sc = sm_scale * 1.4426950408889634f * kscale * ((FMT == TSB200_KV_FP8 && TSB_ATTN_ALU_WIDEN) ? 256.0f : 1.0f);
+  // NVFP4 keys reach the MMA as code * block scale * 2^-7, values as code * 2^-14 (see below)
+  if (FMT == TSB200_KV_NVFP4) vscale = 16384.0f;
+  const float sc = sm_scale * 1.4426950408889634f * kscale *
+                   ((FMT == TSB200_KV_FP8 && TSB_ATTN_ALU_WIDEN) ? 256.0f : (FMT == TSB200_KV_NVFP4 ? 128.0f : 1.0f));
 
   float oacc[NC][4];
 #pragma unroll
@@ -151,7 +185,8 @@ decode_attn_mma_kernel(tsb200_kv_desc kv, const T* __restrict__ q, int64_t qs, i
 #pragma unroll
       for (int ci = lane; ci < REC_CHUNKS; ci += 32) {
         int phys = ci;
-        if (ci < CODE_CHUNKS) phys = k_phys_chunk<D>(ci / (D / 16), ci % (D / 16));
+        if (ci < CODE_CHUNKS)
+          phys = FP4 ? k4_phys_chunk<D>(ci / ROW_CHUNKS, ci % ROW_CHUNKS) : k_phys_chunk<D>(ci / ROW_CHUNKS, ci % ROW_CHUNKS);
         cp_async16(sK + phys * 16, kr + ci * 16);
         cp_async16(sV + ci * 16, vr + ci * 16);
       }
@@ -174,8 +209,31 @@ decode_attn_mma_kernel(tsb200_kv_desc kv, const T* __restrict__ q, int64_t qs, i
 
     // ---- S^T = K . Q^T -----------------------------------------------------------
     float sacc[4] = {0.f, 0.f, 0.f, 0.f};
+    if (FP4) {
+      // the lane's 16 dims of a row = 8 bytes of codes = exactly one scale block
+      const uint8_t* ksc = sK + 16 * (D / 2);
 #pragma unroll
-    for (int hh = 0; hh < D / 64; ++hh) {
+      for (int hh = 0; hh < D / 64; ++hh) {
+        const int j = tid + 4 * hh;
+        const uint2 ka = *reinterpret_cast<const uint2*>(sK + k4_phys_chunk<D>(r1, j >> 1) * 16 + 8 * (j & 1));
+        const uint2 kb = *reinterpret_cast<const uint2*>(sK + k4_phys_chunk<D>(r2, j >> 1) * 16 + 8 * (j & 1));
+        // block scale * 2^-8 (integer widening) * 2^15 -> scale * 2^7 <= 57344; code * 2^-14 times that is
+        // code * scale * 2^-7, exact in f16 (6 significant bits, >= 2^-17)
+        const unsigned k215 = 0x78007800u;
+        const unsigned sa = hmul2_u(e4m3_hi_bytes_alu((unsigned)ksc[r1 * (D / 16) + j] * 0x01000100u), k215);
+        const unsigned sb = hmul2_u(e4m3_hi_bytes_alu((unsigned)ksc[r2 * (D / 16) + j] * 0x01000100u), k215);
+        mma16816(sacc, hmul2_u(e2m1_pair_alu<0>(ka.x), sa), hmul2_u(e2m1_pair_alu<0>(kb.x), sb), hmul2_u(e2m1_pair_alu<1>(ka.x), sa),
+                 hmul2_u(e2m1_pair_alu<1>(kb.x), sb), qf[4 * hh][0], qf[4 * hh][1]);
+        mma16816(sacc, hmul2_u(e2m1_pair_alu<2>(ka.x), sa), hmul2_u(e2m1_pair_alu<2>(kb.x), sb), hmul2_u(e2m1_pair_alu<3>(ka.x), sa),
+                 hmul2_u(e2m1_pair_alu<3>(kb.x), sb), qf[4 * hh + 1][0], qf[4 * hh + 1][1]);
+        mma16816(sacc, hmul2_u(e2m1_pair_alu<0>(ka.y), sa), hmul2_u(e2m1_pair_alu<0>(kb.y), sb), hmul2_u(e2m1_pair_alu<1>(ka.y), sa),
+                 hmul2_u(e2m1_pair_alu<1>(kb.y), sb), qf[4 * hh + 2][0], qf[4 * hh + 2][1]);
+        mma16816(sacc, hmul2_u(e2m1_pair_alu<2>(ka.y), sa), hmul2_u(e2m1_pair_alu<2>(kb.y), sb), hmul2_u(e2m1_pair_alu<3>(ka.y), sa),
+                 hmul2_u(e2m1_pair_alu<3>(kb.y), sb), qf[4 * hh + 3][0], qf[4 * hh + 3][1]);
+      }
+    }
+#pragma unroll
+    for (int hh = 0; hh < (FP4 ? 0 : D / 64); ++hh) {
       const int j = tid + 4 * hh;
       const uint4 ka = *reinterpret_cast<const uint4*>(sK + k_phys_chunk<D>(r1, j) * 16);
       const uint4 kb = *reinterpret_cast<const uint4*>(sK + k_phys_chunk<D>(r2, j) * 16);
@@ -212,10 +270,15 @@ decode_attn_mma_kernel(tsb200_kv_desc kv, const T* __restrict__ q, int64_t qs, i
     l0 = l0 * c0 + (p0 + p2);
     l1 = l1 * c1 + (p1 + p3);
     m0 = mn0; m1 = mn1;
+    if (FP4) vs1 = vs2 = 256.0f;                // NVFP4: the block scales multiply P as scale * 2^-8
     const unsigned P1 = pack_h2(ok1 ? p0 * vs1 : 0.f, ok1 ? p1 * vs1 : 0.f);
     const unsigned P2 = pack_h2(ok2 ? p2 * vs2 : 0.f, ok2 ? p3 * vs2 : 0.f);
-    const unsigned pb0 = movmatrix_trans(P1);   // tokens 4*tid, 4*tid+1 of head gid
-    const unsigned pb1 = movmatrix_trans(P2);   // tokens 4*tid+2, 4*tid+3
+    unsigned pb0 = movmatrix_trans(P1);         // tokens 4*tid, 4*tid+1 of head gid
+    unsigned pb1 = movmatrix_trans(P2);         // tokens 4*tid+2, 4*tid+3
+    if (FP4) {                                  // NVFP4 pairs tokens (4*tid, 4*tid+2) and (4*tid+1, 4*tid+3)
+      const unsigned t0 = __byte_perm(pb0, pb1, 0x5410), t1 = __byte_perm(pb0, pb1, 0x7632);
+      pb0 = t0; pb1 = t1;
+    }
     // bytes of this lane's 4 tokens that are inside the sequence (stale slots -> +0)
     unsigned vmask = 0xffffffffu;
     if (nt < 16) {
@@ -223,8 +286,24 @@ decode_attn_mma_kernel(tsb200_kv_desc kv, const T* __restrict__ q, int64_t qs, i
       vmask = left >= 4 ? 0xffffffffu : (left <= 0 ? 0u : (0xffffffffu >> (8 * (4 - left))));
     }
     // ---- O^T += V^T . P^T -----------------------------------------------------------
+    if (FP4) {
+      const uint8_t* vsc = sV + 16 * (D / 2);
 #pragma unroll
-    for (int mt = 0; mt < NC; ++mt) {
+      for (int mt = 0; mt < NC; ++mt) {
+        // one word = tokens 4*tid..4*tid+3 of dims 16*mt + 2*gid (low nibbles) and + 1 (high nibbles):
+        // MMA rows gid / gid + 8 are those two dims
+        const unsigned wv = *reinterpret_cast<const unsigned*>(sV + (8 * mt + gid) * 16 + 4 * tid);
+        const unsigned sw = *reinterpret_cast<const unsigned*>(vsc + mt * 16 + 4 * tid) & vmask;   // stale slots: scale +0
+        // code pairs 16 bits apart = tokens (0, 2) and (1, 3) of the lane's four; values enter as code * 2^-14
+        // (2^14 is restored with the split scale), weights as p * 2^8 * (block scale * 2^-8)
+        const unsigned b0 = hmul2_u(pb0, e4m3_hi_bytes_alu(__byte_perm(sw, 0u, 0x2404)));
+        const unsigned b1 = hmul2_u(pb1, e4m3_hi_bytes_alu(__byte_perm(sw, 0u, 0x3414)));
+        oacc[mt][0] *= c0; oacc[mt][1] *= c1; oacc[mt][2] *= c0; oacc[mt][3] *= c1;
+        mma16816(oacc[mt], e2m1_pair_alu<0>(wv), e2m1_pair_alu<1>(wv), e2m1_pair_alu<2>(wv), e2m1_pair_alu<3>(wv), b0, b1);
+      }
+    }
+#pragma unroll
+    for (int mt = 0; mt < (FP4 ? 0 : NC); ++mt) {
       const unsigned w1 = *reinterpret_cast<const unsigned*>(sV + (16 * mt + gid) * 16 + 4 * tid) & vmask;
       const unsigned w2 = *reinterpret_cast<const unsigned*>(sV + (16 * mt + gid + 8) * 16 + 4 * tid) & vmask;
       oacc[mt][0] *= c0; oacc[mt][1] *= c1; oacc[mt][2] *= c0; oacc[mt][3] *= c1;
@@ -250,10 +329,12 @@ decode_attn_mma_kernel(tsb200_kv_desc kv, const T* __restrict__ q, int64_t qs, i
 #pragma unroll
   for (int mt = 0; mt < NC; ++mt) {
     float* a = sm_acc + (size_t)w * 8 * D;
-    a[(2 * tid) * D + 16 * mt + gid] = oacc[mt][0];
-    a[(2 * tid + 1) * D + 16 * mt + gid] = oacc[mt][1];
-    a[(2 * tid) * D + 16 * mt + gid + 8] = oacc[mt][2];
-    a[(2 * tid + 1) * D + 16 * mt + gid + 8] = oacc[mt][3];
+    const int da = FP4 ? 16 * mt + 2 * gid : 16 * mt + gid;         // dims of MMA rows gid and gid + 8
+    const int db = FP4 ? da + 1 : da + 8;
+    a[(2 * tid) * D + da] = oacc[mt][0];
+    a[(2 * tid + 1) * D + da] = oacc[mt][1];
+    a[(2 * tid) * D + db] = oacc[mt][2];
+    a[(2 * tid + 1) * D + db] = oacc[mt][3];
   }
   __syncthreads();
   // merge the 4 warps; with one split the result is final, otherwise it is this split's partial
@@ -311,7 +392,7 @@ decode_attn_mma_kernel(tsb200_kv_desc kv, const T* __restrict__ q, int64_t qs, i
 template <typename T, int D, int FMT>
 int launch_mma(const tsb200_kv_desc& kv, const void* q, int64_t qs, int H, float sm_scale, int64_t max_seq_len, int S, int64_t B,
                float* ws, int* counters, void* out, cudaStream_t st) {
-  constexpr int REC = (FMT == TSB200_KV_INT8) ? 16 * D + 64 : 16 * D;
+  constexpr int REC = RecBytes<FMT, D>::value;
   constexpr size_t pipe = (size_t)kWarps * kStages * 2 * REC;
   constexpr size_t merge = (size_t)(kWarps * 16 + kWarps * 8 * D) * sizeof(float);
   constexpr size_t smem = pipe > merge ? pipe : merge;
@@ -344,7 +425,7 @@ extern "C" int tsb200_paged_decode_attn(const tsb200_kv_desc* kv, const void* q,
   if (st != TSB200_OK || noop) return st;
   const int64_t qs = q_batch_stride ? q_batch_stride : (int64_t)H * kv->head_dim;
   if (qs < (int64_t)H * kv->head_dim) return TSB200_ERR_ARG;
-  if (kv->format >= TSB200_KV_NVFP4)   // NVFP4 and unquantized pages: CUDA-core kernel (fp32 math)
+  if (kv->format > TSB200_KV_NVFP4)    // unquantized pages: CUDA-core kernel (fp32 math)
     return tsb200_paged_decode_attn_simt(kv, q, out, dtype, q_batch_stride, B, H, sm_scale, max_seq_len, workspace, workspace_bytes, stream);
   cudaStream_t s = as_stream(stream);
   const int S = choose_splits(B, kv->hkv, max_seq_len);
@@ -368,6 +449,10 @@ extern "C" int tsb200_paged_decode_attn(const tsb200_kv_desc* kv, const void* q,
   r = launch_mma<TT, DD, FF>(*kv, q, qs, H, sm_scale, max_seq_len, -S, B, ws, counters, out, s);                      \
   if (r != TSB200_OK) return r;                                                                                         \
   return launch_reduce<TT, DD>(ws, B * H, S, out, s)
+  if (kv->format == TSB200_KV_NVFP4) {
+    if (dtype == TSB200_F32) { if (D == 64) { TSB_GO(float, 64, TSB200_KV_NVFP4); } else { TSB_GO(float, 128, TSB200_KV_NVFP4); } }
+    else { if (D == 64) { TSB_GO(__nv_bfloat16, 64, TSB200_KV_NVFP4); } else { TSB_GO(__nv_bfloat16, 128, TSB200_KV_NVFP4); } }
+  }
   if (dtype == TSB200_F32) {
     if (D == 64) { if (kv->format == TSB200_KV_INT8) { TSB_GO(float, 64, TSB200_KV_INT8); } else { TSB_GO(float, 64, TSB200_KV_FP8); } }
     else { if (kv->format == TSB200_KV_INT8) { TSB_GO(float, 128, TSB200_KV_INT8); } else { TSB_GO(float, 128, TSB200_KV_FP8); } }
