@@ -9,7 +9,7 @@
 //     each CTA walks its items round-robin while one producer lane keeps issuing TMA loads
 //     across item boundaries into a ring of STAGES.  A stage = KBS consecutive k-blocks: one
 //     weight box of 128 rows x up to 128 bytes of codes (swizzled) + KBS activation tiles;
-//   * two groups of 4 dequant warps take stages alternately.  A thread owns one weight row:
+//   * two groups of 4 dequant warps share every stage (even / odd k-blocks).  A thread owns one weight row:
 //     it reads the row's codes from shared memory, widens them to bf16 pairs in registers (exact
 //     integers) and stores them with tcgen05.st straight into TENSOR MEMORY, where they are the
 //     A operand of the MMA (M = 128 weight rows; K-major, two bf16 per 32-bit column) - no
@@ -34,7 +34,8 @@ using namespace tc;
 namespace {
 
 constexpr int kDqWarps = 8;                 // two groups of four
-constexpr int kThreadsQ = 64 + kDqWarps * 32;
+constexpr int kThreadsQ = 64 + kDqWarps * 32 + 32;   // producer, MMA issuer 0, 8 dequant warps, MMA issuer 1
+constexpr int kIssuer1Warp = 2 + kDqWarps;
 constexpr int kSmemBudget = 208 * 1024;
 constexpr unsigned kTmemCols = 512;
 constexpr unsigned kACol0 = 128;            // TMEM column of A buffer 0; buffer 1 follows at +128
@@ -53,6 +54,14 @@ template <int TN, int BITS> struct QLayout {
   static constexpr int NR = kNRraw > 12 ? 12 : kNRraw;
   static constexpr int kBarBytes = 1024;
   static constexpr int kBytes = NR * kStage + kBarBytes + 1024;
+  // One lane needs ~80-100 cycles to issue one tcgen05.mma (operand set-up on the uniform datapath),
+  // far longer than a narrow MMA runs.  Two lanes of different warps therefore issue the even and the
+  // odd k-blocks of every stage into two separate accumulator CHAINS (MMAs of different threads are not
+  // ordered, so they must not share an accumulator); the epilogue adds the chains.  Accumulators own
+  // tensor-memory columns [0, 128): chain c of a plain item at c * TN; of a gated item gate at
+  // (2 c) * TN and up at (2 c + 1) * TN.
+  static constexpr bool kTwoChains = KBS >= 2 && 2 * TN <= 128;
+  static constexpr bool kTwoChainsGated = KBS >= 2 && 4 * TN <= 128;
 };
 
 __device__ __forceinline__ uint4 lds128(unsigned addr) {
@@ -161,6 +170,7 @@ __device__ __forceinline__ bool warps_rendezvous(unsigned long long* bar, int& u
 // of the workspace header (split counters that far up are not in use at traced sizes).
 #ifdef TSB_TRACE
 __device__ long long g_trace[160 * 32 * 2];     // per CTA: 32 slots of {clock64, globaltimer}
+__device__ long long g_trace_fine[4 * 512];     // CTAs 0..3: 512 clock64 slots each (per-stage stamps)
 __device__ __forceinline__ void trace_stamp(int i) {
   if (blockIdx.x < 160 && i < 32) {
     unsigned long long gt;
@@ -169,9 +179,14 @@ __device__ __forceinline__ void trace_stamp(int i) {
     g_trace[(blockIdx.x * 32 + i) * 2 + 1] = (long long)gt;
   }
 }
+__device__ __forceinline__ void trace_fine(int i) {
+  if (blockIdx.x < 4 && i >= 0 && i < 512) g_trace_fine[blockIdx.x * 512 + i] = clock64();
+}
+#define TSB_FINE(i) trace_fine(i)
 #define TSB_STAMP(i) do { if (blockIdx.x == 0) reinterpret_cast<long long*>(reinterpret_cast<char*>(prog.status) + kWsHeader - 512)[i] = clock64(); trace_stamp(i); } while (0)
 #else
 #define TSB_STAMP(i) do { } while (0)
+#define TSB_FINE(i) do { } while (0)
 #endif
 // per-phase stamps of CTA 0: slot 8 + 4 * phase + k
 #define TSB_STAMP_P(p, k) TSB_STAMP(8 + 4 * (p) + (k))
@@ -232,10 +247,10 @@ linear_tcq_kernel(const __grid_constant__ Program prog) {
   unsigned long long* bars = reinterpret_cast<unsigned long long*>(r_ring + NR * L::kStage);
   unsigned long long* w_full = bars;                        // [NR] weight box landed (the dequant warps wait on it)
   unsigned long long* x_full = bars + NR;                   // [NR] activation tiles landed (the MMA lane waits on it)
-  unsigned long long* raw_empty = bars + 2 * NR;            // [NR] 4 dequant warps of the owning group + MMA commit
-  unsigned long long* a_ready = bars + 3 * NR;              // [2]  4 dequant warps: A buffer stored in TMEM
-  unsigned long long* a_empty = a_ready + 2;                // [2]  MMA commit: A buffer consumed
-  unsigned long long* acc_full = a_empty + 2;               // [1]  MMA commit: accumulator(s) of the item complete
+  unsigned long long* stage_done = bars + 2 * NR;           // [NR] MMA commit: the stage's MMAs are complete, so its
+                                                            //      weight box, activation tiles and A buffer are free
+  unsigned long long* a_ready = bars + 3 * NR;              // [2]  8 dequant warps: A buffer stored in TMEM
+  unsigned long long* acc_full = a_ready + 2;               // [1]  MMA commit: accumulator(s) of the item complete
   unsigned long long* ep_bar = acc_full + 1;                // [1]  rendezvous of the 8 warps
   unsigned* tmem_slot = reinterpret_cast<unsigned*>(ep_bar + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -245,9 +260,9 @@ linear_tcq_kernel(const __grid_constant__ Program prog) {
   pdl_launch_dependents();
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < NR; ++i) { mbar_init(&w_full[i], 1); mbar_init(&x_full[i], 1); mbar_init(&raw_empty[i], 4 + 1); }
-    for (int i = 0; i < 2; ++i) { mbar_init(&a_ready[i], 4); mbar_init(&a_empty[i], 1); }
-    mbar_init(acc_full, 1);
+    for (int i = 0; i < NR; ++i) { mbar_init(&w_full[i], 1); mbar_init(&x_full[i], 1); mbar_init(&stage_done[i], 2); }
+    for (int i = 0; i < 2; ++i) mbar_init(&a_ready[i], kDqWarps);
+    mbar_init(acc_full, 2);                                 // both issuers commit, with or without MMAs of their own
     mbar_init(ep_bar, kDqWarps);
     *abort_flag = 0;
     *last_flag = 0;
@@ -262,7 +277,10 @@ linear_tcq_kernel(const __grid_constant__ Program prog) {
 
   // Work enumeration, identical in every role.  Phase -> items (round-robin over CTAs) -> passes
   // (one per matrix the item touches: 2 for a gated item) -> stages of KBS k-blocks.
-  struct Item { int sub, nt, mt, kb0, nkb; };
+  // ns = stages of the item's K range; the item walks them starting at stage `rot` and wrapping
+  // around, so CTAs that share a K range (same split, different weight tiles) do not all request
+  // the same activation lines from L2 at the same moment.
+  struct Item { int sub, nt, mt, kb0, nkb, ns, rot; };
   auto decode = [&](const Phase& ph, int item) {
     Item it;
     int local = item;
@@ -274,6 +292,8 @@ linear_tcq_kernel(const __grid_constant__ Program prog) {
     it.mt = t / ph.n_tiles;
     it.kb0 = sp * ph.kb_per_split;
     it.nkb = min(ph.kb_per_split, ph.kb_total - it.kb0);
+    it.ns = (it.nkb + KBS - 1) / KBS;
+    it.rot = it.nt % it.ns;
     return it;
   };
 
@@ -303,7 +323,8 @@ linear_tcq_kernel(const __grid_constant__ Program prog) {
           const int passes = ph.gated ? 2 : 1;
           for (int ps = 0; ps < passes; ++ps) {
             const SubGemm& sg = ph.sub[ph.gated ? ps : it.sub];
-            for (int i = 0; i < it.nkb; i += KBS, ++gs) {
+            for (int jj = 0; jj < it.ns; ++jj, ++gs) {
+              const int i = ((jj + it.rot) % it.ns) * KBS;
               const int rel = gs - gs_phase0;
               if (rel >= rel_end) return gs;
               if (rel < rel_begin) continue;
@@ -311,7 +332,7 @@ linear_tcq_kernel(const __grid_constant__ Program prog) {
               uint8_t* st = r_ring + s * L::kStage;
               const int kcol = (it.kb0 + i) * BK;
               if (do_w) {                                     // the stage is free once its previous user is done
-                if (gs >= NR && !mbar_wait(&raw_empty[s], ((gs / NR) - 1) & 1, abort_flag, 1)) { ok = false; return gs; }
+                if (gs >= NR && !mbar_wait(&stage_done[s], ((gs / NR) - 1) & 1, abort_flag, 1)) { ok = false; return gs; }
                 mbar_expect_tx(&w_full[s], (unsigned)L::kRaw);
                 tma_load_2d(st + L::kX, &sg.map_w, kcol * BITS / 8, it.nt * BM, &w_full[s]);
               }
@@ -345,35 +366,44 @@ linear_tcq_kernel(const __grid_constant__ Program prog) {
         if (gs_phase0 < 0) break;
       }
     }
-  } else if (warp == 1) {
-    // ---------------------------------------------------------------- MMA issuer
+  } else if (warp == 1 || warp == kIssuer1Warp) {
+    // ---------------------------------------------------------------- MMA issuers
     if (lane == 0) {
+      const int me = warp == 1 ? 0 : 1;                       // issuer 0: even k-blocks / chain 0; issuer 1: odd / chain 1
       constexpr unsigned idesc = idesc_bf16(TN);
       int gs = 0;
       bool ok = true;
       for (int p = 0; p < prog.n_phases && ok; ++p) {
         const Phase& ph = prog.ph[p];
+        const bool two = ph.gated ? L::kTwoChainsGated : L::kTwoChains;
         for (int item = blockIdx.x; item < ph.items && ok; item += gridDim.x) {
           const Item it = decode(ph, item);
           const int passes = ph.gated ? 2 : 1;
           for (int ps = 0; ps < passes && ok; ++ps) {
-            const unsigned d_tmem = tmem_base + ps * TN;      // gated: gate -> columns [0, TN), up -> [TN, 2 TN)
-            for (int i = 0; i < it.nkb; i += KBS, ++gs) {
+            const unsigned d_tmem = tmem_base + (unsigned)((ph.gated ? 2 * (two ? me : 0) + ps : (two ? me : 0)) * TN);
+            bool first = true;                                // the chain's first MMA of the pass overwrites
+            for (int jj = 0; jj < it.ns; ++jj, ++gs) {
+              const int i = ((jj + it.rot) % it.ns) * KBS;
               const int s = gs % NR, buf = gs & 1;
-              ok = mbar_wait(&x_full[s], (gs / NR) & 1, abort_flag, 2) && mbar_wait(&a_ready[buf], (gs >> 1) & 1, abort_flag, 3);
+              ok = mbar_wait(&x_full[s], (gs / NR) & 1, abort_flag, 2);
+              if (me == 0) TSB_FINE(8 * gs + 6);
+              ok = ok && mbar_wait(&a_ready[buf], (gs >> 1) & 1, abort_flag, 3);
               if (!ok) break;
+              if (me == 0) TSB_FINE(8 * gs + 0);
               tc_fence_after();
               const unsigned a_tmem = tmem_base + kACol0 + buf * 128;
               const unsigned x_base = smem_u32(r_ring + s * L::kStage);
               const int nsub = min(KBS, it.nkb - i);
-              for (int j = 0; j < nsub; ++j) {
+              for (int j = two ? me : 0; j < nsub && (two || me == 0); j += two ? 2 : 1) {
                 const unsigned long long bdesc = smem_desc_sw128(x_base + j * L::kXTile);
 #pragma unroll
-                for (int k = 0; k < BK / 16; ++k)   // A: 8 TMEM columns per K=16; B: +32 bytes inside the swizzle atom
-                  umma_bf16_ts(d_tmem, a_tmem + j * 32 + k * 8, bdesc + 2 * k, idesc, (i + j > 0 || k > 0) ? 1u : 0u);
+                for (int k = 0; k < BK / 16; ++k) { // A: 8 TMEM columns per K=16; B: +32 bytes inside the swizzle atom
+                  umma_bf16_ts(d_tmem, a_tmem + j * 32 + k * 8, bdesc + 2 * k, idesc, first ? 0u : 1u);
+                  first = false;
+                }
               }
-              umma_commit(&a_empty[buf]);
-              umma_commit(&raw_empty[s]);
+              umma_commit(&stage_done[s]);                     // arrives once this lane's MMAs (if any) are complete
+              if (me == 0) TSB_FINE(8 * gs + 1);
             }
           }
           if (ok) umma_commit(acc_full);
@@ -382,7 +412,7 @@ linear_tcq_kernel(const __grid_constant__ Program prog) {
     }
   } else {
     // ---------------------------------------------------------------- dequant + epilogue
-    const int grp = (warp - 2) >> 2;                         // dequant group 0 / 1: stages of that parity
+    const int grp = (warp - 2) >> 2;                         // dequant group 0 / 1: k-blocks of that parity in every stage
     const int q = warp & 3;                                  // TMEM lane quarter this warp may access
     const int row = q * 32 + lane;                           // weight row within the tile = TMEM lane
     const unsigned lane_addr = tmem_base + ((unsigned)(q * 32) << 16);
@@ -405,26 +435,32 @@ linear_tcq_kernel(const __grid_constant__ Program prog) {
           bv1 = (ph.sub[1].bias && n < ph.N) ? __bfloat162float(ph.sub[1].bias[n]) : 0.f;
         }
         for (int ps = 0; ps < passes && ok; ++ps) {
-          for (int i = 0; i < it.nkb; i += KBS, ++gs) {
-            if ((gs & 1) != grp) continue;
+          for (int jj = 0; jj < it.ns; ++jj, ++gs) {
+            const int i = ((jj + it.rot) % it.ns) * KBS;
             const int s = gs % NR, buf = gs & 1;
             ok = mbar_wait(&w_full[s], (gs / NR) & 1, abort_flag, 4);
-            if (ok && gs >= 2) ok = mbar_wait(&a_empty[buf], ((gs >> 1) - 1) & 1, abort_flag, 5);
+            if (threadIdx.x == 64) TSB_FINE(8 * gs + 2);
+            // the A buffer is free once the MMAs of the stage two back are complete
+            if (ok && gs >= 2) ok = mbar_wait(&stage_done[(gs - 2) % NR], ((gs - 2) / NR) & 1, abort_flag, 5);
             if (!ok) break;
+            if (threadIdx.x == 64) TSB_FINE(8 * gs + 3);
             if (gs == 0 && threadIdx.x == 64) TSB_STAMP(2);
             tc_fence_after();
             const unsigned raw = smem_u32(r_ring + s * L::kStage + L::kX);
             const int nsub = min(KBS, it.nkb - i);
-            for (int j = 0; j < nsub; ++j) {
+            for (int j = grp; j < nsub; j += 2) {              // both groups work on the stage: half the latency
               unsigned regs[32];
               dequant_row_regs<BITS, L::kRawStageRow>(raw, row, j, regs);
               tmem_st32(lane_addr + kACol0 + buf * 128 + j * 32, regs);
             }
+            if (threadIdx.x == 64) TSB_FINE(8 * gs + 4);
             tmem_st_wait();
+            if (threadIdx.x == 64) TSB_FINE(8 * gs + 5);
+            if (lane == 0 && gs < 8) { TSB_FINE(128 + 8 * gs + (warp - 2)); }
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) { mbar_arrive(&a_ready[buf]); mbar_arrive(&raw_empty[s]); }
-            if (threadIdx.x == 64) { if (gs == 0) TSB_STAMP(3); if (item == blockIdx.x && ps == 0 && i == 0) TSB_STAMP_P(p, 2); }
+            if (lane == 0) mbar_arrive(&a_ready[buf]);
+            if (threadIdx.x == 64) { if (gs == 0) TSB_STAMP(3); if (item == blockIdx.x && ps == 0 && jj == 0) TSB_STAMP_P(p, 2); }
           }
         }
         if (!ok) break;
@@ -436,15 +472,32 @@ linear_tcq_kernel(const __grid_constant__ Program prog) {
         const int64_t m0 = (int64_t)it.mt * TN;
         const bool split = ph.splits > 1;
         constexpr int CH = TN / 2;                           // token columns handled by this warp
+        // second accumulator chain: present when the phase runs two issuers and the item has >= 2 k-blocks
+        const bool chain2 = (ph.gated ? L::kTwoChainsGated : L::kTwoChains) && it.nkb >= 2;
+        const unsigned acc1 = (unsigned)((ph.gated ? 2 : 1) * TN);   // column offset of chain 1
         float* slice = ph.partial + (size_t)item * (TN * BM);
         __nv_bfloat16* y = sg0.y;
 #pragma unroll 1
         for (int c0 = grp * CH; c0 < (grp + 1) * CH; c0 += 8) {
           unsigned r[8];
           tmem_ld8(lane_addr + (unsigned)c0, r);
+          if (chain2) {
+            unsigned t[8];
+            tmem_ld8(lane_addr + acc1 + (unsigned)c0, t);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 8; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) + __uint_as_float(t[j]));
+          }
           if (ph.gated) {
             unsigned r2[8];
             tmem_ld8(lane_addr + (unsigned)(TN + c0), r2);
+            if (chain2) {
+              unsigned t[8];
+              tmem_ld8(lane_addr + acc1 + (unsigned)(TN + c0), t);
+              tmem_ld_wait();
+#pragma unroll
+              for (int j = 0; j < 8; ++j) r2[j] = __float_as_uint(__uint_as_float(r2[j]) + __uint_as_float(t[j]));
+            }
             tmem_ld_wait();
             if (n < ph.N) {
 #pragma unroll
@@ -766,5 +819,8 @@ int gemm_tcq(const void* W, int bits, const float* scale, const void* bias, cons
 #ifdef TSB_TRACE
 extern "C" int tsb200_trace_read(void* host, size_t nbytes) {
   return (int)cudaMemcpyFromSymbol(host, tsb::g_trace, nbytes < sizeof(tsb::g_trace) ? nbytes : sizeof(tsb::g_trace));
+}
+extern "C" int tsb200_trace_read_fine(void* host, size_t nbytes) {
+  return (int)cudaMemcpyFromSymbol(host, tsb::g_trace_fine, nbytes < sizeof(tsb::g_trace_fine) ? nbytes : sizeof(tsb::g_trace_fine));
 }
 #endif
