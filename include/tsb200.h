@@ -219,6 +219,15 @@ int tsb200_rope_append(const tsb200_kv_desc* kv, void* q, int q_heads, int64_t q
                        const float* rope_cos, const float* rope_sin, int64_t rope_rows,
                        void* stream);
 
+/* Dequantizing gather: k_out, v_out [B, L, hkv, d] (act dtype) <- the first L positions of every
+ * sequence, dequantized (fp8: times the sequence's scale); positions >= seq_lens[b] become zeros.
+ * Serves attention reads over T > 1 query tokens (prefill with a library attention kernel): the
+ * reference attends over the cache tensors themselves (blocks/mha.py:537-612; HF
+ * past_key_values.update returns them), which for a quantized cache are its dequantized values.
+ * L <= bt_stride * 16. */
+int tsb200_kv_gather(const tsb200_kv_desc* kv, void* k_out, void* v_out, int dtype, int64_t B, int64_t L,
+                     void* stream);
+
 /* Split-K paged decode attention: one query token per sequence.
  * Replaces blocks/mha.py:9-103 (attention(): GQA, softmax(q k^T / sqrt(d)) v) for the
  * decode step, reading the quantized pages directly.

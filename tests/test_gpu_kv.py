@@ -110,6 +110,41 @@ def test_append_empty_and_overflow(cuda):
     assert np.array_equal(g.k_pool.cpu().numpy(), o.k_pool)
 
 
+@pytest.mark.parametrize("fmt", FMTS + ["fp32", "bf16"])
+@pytest.mark.parametrize("d", [64, 128])
+def test_gather_dequantizes_bit_exact(cuda, fmt, d):
+    """tsb200_kv_gather == the oracle's dequantized cache, element for element (fp32 output), with
+    ragged lengths, an empty sequence and zeros beyond each length."""
+    from transformer_surgeon_b200 import ops
+    rng = np.random.default_rng(21)
+    B, Hkv = 4, 2
+    lens = np.array([37, 16, 0, 1], dtype=np.int32)
+    T = int(lens.max())
+    src = torch.bfloat16 if fmt == "bf16" else torch.float32
+    if fmt in FMTS:
+        o, g = make_pair(fmt, B, 3, Hkv, d, cuda, rng)
+        k, v = outlier_kv(rng, B, T, Hkv, d, src)
+        sync_scales(o, g, k, v)
+        o.append(k.float().numpy(), v.float().numpy(), new_lens=lens)
+    else:                                           # unquantized pages: no oracle object needed
+        bt = torch.from_numpy(rng.permutation(B * 3 + 2)[:B * 3].reshape(B, 3).astype(np.int32)).to(cuda)
+        g = ops.PagedKV(fmt, B * 3 + 2, Hkv, d, bt, torch.zeros(B, dtype=torch.int32, device=cuda), cuda)
+        k, v = outlier_kv(rng, B, T, Hkv, d, src)
+    nl = torch.from_numpy(lens).to(cuda)
+    g.append(k.to(cuda), v.to(cuda), new_lens=nl)
+    g.seq_lens.copy_(nl)
+    L = 40
+    kd, vd = ops.kv_gather(g, L, dtype=torch.float32)
+    kd, vd = kd.cpu().numpy(), vd.cpu().numpy()
+    for b in range(B):
+        if fmt in FMTS:
+            Kr, Vr = o.gather(b)
+        else:                                       # unquantized pages hold the appended values themselves
+            Kr, Vr = k[b, :lens[b]].float().numpy(), v[b, :lens[b]].float().numpy()
+        assert np.array_equal(kd[b, :lens[b]], Kr) and np.array_equal(vd[b, :lens[b]], Vr)
+        assert not kd[b, lens[b]:].any() and not vd[b, lens[b]:].any()
+
+
 @pytest.mark.parametrize("fmt", FMTS)
 @pytest.mark.parametrize("name", ["fp32", "bf16"])
 @pytest.mark.parametrize("H,Hkv,d", [(8, 2, 128), (14, 2, 64), (4, 4, 128), (32, 8, 128)])

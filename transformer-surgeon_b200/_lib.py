@@ -57,6 +57,7 @@ SIGNATURES = {
     "tsb200_kv_record_bytes": (_sz, [_i32, _i32]),
     "tsb200_kv_fp8_scales": (_i32, [_vp, _vp, _i32, _i64, _i64, _i32, _i32, _vp, _vp, _vp, _i64, _vp, _vp, _vp]),
     "tsb200_kv_append": (_i32, [_KD, _vp, _vp, _i32, _i64, _i64, _i64, _i64, _vp, _vp, _vp, _i64, _vp]),
+    "tsb200_kv_gather": (_i32, [_KD, _vp, _vp, _i32, _i64, _i64, _vp]),
     "tsb200_rope_append": (_i32, [_KD, _vp, _i32, _i64, _vp, _vp, _i32, _i64, _i64, _i64, _i64, _vp, _vp, _vp, _i64, _vp]),
     "tsb200_paged_decode_attn_workspace_bytes": (_sz, [_i64, _i32, _i32, _i64]),
     "tsb200_paged_decode_attn": (_i32, [_KD, _vp, _vp, _i32, _i64, _i64, _i32, _f32, _i64, _vp, _sz, _vp]),

@@ -1,0 +1,116 @@
+"""Hugging Face drop-in for the KV-cache boundary of the reference's HF path.
+
+The reference's model classes inherit `generate()` from `transformers`
+(models/qwen2_c/define_qwen2_c.py:22-27, models/llama_c/define_llama_c.py:24-30): every attention
+layer calls `past_key_values.update(key, value, layer_idx)` and hands what comes back to the
+attention function selected by `config._attn_implementation`.  This module supplies both halves:
+
+  * `PagedQuantCache` - a `transformers.Cache` whose layers quantize-and-append into the paged pools
+    (`tsb200_kv_append`) instead of concatenating tensors;
+  * the attention function registered as `"tsb200_paged"`: one query token per sequence goes to the
+    paged decode kernel (`tsb200_paged_decode_attn`); a prompt (T > 1) attends over the cache's
+    DEQUANTIZED contents (`tsb200_kv_gather`) with torch's scaled-dot-product attention.
+
+Usage (generate() itself is untouched):
+
+    model.config._attn_implementation = "tsb200_paged"      # or attn_implementation= at load time
+    cache = PagedQuantCache(model.config, batch, max_len, kv_format="int8")
+    model.generate(ids, past_key_values=cache, do_sample=False, ...)
+
+Limits: every sequence of the batch has the same length (no padding mask on the decode step);
+no beam reordering, cropping or sliding windows.
+"""
+import torch
+from transformers import AttentionInterface
+from transformers.cache_utils import Cache, CacheLayerMixin
+from transformers.integrations.sdpa_attention import sdpa_attention_forward
+from transformers.masking_utils import AttentionMaskInterface, sdpa_mask
+
+from . import ops
+
+ATTN_NAME = "tsb200_paged"
+
+
+class PagedCacheLayer(CacheLayerMixin):
+    """One layer's paged pools.  Sequence b owns pages [b * P, (b + 1) * P) in logical order."""
+
+    def __init__(self, kv_format, batch, max_len, hkv, head_dim, device):
+        super().__init__()
+        self.kv_format, self.batch, self.max_len = kv_format, batch, int(max_len)
+        pages = (self.max_len + 15) // 16
+        self.block_table = torch.arange(batch * pages, dtype=torch.int32, device=device).reshape(batch, pages)
+        self.seq_lens = torch.zeros(batch, dtype=torch.int32, device=device)
+        self.kv = ops.PagedKV(kv_format, batch * pages, hkv, head_dim, self.block_table, self.seq_lens, device)
+        self.cumulative_length = 0
+        self.is_initialized = True
+        self.device = device
+
+    def lazy_initialization(self, key_states, value_states):
+        pass                                    # pools are allocated up front
+
+    def update(self, key_states, value_states, *args, **kwargs):
+        """key_states, value_states [B, hkv, T, d] (keys after RoPE).  Appends; returns what the
+        attention function needs: the dense dequantized cache for T > 1, the tagged inputs for T = 1."""
+        B, hkv, T, d = key_states.shape
+        if B != self.batch:
+            raise ValueError(f"cache was built for batch {self.batch}, got {B}")
+        if self.cumulative_length + T > self.max_len:
+            raise ValueError(f"cache holds {self.max_len} positions, {self.cumulative_length + T} requested")
+        k = key_states.transpose(1, 2).contiguous()
+        v = value_states.transpose(1, 2).contiguous()
+        if self.kv.k_scale is not None and self.cumulative_length == 0:
+            self.kv.set_fp8_scales(k, v)        # amax/448 over the prompt, frozen for decode
+        self.kv.append(k, v)
+        self.seq_lens += T
+        self.cumulative_length += T
+        if T == 1:
+            key_states._tsb_layer = self        # the attention function reads the pages directly
+            return key_states, value_states
+        L = self.cumulative_length
+        kd, vd = ops.kv_gather(self.kv, L, dtype=key_states.dtype)
+        kd, vd = kd.transpose(1, 2), vd.transpose(1, 2)
+        kd._tsb_layer = self
+        return kd, vd
+
+    def get_mask_sizes(self, query_length):
+        return self.cumulative_length + query_length, 0
+
+    def get_seq_length(self):
+        return self.cumulative_length
+
+    def get_max_cache_shape(self):
+        return self.max_len
+
+    def reset(self):
+        self.seq_lens.zero_()
+        self.cumulative_length = 0
+
+
+class PagedQuantCache(Cache):
+    """`past_key_values` object backed by quantized paged pools, one `PagedCacheLayer` per decoder layer."""
+
+    def __init__(self, config, batch, max_len, kv_format="int8", device="cuda"):
+        if getattr(config, "_attn_implementation", None) != ATTN_NAME:
+            raise ValueError(f'set config._attn_implementation = "{ATTN_NAME}": other attention functions would '
+                             "see only the newest token on a decode step")
+        text = config.get_text_config() if hasattr(config, "get_text_config") else config
+        hkv = getattr(text, "num_key_value_heads", None) or text.num_attention_heads
+        head_dim = getattr(text, "head_dim", None) or text.hidden_size // text.num_attention_heads
+        device = torch.device(device)
+        layers = [PagedCacheLayer(kv_format, batch, max_len, hkv, head_dim, device) for _ in range(text.num_hidden_layers)]
+        super().__init__(layers=layers)
+
+
+def paged_attention_forward(module, query, key, value, attention_mask, dropout=0.0, scaling=None, **kwargs):
+    """Attention function for `ALL_ATTENTION_FUNCTIONS`: query [B, H, T, d] -> ([B, T, H, d], None)."""
+    layer = getattr(key, "_tsb_layer", None)
+    if layer is not None and query.shape[2] == 1 and key.shape[2] == 1:
+        q = query[:, :, 0, :].contiguous()
+        out = ops.paged_decode_attention(layer.kv, q, max_seq_len=layer.max_len, sm_scale=scaling)
+        return out[:, None], None
+    kwargs.pop("is_causal", None)
+    return sdpa_attention_forward(module, query, key, value, attention_mask, dropout=dropout, scaling=scaling, **kwargs)
+
+
+AttentionInterface.register(ATTN_NAME, paged_attention_forward)
+AttentionMaskInterface.register(ATTN_NAME, sdpa_mask)

@@ -51,7 +51,7 @@ def _token_strided(t, name):
     B, T, h, d = t.shape
     if t.numel() == 0:
         return h * d
-    if t.stride(3) != 1 or t.stride(2) != d:
+    if t.stride(3) != 1 or (h > 1 and t.stride(2) != d):     # the stride of a size-1 dimension is arbitrary
         raise ValueError(f"{name}: the (heads, d) block of a token must be dense")
     if T == 1:                       # decode: one token per sequence, spaced by the batch stride
         return t.stride(0) if B > 1 else h * d
@@ -322,6 +322,19 @@ class PagedKV:
         check(lib.tsb200_kv_append(C.byref(d), _p(k), _p(v), _dt(k), ks, vs, B, T, _p(new_lens),
                                    _p(cos), _p(sin), 0 if cos is None else cos.shape[0], _stream()),
               "tsb200_kv_append")
+
+
+def kv_gather(kv, L, dtype=torch.bfloat16, seq_lens=None):
+    """Dense dequantized copies k, v [B, L, hkv, d] of the first L cached positions of every
+    sequence (zeros beyond seq_lens[b]): what an attention over T > 1 query tokens reads."""
+    lib = _lib.load()
+    B = kv.block_table.shape[0]
+    dev = kv.k_pool.device
+    k = torch.empty((B, L, kv.hkv, kv.head_dim), dtype=dtype, device=dev)
+    v = torch.empty_like(k)
+    d = kv.desc(seq_lens)
+    check(lib.tsb200_kv_gather(C.byref(d), _p(k), _p(v), _dt(k), B, L, _stream()), "tsb200_kv_gather")
+    return k, v
 
 
 def decode_attn_workspace_bytes(B, H, head_dim, max_seq_len):
