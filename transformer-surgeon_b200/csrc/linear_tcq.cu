@@ -195,7 +195,8 @@ constexpr int kMaxPhases = 4;
 
 struct SubGemm {                 // one packed weight matrix and its operands
   CUtensorMap map_w;             // uint8 [N, row_bytes], box 128 rows x stage-row bytes, swizzled
-  CUtensorMap map_x;             // bf16 [M, K], box TN rows x 64, 128-byte swizzle
+  CUtensorMap map_x;             // bf16 [M, K]: box TN rows x 64, 128-byte swizzle; or (x3d) the 3-D view
+                                 //    [K/64][M][64] with box (64, TN, KBS): one copy per stage
   const float* scale;            // [N]
   const __nv_bfloat16* bias;     // [N] or null
   __nv_bfloat16* y;              // [M, N]
@@ -210,6 +211,7 @@ struct Phase {
   int n_tiles, m_tiles, items_per_sub, items;
   float* partial;                // split-K: fp32 slices [items][TN][128] of this phase
   int* counters;                 // split-K: zero-filled int32 [nsub * n_tiles * m_tiles], left zero
+  int x3d;                       // activations loaded with one 3-D box per stage (K a multiple of 64)
   int scatter;                   // split-K: 1 = every CTA holds at most one item of the phase and all CTAs are
                                  //    co-resident, so the CTAs of a tile wait for one another and each sums its
                                  //    share of the tile's columns; 0 = the last CTA to arrive sums the whole tile
@@ -338,9 +340,13 @@ linear_tcq_kernel(const __grid_constant__ Program prog) {
               }
               if (do_x) {
                 mbar_expect_tx(&x_full[s], (unsigned)L::kX);
+                if (ph.x3d) {                                 // k-blocks beyond K are zero-filled by the copy engine
+                  tma_load_3d(st, &sg.map_x, 0, it.mt * TN, it.kb0 + i, &x_full[s]);
+                } else {
 #pragma unroll
-                for (int j = 0; j < KBS; ++j)                 // columns beyond K are zero-filled by the copy engine
-                  tma_load_2d(st + j * L::kXTile, &sg.map_x, kcol + j * BK, it.mt * TN, &x_full[s]);
+                  for (int j = 0; j < KBS; ++j)               // columns beyond K are zero-filled by the copy engine
+                    tma_load_2d(st + j * L::kXTile, &sg.map_x, kcol + j * BK, it.mt * TN, &x_full[s]);
+                }
               }
               if (gs == 0 && do_w) TSB_STAMP(1);
             }
@@ -364,6 +370,13 @@ linear_tcq_kernel(const __grid_constant__ Program prog) {
         walk(ph, 0, NR, false, true);
         gs_phase0 = walk(ph, NR, 0x7fffffff, true, true);
         if (gs_phase0 < 0) break;
+#ifdef TSB_TRACE
+        if (p == 0 && prog.n_phases == 1) {     // true landing times of the first stages (single-phase runs)
+          TSB_FINE(256);
+          for (int q = 0; q < NR && q < gs_phase0; ++q) { mbar_wait(&w_full[q], 0, abort_flag, 1); TSB_FINE(260 + q); }
+          for (int q = 0; q < NR && q < gs_phase0; ++q) { mbar_wait(&x_full[q], 0, abort_flag, 1); TSB_FINE(280 + q); }
+        }
+#endif
       }
     }
   } else if (warp == 1 || warp == kIssuer1Warp) {
@@ -438,10 +451,10 @@ linear_tcq_kernel(const __grid_constant__ Program prog) {
           for (int jj = 0; jj < it.ns; ++jj, ++gs) {
             const int i = ((jj + it.rot) % it.ns) * KBS;
             const int s = gs % NR, buf = gs & 1;
-            ok = mbar_wait(&w_full[s], (gs / NR) & 1, abort_flag, 4);
+            ok = mbar_wait_relaxed(&w_full[s], (gs / NR) & 1, abort_flag, 4);
             if (threadIdx.x == 64) TSB_FINE(8 * gs + 2);
             // the A buffer is free once the MMAs of the stage two back are complete
-            if (ok && gs >= 2) ok = mbar_wait(&stage_done[(gs - 2) % NR], ((gs - 2) / NR) & 1, abort_flag, 5);
+            if (ok && gs >= 2) ok = mbar_wait_relaxed(&stage_done[(gs - 2) % NR], ((gs - 2) / NR) & 1, abort_flag, 5);
             if (!ok) break;
             if (threadIdx.x == 64) TSB_FINE(8 * gs + 3);
             if (gs == 0 && threadIdx.x == 64) TSB_STAMP(2);
@@ -464,7 +477,7 @@ linear_tcq_kernel(const __grid_constant__ Program prog) {
           }
         }
         if (!ok) break;
-        ok = mbar_wait(acc_full, it_count & 1, abort_flag, 6);
+        ok = mbar_wait_relaxed(acc_full, it_count & 1, abort_flag, 6);
         if (!ok) break;
         if (threadIdx.x == 64) TSB_STAMP(5);
         tc_fence_after();
@@ -726,14 +739,20 @@ int num_sms() {
   return sms[dev];
 }
 
-bool fill_sub(SubGemm& sg, const GemmSpec& g, int64_t M, int tn, int bits) {
+// k-blocks per stage: must equal QLayout<TN, BITS>::KBS
+int stage_kbs(int tn, int bits) { return raw_box_bytes(tn, bits) / (BK * bits / 8); }
+
+bool fill_sub(SubGemm& sg, const GemmSpec& g, int64_t M, int tn, int bits, bool x3d) {
   const uint64_t rb = tsb200_packed_row_bytes(g.K, bits);
   const int box = raw_box_bytes(tn, bits);
   const CUtensorMapSwizzle sw = box == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : (box == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B);
   if (!make_map(&sg.map_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, g.W, rb, (uint64_t)g.N, rb, (uint32_t)box, BM, sw)) return false;
-  if (!make_map(&sg.map_x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, g.x, (uint64_t)g.K, (uint64_t)M, (uint64_t)g.K * 2, BK, (uint32_t)tn,
-                CU_TENSOR_MAP_SWIZZLE_128B))
+  if (x3d) {
+    if (!make_map_x3d(&sg.map_x, g.x, (uint64_t)g.K, (uint64_t)M, (uint32_t)tn, (uint32_t)stage_kbs(tn, bits))) return false;
+  } else if (!make_map(&sg.map_x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, g.x, (uint64_t)g.K, (uint64_t)M, (uint64_t)g.K * 2, BK,
+                       (uint32_t)tn, CU_TENSOR_MAP_SWIZZLE_128B)) {
     return false;
+  }
   sg.scale = g.scale;
   sg.bias = (const __nv_bfloat16*)g.bias;
   sg.y = (__nv_bfloat16*)g.y;
@@ -776,9 +795,10 @@ int run_program_tcq(const PhaseSpec* specs, int n_phases, int bits, int64_t M, u
     ph.m_tiles = g.m_tiles;
     ph.items = g.items;
     ph.items_per_sub = ps.gated ? g.items : g.items / ps.nsub;
+    ph.x3d = (ph.K % BK == 0) ? 1 : 0;
     for (int j = 0; j < ps.nsub; ++j) {
       if (ps.g[j].N != ph.N || ps.g[j].K != ph.K) return TSB200_ERR_ARG;
-      if (!fill_sub(ph.sub[j], ps.g[j], M, g.tn, bits)) return TSB200_ERR_CUDA;
+      if (!fill_sub(ph.sub[j], ps.g[j], M, g.tn, bits, ph.x3d != 0)) return TSB200_ERR_CUDA;
     }
     const int tiles = ps.nsub * g.n_tiles * g.m_tiles;
     if (g.splits > 1 && ctr_off + tiles > kMaxCounters) return TSB200_ERR_UNSUPPORTED;

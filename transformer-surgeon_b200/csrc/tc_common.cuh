@@ -84,12 +84,31 @@ __device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned pari
   *abort_flag = code;
   return false;
 }
+// Same, for warps that are not on the critical path: sleeps between polls, so that many waiting warps do
+// not crowd the single lanes that issue copies and MMAs out of the issue slots and the memory pipeline.
+__device__ __forceinline__ bool mbar_wait_relaxed(unsigned long long* bar, unsigned parity, volatile int* abort_flag, int code) {
+  for (unsigned i = 0; i < kSpinLimit; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((i & 63u) == 63u && *abort_flag) return false;
+    __nanosleep(64);
+  }
+  *abort_flag = code;
+  return false;
+}
 
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, unsigned long long* bar) {
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n" ::"r"(
           smem_u32(dst)),
       "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar))
+      : "memory");
+}
+
+__device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, int x, int y, int z, unsigned long long* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];\n" ::"r"(
+          smem_u32(dst)),
+      "l"(map), "r"(x), "r"(y), "r"(z), "r"(smem_u32(bar))
       : "memory");
 }
 
@@ -177,6 +196,20 @@ inline bool make_map(CUtensorMap* map, CUtensorMapDataType dt, const void* base,
   cuuint32_t estr[2] = {1, 1};
   return fn(map, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swz,
             CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// bf16 activations x[M, K] (K a multiple of 64) viewed as [K/64 k-blocks][M rows][64 columns]: one box of
+// (64, box_rows, box_kb) lands as box_kb consecutive 128-byte-swizzled tiles of box_rows x 64.
+inline bool make_map_x3d(CUtensorMap* map, const void* base, uint64_t K, uint64_t M, uint32_t box_rows, uint32_t box_kb) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  cuuint64_t dims[3] = {64, M, K / 64};
+  cuuint64_t strides[2] = {K * 2, 128};
+  cuuint32_t box[3] = {64, box_rows, box_kb};
+  cuuint32_t estr[3] = {1, 1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
 }  // namespace tc
