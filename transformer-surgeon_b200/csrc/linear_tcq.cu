@@ -279,10 +279,7 @@ linear_tcq_kernel(const __grid_constant__ Program prog) {
 
   // Work enumeration, identical in every role.  Phase -> items (round-robin over CTAs) -> passes
   // (one per matrix the item touches: 2 for a gated item) -> stages of KBS k-blocks.
-  // ns = stages of the item's K range; the item walks them starting at stage `rot` and wrapping
-  // around, so CTAs that share a K range (same split, different weight tiles) do not all request
-  // the same activation lines from L2 at the same moment.
-  struct Item { int sub, nt, mt, kb0, nkb, ns, rot; };
+  struct Item { int sub, nt, mt, kb0, nkb, ns; };        // ns = stages of the item's K range
   auto decode = [&](const Phase& ph, int item) {
     Item it;
     int local = item;
@@ -295,7 +292,6 @@ linear_tcq_kernel(const __grid_constant__ Program prog) {
     it.kb0 = sp * ph.kb_per_split;
     it.nkb = min(ph.kb_per_split, ph.kb_total - it.kb0);
     it.ns = (it.nkb + KBS - 1) / KBS;
-    it.rot = it.nt % it.ns;
     return it;
   };
 
@@ -326,7 +322,7 @@ linear_tcq_kernel(const __grid_constant__ Program prog) {
           for (int ps = 0; ps < passes; ++ps) {
             const SubGemm& sg = ph.sub[ph.gated ? ps : it.sub];
             for (int jj = 0; jj < it.ns; ++jj, ++gs) {
-              const int i = ((jj + it.rot) % it.ns) * KBS;
+              const int i = jj * KBS;
               const int rel = gs - gs_phase0;
               if (rel >= rel_end) return gs;
               if (rel < rel_begin) continue;
@@ -356,20 +352,26 @@ linear_tcq_kernel(const __grid_constant__ Program prog) {
       };
       for (int p = 0; p < prog.n_phases && ok; ++p) {
         const Phase& ph = prog.ph[p];
-        walk(ph, 0, NR, true, false);
-        TSB_STAMP_P(p, 0);
-        prefetch_maps(p + 1);
-        if (p == 0) {
-          pdl_wait();
-        } else {
-          ok = ok && grid_wait(&prog.grid_bar[p - 1], (int)gridDim.x, abort_flag);
-          asm volatile("fence.proxy.async;\n" ::: "memory");  // other CTAs' stores -> visible to the copy engine
+        // three passes over the phase's stages (one inlined copy of the walk): weights of the first NR
+        // stages; after the dependency wait their activations; then everything else
+#pragma unroll 1
+        for (int pass = 0; pass < 3 && ok; ++pass) {
+          if (pass == 1) {
+            TSB_STAMP_P(p, 0);
+            prefetch_maps(p + 1);
+            if (p == 0) {
+              pdl_wait();
+            } else {
+              ok = ok && grid_wait(&prog.grid_bar[p - 1], (int)gridDim.x, abort_flag);
+              asm volatile("fence.proxy.async;\n" ::: "memory");  // other CTAs' stores -> visible to the copy engine
+            }
+            if (!ok) break;
+            TSB_STAMP_P(p, 1);
+          }
+          const int gs_end = walk(ph, pass == 2 ? NR : 0, pass == 2 ? 0x7fffffff : NR, pass != 1, pass != 0);
+          if (pass == 2) gs_phase0 = gs_end;
         }
-        if (!ok) break;
-        TSB_STAMP_P(p, 1);
-        walk(ph, 0, NR, false, true);
-        gs_phase0 = walk(ph, NR, 0x7fffffff, true, true);
-        if (gs_phase0 < 0) break;
+        if (!ok || gs_phase0 < 0) break;
 #ifdef TSB_TRACE
         if (p == 0 && prog.n_phases == 1) {     // true landing times of the first stages (single-phase runs)
           TSB_FINE(256);
@@ -396,7 +398,7 @@ linear_tcq_kernel(const __grid_constant__ Program prog) {
             const unsigned d_tmem = tmem_base + (unsigned)((ph.gated ? 2 * (two ? me : 0) + ps : (two ? me : 0)) * TN);
             bool first = true;                                // the chain's first MMA of the pass overwrites
             for (int jj = 0; jj < it.ns; ++jj, ++gs) {
-              const int i = ((jj + it.rot) % it.ns) * KBS;
+              const int i = jj * KBS;
               const int s = gs % NR, buf = gs & 1;
               ok = mbar_wait(&x_full[s], (gs / NR) & 1, abort_flag, 2);
               if (me == 0) TSB_FINE(8 * gs + 6);
@@ -449,7 +451,7 @@ linear_tcq_kernel(const __grid_constant__ Program prog) {
         }
         for (int ps = 0; ps < passes && ok; ++ps) {
           for (int jj = 0; jj < it.ns; ++jj, ++gs) {
-            const int i = ((jj + it.rot) % it.ns) * KBS;
+            const int i = jj * KBS;
             const int s = gs % NR, buf = gs & 1;
             ok = mbar_wait_relaxed(&w_full[s], (gs / NR) & 1, abort_flag, 4);
             if (threadIdx.x == 64) TSB_FINE(8 * gs + 2);
