@@ -119,3 +119,43 @@ def test_pack_model_rebinds_per_instance(cuda):
     surgeon.unpack_model(net)
     assert "forward" not in net[0].__dict__ and not hasattr(net[0], "_tsb200")
     assert torch.equal(net(x), ref)
+
+
+def test_packed_state_round_trip(cuda, tmp_path):
+    """Packed codes and scales survive a save / load through plain tensors: the reloaded layers hold
+    byte-identical containers and give bit-identical outputs, with the float weights never read."""
+    from transformer_surgeon_b200 import surgeon, ops
+
+    class LinearCompressed(torch.nn.Linear):
+        def __init__(self, i, o, bias=True, rank=None):
+            super().__init__(i, o, bias=bias)
+            self.skip, self.rank, self.linear_V = False, ("full" if rank is None else rank), None
+            if isinstance(rank, int):
+                self.linear_V = torch.nn.Linear(i, rank, bias=False)
+                self.weight = torch.nn.Parameter(torch.randn(o, rank) * 0.1)
+
+    def build():
+        torch.manual_seed(1)
+        net = torch.nn.Sequential(LinearCompressed(128, 256, rank=64), LinearCompressed(256, 128, bias=False)).to(cuda).bfloat16()
+        net.config = type("Cfg", (), {})()
+        net.config.compression_config = {"0": {"quantization": {"precision": 4, "granularity": "per_channel", "eps": 1e-6}},
+                                         "1": {"quantization": {"precision": 8, "granularity": "per_channel", "eps": 1e-6}}}
+        return net
+
+    net = build()
+    assert surgeon.pack_model(net, cuda) == 2
+    x = torch.randn(16, 128, device=cuda).bfloat16()
+    y = net[1](net[0](x))
+    torch.save(surgeon.packed_state_dict(net), tmp_path / "packed.pt")
+    other = build()
+    for prm in other.parameters():                      # the float weights must not matter after loading
+        prm.data.zero_()
+    assert surgeon.load_packed_state_dict(other, torch.load(tmp_path / "packed.pt"), cuda) == 2
+    for a, b in zip(net, other):
+        assert torch.equal(a._tsb200.u.data, b._tsb200.u.data) and torch.equal(a._tsb200.u.scales, b._tsb200.u.scales)
+        assert a._tsb200.u.bits == b._tsb200.u.bits
+    assert torch.equal(other[1](other[0](x)), y)
+    bad = surgeon.packed_state_dict(net)
+    bad["0._tsb200.u.data"] = bad["0._tsb200.u.data"][:, :-4]
+    with pytest.raises(ValueError):
+        surgeon.load_packed_state_dict(build(), bad, cuda)

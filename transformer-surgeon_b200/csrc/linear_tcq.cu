@@ -309,76 +309,76 @@ linear_tcq_kernel(const __grid_constant__ Program prog) {
       };
       // The packed weights are constants: for the first NR stages of a phase their boxes are
       // requested BEFORE the phase's activations exist (before the wait on the preceding kernel
-      // for phase 0, before the grid barrier for later phases); the activation tiles follow.  The
-      // two kinds of data complete separate barriers, so the dequant warps already fill both A
-      // buffers of the next phase while the barrier is pending.
+      // for phase 0, before the grid barrier for later phases) and the matching activation loads are
+      // only noted down; once the dependency is met they are fired from that list - a handful of
+      // instructions on the critical path.  The two kinds of data complete separate barriers, so the
+      // dequant warps already fill both A buffers of the next phase while the barrier is pending.
+      struct Pending { const CUtensorMap* map; int y, kb, s; };
+      Pending pend[NR];
       bool ok = true;
-      int gs_phase0 = 0;                                      // stage counter at the start of the phase
-      auto walk = [&](const Phase& ph, int rel_begin, int rel_end, bool do_w, bool do_x) -> int {
-        int gs = gs_phase0;                                   // absolute stage counter
-        for (int item = blockIdx.x; item < ph.items && ok; item += gridDim.x) {
-          const Item it = decode(ph, item);
-          const int passes = ph.gated ? 2 : 1;
-          for (int ps = 0; ps < passes; ++ps) {
-            const SubGemm& sg = ph.sub[ph.gated ? ps : it.sub];
-            for (int jj = 0; jj < it.ns; ++jj, ++gs) {
-              const int i = jj * KBS;
-              const int rel = gs - gs_phase0;
-              if (rel >= rel_end) return gs;
-              if (rel < rel_begin) continue;
-              const int s = gs % NR;
-              uint8_t* st = r_ring + s * L::kStage;
-              const int kcol = (it.kb0 + i) * BK;
-              if (do_w) {                                     // the stage is free once its previous user is done
-                if (gs >= NR && !mbar_wait(&stage_done[s], ((gs / NR) - 1) & 1, abort_flag, 1)) { ok = false; return gs; }
-                mbar_expect_tx(&w_full[s], (unsigned)L::kRaw);
-                tma_load_2d(st + L::kX, &sg.map_w, kcol * BITS / 8, it.nt * BM, &w_full[s]);
-              }
-              if (do_x) {
-                mbar_expect_tx(&x_full[s], (unsigned)L::kX);
-                if (ph.x3d) {                                 // k-blocks beyond K are zero-filled by the copy engine
-                  tma_load_3d(st, &sg.map_x, 0, it.mt * TN, it.kb0 + i, &x_full[s]);
-                } else {
-#pragma unroll
-                  for (int j = 0; j < KBS; ++j)               // columns beyond K are zero-filled by the copy engine
-                    tma_load_2d(st + j * L::kXTile, &sg.map_x, kcol + j * BK, it.mt * TN, &x_full[s]);
-                }
-              }
-              if (gs == 0 && do_w) TSB_STAMP(1);
-            }
-          }
-        }
-        return gs;
-      };
+      int gs = 0;                                             // absolute stage counter
+#pragma unroll 1
       for (int p = 0; p < prog.n_phases && ok; ++p) {
         const Phase& ph = prog.ph[p];
-        // three passes over the phase's stages (one inlined copy of the walk): weights of the first NR
-        // stages; after the dependency wait their activations; then everything else
+        const int passes = ph.gated ? 2 : 1;
+        int npend = 0;
+        bool released = false;                                // activations of this phase may be read
+        int item = blockIdx.x, ps = 0, jj = 0;
+        Item it = decode(ph, item < ph.items ? item : 0);
 #pragma unroll 1
-        for (int pass = 0; pass < 3 && ok; ++pass) {
-          if (pass == 1) {
+        while (ok) {
+          const bool end = item >= ph.items;
+          if (!released && (npend == NR || end)) {
             TSB_STAMP_P(p, 0);
             prefetch_maps(p + 1);
             if (p == 0) {
               pdl_wait();
             } else {
-              ok = ok && grid_wait(&prog.grid_bar[p - 1], (int)gridDim.x, abort_flag);
+              ok = grid_wait(&prog.grid_bar[p - 1], (int)gridDim.x, abort_flag);
               asm volatile("fence.proxy.async;\n" ::: "memory");  // other CTAs' stores -> visible to the copy engine
             }
-            if (!ok) break;
             TSB_STAMP_P(p, 1);
+            released = true;
+            if (!ok) break;
           }
-          const int gs_end = walk(ph, pass == 2 ? NR : 0, pass == 2 ? 0x7fffffff : NR, pass != 1, pass != 0);
-          if (pass == 2) gs_phase0 = gs_end;
+          if (released) {                                     // fire the noted activation loads
+#pragma unroll 1
+            for (int q = 0; q < npend; ++q) {
+              const int s = pend[q].s;
+              uint8_t* st = r_ring + s * L::kStage;
+              mbar_expect_tx(&x_full[s], (unsigned)L::kX);
+              if (ph.x3d) {                                   // k-blocks beyond K are zero-filled by the copy engine
+                tma_load_3d(st, pend[q].map, 0, pend[q].y, pend[q].kb, &x_full[s]);
+              } else {
+#pragma unroll 1
+                for (int j = 0; j < KBS; ++j)                 // columns beyond K are zero-filled by the copy engine
+                  tma_load_2d(st + j * L::kXTile, pend[q].map, (pend[q].kb + j) * BK, pend[q].y, &x_full[s]);
+              }
+            }
+            npend = 0;
+          }
+          if (end) break;
+          {
+            const SubGemm& sg = ph.sub[ph.gated ? ps : it.sub];
+            const int s = gs % NR, kb = it.kb0 + jj * KBS;
+            // the stage is free once its previous user's MMAs are complete
+            if (gs >= NR && !mbar_wait(&stage_done[s], ((gs / NR) - 1) & 1, abort_flag, 1)) { ok = false; break; }
+            mbar_expect_tx(&w_full[s], (unsigned)L::kRaw);
+            tma_load_2d(r_ring + s * L::kStage + L::kX, &sg.map_w, kb * (BK * BITS / 8), it.nt * BM, &w_full[s]);
+            if (gs == 0) TSB_STAMP(1);
+            pend[npend].map = &sg.map_x; pend[npend].y = it.mt * TN; pend[npend].kb = kb; pend[npend].s = s;
+            ++npend;
+          }
+          ++gs;
+          if (++jj == it.ns) {
+            jj = 0;
+            if (++ps == passes) {
+              ps = 0;
+              item += gridDim.x;
+              if (item < ph.items) it = decode(ph, item);
+            }
+          }
         }
-        if (!ok || gs_phase0 < 0) break;
-#ifdef TSB_TRACE
-        if (p == 0 && prog.n_phases == 1) {     // true landing times of the first stages (single-phase runs)
-          TSB_FINE(256);
-          for (int q = 0; q < NR && q < gs_phase0; ++q) { mbar_wait(&w_full[q], 0, abort_flag, 1); TSB_FINE(260 + q); }
-          for (int q = 0; q < NR && q < gs_phase0; ++q) { mbar_wait(&x_full[q], 0, abort_flag, 1); TSB_FINE(280 + q); }
-        }
-#endif
       }
     }
   } else if (warp == 1 || warp == kIssuer1Warp) {

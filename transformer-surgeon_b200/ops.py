@@ -162,6 +162,29 @@ class Factor:
     def codes(self):
         return unpack_codes(self.data, self.rows, self.cols, self.bits)
 
+    def state(self, prefix=""):
+        """Tensors that rebuild this factor without re-quantizing: the packed container (or dense
+        matrix), the row scales and a meta vector [bits, rows, cols]."""
+        d = {prefix + "data": self.data, prefix + "meta": torch.tensor([self.bits, self.rows, self.cols], dtype=torch.int64)}
+        if self.scales is not None:
+            d[prefix + "scales"] = self.scales
+        return d
+
+    @staticmethod
+    def from_state(sd, prefix="", device="cuda"):
+        bits, rows, cols = (int(v) for v in sd[prefix + "meta"].tolist())
+        data = sd[prefix + "data"].to(device).contiguous()
+        scales = sd.get(prefix + "scales")
+        if bits >= 16:
+            if tuple(data.shape) != (rows, cols):
+                raise ValueError("dense factor: shape does not match its meta record")
+            return Factor(data, None, bits, rows, cols)
+        if data.dtype != torch.uint8 or tuple(data.shape) != (rows, packed_row_bytes(cols, bits)):
+            raise ValueError("packed factor: container shape does not match its meta record")
+        if scales is None or scales.numel() != rows:
+            raise ValueError("packed factor: one fp32 scale per row is required")
+        return Factor(data, scales.to(device=device, dtype=torch.float32).contiguous(), bits, rows, cols)
+
     def reconstruct(self, dtype):
         if self.bits >= 16:
             return self.data
@@ -206,6 +229,25 @@ class PackedLinear:
 
     def workspace_bytes(self, M):
         return int(_lib.load().tsb200_linear_workspace_bytes(C.byref(self.desc), M))
+
+    def state(self, prefix=""):
+        """Flat dict of tensors (torch.save / safetensors friendly) that `from_state` turns back into
+        the same layer: codes and scales are stored, never re-derived."""
+        d = self.u.state(prefix + "u.")
+        if self.v is not None:
+            d.update(self.v.state(prefix + "v."))
+        if self.bias is not None:
+            d[prefix + "bias"] = self.bias
+        d[prefix + "act_bf16"] = torch.tensor([1 if self.act_dtype == torch.bfloat16 else 0], dtype=torch.int64)
+        return d
+
+    @staticmethod
+    def from_state(sd, prefix="", device="cuda"):
+        act = torch.bfloat16 if int(sd[prefix + "act_bf16"].item()) else torch.float32
+        u = Factor.from_state(sd, prefix + "u.", device)
+        v = Factor.from_state(sd, prefix + "v.", device) if prefix + "v.meta" in sd else None
+        bias = sd.get(prefix + "bias")
+        return PackedLinear(u, v, None if bias is None else bias.to(device), act)
 
     def __call__(self, x, out=None, ws=None):
         lib = _lib.load()

@@ -131,6 +131,38 @@ def pack_model(model, device="cuda"):
     return n
 
 
+PACKED_KEY = "._tsb200."
+
+
+def packed_state_dict(model):
+    """Packed codes, scales and biases of every packed LinearCompressed of `model` as a flat dict of
+    CPU tensors keyed `<module path>._tsb200.<field>` - extra entries for a checkpoint, so that
+    loading does not need the pack step (the reference re-creates factorised modules from
+    `config.compression_config` on load, utils/modeling.py:65-77, but discards quantization codes)."""
+    sd = {}
+    for path, m in model.named_modules():
+        if hasattr(m, "_tsb200"):
+            for k, t in m._tsb200.state(path + PACKED_KEY).items():
+                sd[k] = t.detach().cpu()
+    return sd
+
+
+def load_packed_state_dict(model, sd, device="cuda"):
+    """Attach kernels from `packed_state_dict` output; the modules' float weights are not read.
+    Returns the number of modules attached; a LinearCompressed without an entry is left alone."""
+    n = 0
+    for path, m in model.named_modules():
+        if not _is_linear_compressed(m) or (path + PACKED_KEY + "u.meta") not in sd:
+            continue
+        p = ops.PackedLinear.from_state(sd, path + PACKED_KEY, device)
+        if p.out_features != m.weight.shape[0] or p.in_features != (m.linear_V.weight.shape[1] if p.v is not None else m.weight.shape[1]):
+            raise ValueError(f"{path}: packed entry is {p.out_features}x{p.in_features}, module differs")
+        m._tsb200 = p
+        m.forward = types.MethodType(_packed_forward, m)
+        n += 1
+    return n
+
+
 def unpack_model(model):
     for _, m in model.named_modules():
         if hasattr(m, "_tsb200"):
