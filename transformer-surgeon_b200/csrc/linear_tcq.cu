@@ -248,11 +248,12 @@ linear_tcq_kernel(const __grid_constant__ Program prog) {
   uint8_t* r_ring = smem;                                   // NR x {KBS activation tiles, raw codes}
   unsigned long long* bars = reinterpret_cast<unsigned long long*>(r_ring + NR * L::kStage);
   unsigned long long* w_full = bars;                        // [NR] weight box landed (the dequant warps wait on it)
-  unsigned long long* x_full = bars + NR;                   // [NR] activation tiles landed (the MMA lane waits on it)
+  unsigned long long* x_full = bars + NR;                   // [NR] stage ready for the MMA lanes: activation tiles landed
+                                                            //      (one arrival + bytes) AND the 8 dequant warps stored
+                                                            //      its A operand - one wait per stage for the issuers
   unsigned long long* stage_done = bars + 2 * NR;           // [NR] MMA commit: the stage's MMAs are complete, so its
                                                             //      weight box, activation tiles and A buffer are free
-  unsigned long long* a_ready = bars + 3 * NR;              // [2]  8 dequant warps: A buffer stored in TMEM
-  unsigned long long* acc_full = a_ready + 2;               // [1]  MMA commit: accumulator(s) of the item complete
+  unsigned long long* acc_full = bars + 3 * NR;             // [1]  MMA commit: accumulator(s) of the item complete
   unsigned long long* ep_bar = acc_full + 1;                // [1]  rendezvous of the 8 warps
   unsigned* tmem_slot = reinterpret_cast<unsigned*>(ep_bar + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -262,8 +263,7 @@ linear_tcq_kernel(const __grid_constant__ Program prog) {
   pdl_launch_dependents();
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < NR; ++i) { mbar_init(&w_full[i], 1); mbar_init(&x_full[i], 1); mbar_init(&stage_done[i], 2); }
-    for (int i = 0; i < 2; ++i) mbar_init(&a_ready[i], kDqWarps);
+    for (int i = 0; i < NR; ++i) { mbar_init(&w_full[i], 1); mbar_init(&x_full[i], 1 + kDqWarps); mbar_init(&stage_done[i], 2); }
     mbar_init(acc_full, 2);                                 // both issuers commit, with or without MMAs of their own
     mbar_init(ep_bar, kDqWarps);
     *abort_flag = 0;
@@ -401,8 +401,6 @@ linear_tcq_kernel(const __grid_constant__ Program prog) {
               const int i = jj * KBS;
               const int s = gs % NR, buf = gs & 1;
               ok = mbar_wait(&x_full[s], (gs / NR) & 1, abort_flag, 2);
-              if (me == 0) TSB_FINE(8 * gs + 6);
-              ok = ok && mbar_wait(&a_ready[buf], (gs >> 1) & 1, abort_flag, 3);
               if (!ok) break;
               if (me == 0) TSB_FINE(8 * gs + 0);
               tc_fence_after();
@@ -474,7 +472,7 @@ linear_tcq_kernel(const __grid_constant__ Program prog) {
             if (lane == 0 && gs < 8) { TSB_FINE(128 + 8 * gs + (warp - 2)); }
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(&a_ready[buf]);
+            if (lane == 0) mbar_arrive(&x_full[s]);
             if (threadIdx.x == 64) { if (gs == 0) TSB_STAMP(3); if (item == blockIdx.x && ps == 0 && jj == 0) TSB_STAMP_P(p, 2); }
           }
         }
