@@ -38,11 +38,12 @@ constexpr int kThreadsQ = 64 + kDqWarps * 32 + 32;   // producer, MMA issuer 0, 
 constexpr int kIssuer1Warp = 2 + kDqWarps;
 constexpr int kSmemBudget = 208 * 1024;
 constexpr unsigned kTmemCols = 512;
-constexpr unsigned kACol0 = 128;            // TMEM column of A buffer 0; buffer 1 follows at +128
 
 template <int TN, int BITS> struct QLayout {
   static constexpr int kKbsFull = 1024 / BITS / BK;        // k-blocks in a 128-byte row of codes
-  static constexpr int kKbsCap = TN <= 32 ? 4 : 2;         // A buffer = KBS * 32 TMEM columns <= 128
+  // A buffer = KBS * 32 TMEM columns <= 128; the 256-token tile keeps one k-block (32 KB of activations) per stage
+  static constexpr int kKbsCap = TN <= 32 ? 4 : (TN <= 128 ? 2 : 1);
+  static constexpr unsigned kACol0 = TN > 128 ? 256 : 128;  // TMEM column of A buffer 0 (accumulators sit below); buffer 1 at +128
   static constexpr int KBS = kKbsFull < kKbsCap ? kKbsFull : kKbsCap;
   static constexpr int kRawRow = BK * BITS / 8;            // bytes of one weight row per k-block
   static constexpr int kRawStageRow = KBS * kRawRow;       // bytes of one weight row per stage (32/64/128)
@@ -80,7 +81,7 @@ __device__ __forceinline__ uint2 lds64(unsigned addr) {
 // so threads reading the same chunk of consecutive rows hit different banks.
 template <int RB>
 __device__ __forceinline__ unsigned raw_chunk(unsigned raw, int row, int chunk) {
-  const int x = RB == 128 ? (row & 7) : (RB == 64 ? ((row >> 1) & 3) : ((row >> 2) & 1));
+  const int x = RB == 128 ? (row & 7) : (RB == 64 ? ((row >> 1) & 3) : (RB == 32 ? ((row >> 2) & 1) : 0));   // 16-byte rows: no swizzle
   return raw + row * RB + ((chunk ^ x) << 4);
 }
 
@@ -404,7 +405,7 @@ linear_tcq_kernel(const __grid_constant__ Program prog) {
               if (!ok) break;
               if (me == 0) TSB_FINE(8 * gs + 0);
               tc_fence_after();
-              const unsigned a_tmem = tmem_base + kACol0 + buf * 128;
+              const unsigned a_tmem = tmem_base + L::kACol0 + buf * 128;
               const unsigned x_base = smem_u32(r_ring + s * L::kStage);
               const int nsub = min(KBS, it.nkb - i);
               for (int j = two ? me : 0; j < nsub && (two || me == 0); j += two ? 2 : 1) {
@@ -464,7 +465,7 @@ linear_tcq_kernel(const __grid_constant__ Program prog) {
             for (int j = grp; j < nsub; j += 2) {              // both groups work on the stage: half the latency
               unsigned regs[32];
               dequant_row_regs<BITS, L::kRawStageRow>(raw, row, j, regs);
-              tmem_st32(lane_addr + kACol0 + buf * 128 + j * 32, regs);
+              tmem_st32(lane_addr + L::kACol0 + buf * 128 + j * 32, regs);
             }
             if (threadIdx.x == 64) TSB_FINE(8 * gs + 4);
             tmem_st_wait();
@@ -722,7 +723,7 @@ int launch_q_bits(int bits, const Program& prog, int grid, bool coresident, cuda
 // Inner extent (bytes) of the weight box: must equal QLayout<TN, BITS>::kRawStageRow.
 int raw_box_bytes(int tn, int bits) {
   const int full = 1024 / bits / BK;
-  const int cap = tn <= 32 ? 4 : 2;
+  const int cap = tn <= 32 ? 4 : (tn <= 128 ? 2 : 1);
   const int kbs = full < cap ? full : cap;
   return kbs * BK * bits / 8;
 }
@@ -745,7 +746,8 @@ int stage_kbs(int tn, int bits) { return raw_box_bytes(tn, bits) / (BK * bits / 
 bool fill_sub(SubGemm& sg, const GemmSpec& g, int64_t M, int tn, int bits, bool x3d) {
   const uint64_t rb = tsb200_packed_row_bytes(g.K, bits);
   const int box = raw_box_bytes(tn, bits);
-  const CUtensorMapSwizzle sw = box == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : (box == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B);
+  const CUtensorMapSwizzle sw = box == 128 ? CU_TENSOR_MAP_SWIZZLE_128B
+                                : (box == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : (box == 32 ? CU_TENSOR_MAP_SWIZZLE_32B : CU_TENSOR_MAP_SWIZZLE_NONE));
   if (!make_map(&sg.map_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, g.W, rb, (uint64_t)g.N, rb, (uint32_t)box, BM, sw)) return false;
   if (x3d) {
     if (!make_map_x3d(&sg.map_x, g.x, (uint64_t)g.K, (uint64_t)M, (uint32_t)tn, (uint32_t)stage_kbs(tn, bits))) return false;
