@@ -43,7 +43,7 @@ template <int TN, int BITS> struct QLayout {
   static constexpr int kKbsFull = 1024 / BITS / BK;        // k-blocks in a 128-byte row of codes
   // A buffer = KBS * 32 TMEM columns <= 128; the 256-token tile keeps one k-block (32 KB of activations) per stage
   static constexpr int kKbsCap = TN <= 32 ? 4 : (TN <= 128 ? 2 : 1);
-  static constexpr unsigned kACol0 = TN > 128 ? 256 : 128;  // TMEM column of A buffer 0 (accumulators sit below); buffer 1 at +128
+  static constexpr unsigned kACol0 = 256;                   // TMEM column of A buffer 0 (accumulators sit below); buffer 1 at +128
   static constexpr int KBS = kKbsFull < kKbsCap ? kKbsFull : kKbsCap;
   static constexpr int kRawRow = BK * BITS / 8;            // bytes of one weight row per k-block
   static constexpr int kRawStageRow = KBS * kRawRow;       // bytes of one weight row per stage (32/64/128)
@@ -55,14 +55,18 @@ template <int TN, int BITS> struct QLayout {
   static constexpr int NR = kNRraw > 12 ? 12 : kNRraw;
   static constexpr int kBarBytes = 1024;
   static constexpr int kBytes = NR * kStage + kBarBytes + 1024;
-  // One lane needs ~80-100 cycles to issue one tcgen05.mma (operand set-up on the uniform datapath),
-  // far longer than a narrow MMA runs.  Two lanes of different warps therefore issue the even and the
-  // odd k-blocks of every stage into two separate accumulator CHAINS (MMAs of different threads are not
-  // ordered, so they must not share an accumulator); the epilogue adds the chains.  Accumulators own
-  // tensor-memory columns [0, 128): chain c of a plain item at c * TN; of a gated item gate at
-  // (2 c) * TN and up at (2 c + 1) * TN.
-  static constexpr bool kTwoChains = KBS >= 2 && 2 * TN <= 128;
-  static constexpr bool kTwoChainsGated = KBS >= 2 && 4 * TN <= 128;
+  // The tensor pipe needs ~55 + N/2 cycles per tcgen05.mma (the A operand is read from tensor memory), and
+  // the lane that issues them spends another ~300-400 cycles per stage between its last MMA and the next
+  // stage's first (commit, wait, descriptors) during which the pipe would idle.  Two lanes of different warps
+  // therefore issue ALTERNATE STAGES, so one lane's gap hides behind the other's MMAs.  MMAs of different
+  // threads are not ordered, so each lane accumulates into its own CHAIN (accumulator) and the epilogue adds
+  // the chains.  Accumulators own tensor-memory columns [0, 256): chain c of a plain item at c * TN; of a
+  // gated item gate at (2 c) * TN and up at (2 c + 1) * TN.
+  // Narrow token tiles (decode: items of one to a few stages, 4 k-blocks per stage) instead split every stage
+  // between the lanes by k-block parity, which also halves the latency of a single-stage item.
+  static constexpr bool kTwoChains = 2 * TN <= 256;
+  static constexpr bool kTwoChainsGated = 4 * TN <= 256;
+  static constexpr bool kSplitStage = TN <= 32 && KBS >= 2;
 };
 
 __device__ __forceinline__ uint4 lds128(unsigned addr) {
@@ -264,7 +268,7 @@ linear_tcq_kernel(const __grid_constant__ Program prog) {
   pdl_launch_dependents();
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < NR; ++i) { mbar_init(&w_full[i], 1); mbar_init(&x_full[i], 1 + kDqWarps); mbar_init(&stage_done[i], 2); }
+    for (int i = 0; i < NR; ++i) { mbar_init(&w_full[i], 1); mbar_init(&x_full[i], 1 + kDqWarps); mbar_init(&stage_done[i], L::kSplitStage ? 2 : 1); }
     mbar_init(acc_full, 2);                                 // both issuers commit, with or without MMAs of their own
     mbar_init(ep_bar, kDqWarps);
     *abort_flag = 0;
@@ -385,7 +389,7 @@ linear_tcq_kernel(const __grid_constant__ Program prog) {
   } else if (warp == 1 || warp == kIssuer1Warp) {
     // ---------------------------------------------------------------- MMA issuers
     if (lane == 0) {
-      const int me = warp == 1 ? 0 : 1;                       // issuer 0: even k-blocks / chain 0; issuer 1: odd / chain 1
+      const int me = warp == 1 ? 0 : 1;                       // issuer 0: even stages / chain 0; issuer 1: odd stages / chain 1
       constexpr unsigned idesc = idesc_bf16(TN);
       int gs = 0;
       bool ok = true;
@@ -399,16 +403,18 @@ linear_tcq_kernel(const __grid_constant__ Program prog) {
             const unsigned d_tmem = tmem_base + (unsigned)((ph.gated ? 2 * (two ? me : 0) + ps : (two ? me : 0)) * TN);
             bool first = true;                                // the chain's first MMA of the pass overwrites
             for (int jj = 0; jj < it.ns; ++jj, ++gs) {
+              if (!L::kSplitStage && (two ? (gs & 1) != me : me != 0)) continue;     // the other lane's stage
               const int i = jj * KBS;
               const int s = gs % NR, buf = gs & 1;
               ok = mbar_wait(&x_full[s], (gs / NR) & 1, abort_flag, 2);
               if (!ok) break;
-              if (me == 0) TSB_FINE(8 * gs + 0);
+              TSB_FINE(8 * gs + 0);
               tc_fence_after();
               const unsigned a_tmem = tmem_base + L::kACol0 + buf * 128;
               const unsigned x_base = smem_u32(r_ring + s * L::kStage);
               const int nsub = min(KBS, it.nkb - i);
-              for (int j = two ? me : 0; j < nsub && (two || me == 0); j += two ? 2 : 1) {
+              const bool halves = L::kSplitStage && two;      // this lane takes the k-blocks of its parity
+              for (int j = halves ? me : 0; j < nsub && (!L::kSplitStage || two || me == 0); j += halves ? 2 : 1) {
                 const unsigned long long bdesc = smem_desc_sw128(x_base + j * L::kXTile);
 #pragma unroll
                 for (int k = 0; k < BK / 16; ++k) { // A: 8 TMEM columns per K=16; B: +32 bytes inside the swizzle atom
@@ -416,8 +422,8 @@ linear_tcq_kernel(const __grid_constant__ Program prog) {
                   first = false;
                 }
               }
-              umma_commit(&stage_done[s]);                     // arrives once this lane's MMAs (if any) are complete
-              if (me == 0) TSB_FINE(8 * gs + 1);
+              umma_commit(&stage_done[s]);                     // arrives once the stage's MMAs are complete
+              TSB_FINE(8 * gs + 1);
             }
           }
           if (ok) umma_commit(acc_full);
@@ -486,16 +492,22 @@ linear_tcq_kernel(const __grid_constant__ Program prog) {
         const int64_t m0 = (int64_t)it.mt * TN;
         const bool split = ph.splits > 1;
         constexpr int CH = TN / 2;                           // token columns handled by this warp
-        // second accumulator chain: present when the phase runs two issuers and the item has >= 2 k-blocks
-        const bool chain2 = (ph.gated ? L::kTwoChainsGated : L::kTwoChains) && it.nkb >= 2;
+        // accumulator chains: with two issuers chain c holds the stages of parity c; a pass of a single stage
+        // leaves the other chain unwritten.  g0 = first stage of the (gate) pass, g0u = of the up pass.
+        const bool two = ph.gated ? L::kTwoChainsGated : L::kTwoChains;
+        const int g0 = gs - passes * it.ns, g0u = gs - it.ns;
+        const bool v0 = L::kSplitStage || !two || it.ns >= 2 || (g0 & 1) == 0;
+        const bool v1 = two && (L::kSplitStage ? it.nkb >= 2 : (it.ns >= 2 || (g0 & 1) == 1));
+        const bool u0 = L::kSplitStage || !two || it.ns >= 2 || (g0u & 1) == 0;
+        const bool u1 = two && (L::kSplitStage ? it.nkb >= 2 : (it.ns >= 2 || (g0u & 1) == 1));
         const unsigned acc1 = (unsigned)((ph.gated ? 2 : 1) * TN);   // column offset of chain 1
         float* slice = ph.partial + (size_t)item * (TN * BM);
         __nv_bfloat16* y = sg0.y;
 #pragma unroll 1
         for (int c0 = grp * CH; c0 < (grp + 1) * CH; c0 += 8) {
           unsigned r[8];
-          tmem_ld8(lane_addr + (unsigned)c0, r);
-          if (chain2) {
+          tmem_ld8(lane_addr + (v0 ? 0u : acc1) + (unsigned)c0, r);
+          if (v0 && v1) {
             unsigned t[8];
             tmem_ld8(lane_addr + acc1 + (unsigned)c0, t);
             tmem_ld_wait();
@@ -504,8 +516,8 @@ linear_tcq_kernel(const __grid_constant__ Program prog) {
           }
           if (ph.gated) {
             unsigned r2[8];
-            tmem_ld8(lane_addr + (unsigned)(TN + c0), r2);
-            if (chain2) {
+            tmem_ld8(lane_addr + (u0 ? 0u : acc1) + (unsigned)(TN + c0), r2);
+            if (u0 && u1) {
               unsigned t[8];
               tmem_ld8(lane_addr + acc1 + (unsigned)(TN + c0), t);
               tmem_ld_wait();
