@@ -324,7 +324,11 @@ int gemm_tc(const void* W, int bits, const float* scale, const void* bias, const
   return TSB200_OK;
 }
 
-bool tc_supported_factor(int bits, int64_t K) { return (bits == 2 || bits == 4 || bits == 8 || bits == 16) && (K % 8) == 0; }
+// 1-bit rows are 8 bytes per 64 columns: the copy engine wants a 16-byte row pitch
+bool tc_supported_factor(int bits, int64_t K) {
+  if (bits == 1) return K % 128 == 0;
+  return (bits == 2 || bits == 4 || bits == 8 || bits == 16) && (K % 8) == 0;
+}
 
 }  // namespace
 

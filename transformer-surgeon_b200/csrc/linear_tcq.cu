@@ -106,6 +106,16 @@ __device__ __forceinline__ void dequant_row_regs(unsigned raw, int r, int sub, u
           o[h * 16 + c * 4 + j] = bf16x2_sub(((t >> (4 * j)) & 0x000f000fu) | 0x43004300u, 0x43084308u);
       }
     }
+  } else if (BITS == 1) {
+    // 8 bytes per k-block: word w covers columns 32 w .. 32 w + 31, bit i = column 2 i, bit 16 + i = column 2 i + 1,
+    // so one shift brings the two bits of an output pair to bits 0 and 16; bit 1 -> +1.0, bit 0 -> -1.0 (the sign
+    // bit of bf16 1.0 is the inverted code bit)
+    const uint2 q = lds64(raw_chunk<RB>(raw, r, sub >> 1) + 8 * (sub & 1));
+    const unsigned w[2] = {~q.x, ~q.y};
+#pragma unroll
+    for (int g = 0; g < 2; ++g)
+#pragma unroll
+      for (int j = 0; j < 16; ++j) o[g * 16 + j] = (((w[g] >> j) & 0x00010001u) << 15) | 0x3F803F80u;
   } else if (BITS == 2) {
     const uint4 q = lds128(raw_chunk<RB>(raw, r, sub));
     const unsigned w[4] = {q.x, q.y, q.z, q.w};
@@ -725,6 +735,7 @@ int launch_q(const Program& prog, int grid, bool coresident, cudaStream_t s) {
 template <int TN>
 int launch_q_bits(int bits, const Program& prog, int grid, bool coresident, cudaStream_t s) {
   switch (bits) {
+    case 1: return launch_q<TN, 1>(prog, grid, coresident, s);
     case 2: return launch_q<TN, 2>(prog, grid, coresident, s);
     case 4: return launch_q<TN, 4>(prog, grid, coresident, s);
     case 8: return launch_q<TN, 8>(prog, grid, coresident, s);
@@ -795,7 +806,7 @@ int run_program_tcq(const PhaseSpec* specs, int n_phases, int bits, int64_t M, u
   for (int p = 0; p < n_phases; ++p) {
     const PhaseSpec& ps = specs[p];
     Phase& ph = prog.ph[p];
-    const GemmPlan g = plan_gemm(M, ps.g[0].N, ps.g[0].K, ps.gated ? 1 : ps.nsub, ps.gated != 0);
+    const GemmPlan g = plan_gemm(M, ps.g[0].N, ps.g[0].K, ps.gated ? 1 : ps.nsub, ps.gated != 0, bits == 1 ? 2 : 1);
     if (p == 0) tn = g.tn;
     if (ps.gated && (g.tn > 64 || ps.nsub != 2)) return TSB200_ERR_UNSUPPORTED;
     ph.nsub = ps.nsub;

@@ -28,7 +28,9 @@ struct GemmPlan {
 };
 // nsub: number of equally shaped matrices sharing the launch (their tiles add up); no_split: keep
 // every tile's K range whole (needed when the epilogue combines two accumulators).
-inline GemmPlan plan_gemm(int64_t M, int64_t N, int64_t K, int nsub = 1, bool no_split = false) {
+// kb_align: every split starts at a multiple of kb_align k-blocks (1-bit containers: 2, so that the byte offset
+// of a weight box stays a multiple of 16); a larger alignment never needs more slices than kb_align = 1.
+inline GemmPlan plan_gemm(int64_t M, int64_t N, int64_t K, int nsub = 1, bool no_split = false, int kb_align = 1) {
   GemmPlan g;
   // a 256-token tile (one k-block per stage) measured slower than 128 at M = 2048 (408 vs 460 TFLOP/s): both
   // are bound by the activation tiles every 128-row weight tile re-reads from L2, not by the MMA shape
@@ -46,6 +48,7 @@ inline GemmPlan plan_gemm(int64_t M, int64_t N, int64_t K, int nsub = 1, bool no
     if (splits < 1) splits = 1;
   }
   g.kb_per_split = (g.kb_total + splits - 1) / splits;
+  g.kb_per_split = (g.kb_per_split + kb_align - 1) / kb_align * kb_align;
   g.splits = (g.kb_total + g.kb_per_split - 1) / g.kb_per_split;
   g.n_tiles = (int)n_tiles;
   g.m_tiles = (int)m_tiles;
