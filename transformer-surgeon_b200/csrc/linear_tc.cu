@@ -339,7 +339,6 @@ int gemm_tcq(const void* W, int bits, const float* scale, const void* bias, cons
 int linear_tc(const tsb200_linear_desc* d, const void* x, void* y, int64_t M, void* workspace, size_t workspace_bytes,
               cudaStream_t s) {
   if (d->act_dtype != TSB200_BF16) return TSB200_ERR_UNSUPPORTED;
-  if (M < 9) return TSB200_ERR_UNSUPPORTED;    // a handful of tokens: the weight-streaming CUDA-core kernel
   const int64_t ku = d->rank > 0 ? d->rank : d->in_features;
   if (!tc_supported_factor(d->u_bits, ku)) return TSB200_ERR_UNSUPPORTED;
   if (d->rank > 0 && !tc_supported_factor(d->v_bits, d->in_features)) return TSB200_ERR_UNSUPPORTED;

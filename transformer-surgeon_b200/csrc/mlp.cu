@@ -14,7 +14,7 @@ size_t align256(size_t v) { return (v + 255) / 256 * 256; }
 
 bool fusable(const tsb200_linear_desc* g, const tsb200_linear_desc* u, const tsb200_linear_desc* d, int64_t M) {
   if (g->act_dtype != TSB200_BF16 || u->act_dtype != TSB200_BF16 || d->act_dtype != TSB200_BF16) return false;
-  if (M < 9 || M > 64) return false;
+  if (M < 1 || M > 64) return false;
   const int bits = g->u_bits;
   if (!(bits == 2 || bits == 4 || bits == 8)) return false;
   if (u->u_bits != bits || d->u_bits != bits) return false;
