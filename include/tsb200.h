@@ -133,8 +133,8 @@ size_t tsb200_linear_workspace_bytes(const tsb200_linear_desc* d, int64_t M);
 /* x [M, in] -> y [M, out].  M == 0 is a no-op. */
 int tsb200_linear(const tsb200_linear_desc* d, const void* x, void* y, int64_t M,
                   void* workspace, size_t workspace_bytes, void* stream);
-/* Same contract; forces the CUDA-core streaming kernel (any M; used for tiny M and as
- * the cross-check of the tensor-core kernel). */
+/* Same contract; forces the CUDA-core streaming kernel (any M; serves fp32 models and shapes the
+ * tensor-core kernel does not take, and is the cross-check of the tensor-core kernel). */
 int tsb200_linear_simt(const tsb200_linear_desc* d, const void* x, void* y, int64_t M,
                        void* workspace, size_t workspace_bytes, void* stream);
 

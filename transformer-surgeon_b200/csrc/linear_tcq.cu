@@ -1,30 +1,36 @@
-// Persistent tcgen05 kernel for LinearCompressed with QUANTIZED factors (int8 / int4 / int2):
+// Persistent tcgen05 kernel for LinearCompressed with QUANTIZED factors (int8 / int4 / int2 / 1-bit):
 //   Y[M, N] = (X[M, K] . Wq[N, K]^T) * scale[N] + bias[N]        (bf16 activations)
 // restating transformersurgeon/blocks/linear_compressed.py:96-100 on packed codes.
 //
 // Decode-time GEMMs stream a few MB of packed weights per call, so the kernel is built around
 // keeping many weight bytes in flight per SM, paying the set-up cost once per SM, and
-// synchronising once per 16 KB of weights rather than once per k-block:
-//   * grid = min(#work items, #SMs); a work item = (128-row weight tile, token tile, K split);
-//     each CTA walks its items round-robin while one producer lane keeps issuing TMA loads
-//     across item boundaries into a ring of STAGES.  A stage = KBS consecutive k-blocks: one
-//     weight box of 128 rows x up to 128 bytes of codes (swizzled) + KBS activation tiles;
-//   * two groups of 4 dequant warps share every stage (even / odd k-blocks).  A thread owns one weight row:
-//     it reads the row's codes from shared memory, widens them to bf16 pairs in registers (exact
-//     integers) and stores them with tcgen05.st straight into TENSOR MEMORY, where they are the
-//     A operand of the MMA (M = 128 weight rows; K-major, two bf16 per 32-bit column) - no
-//     shared-memory A tile, no generic->async proxy fence;
-//   * one lane issues tcgen05.mma (A from TMEM, B = activation tile from shared memory through a
-//     128-byte-swizzle descriptor, N = token tile) accumulating in TMEM columns [0, TN);
-//   * all 8 warps run the epilogue from TMEM (one lane = one weight row): scale, bias, store;
+// synchronising once per 16 KB of weights rather than once per k-block.  Warp roles (11 warps):
+//   * warp 0, one lane: PRODUCER.  grid = min(#work items, #SMs); a work item = (128-row weight
+//     tile, token tile, K split); the lane walks the CTA's items and keeps issuing TMA loads across
+//     item and phase boundaries into a ring of STAGES.  A stage = KBS consecutive k-blocks: one
+//     weight box of 128 rows x up to 128 bytes of codes (swizzled) + the activation tiles of those
+//     k-blocks (one 3-D box).  Weight boxes of a phase's first stages are requested before the
+//     phase's activations exist; the matching activation loads are noted and fired when they do;
+//   * warps 2-9: DEQUANT, two groups of 4 sharing every stage (even / odd k-blocks).  A thread owns
+//     one weight row: it reads the row's codes from shared memory, widens them to bf16 pairs in
+//     registers (exact integers) and stores them with tcgen05.st straight into TENSOR MEMORY, where
+//     they are the A operand of the MMA (M = 128 weight rows; K-major, two bf16 per 32-bit column)
+//     - no shared-memory A tile, no generic->async proxy fence;
+//   * warps 1 and 10, one lane each: MMA ISSUERS (A from TMEM, B = activation tile from shared
+//     memory through a 128-byte-swizzle descriptor, N = token tile), each into its own accumulator
+//     chain (see QLayout); one barrier per stage tells them that both operands are in place, one
+//     commit per stage frees the stage's shared memory and A buffer;
+//   * the 8 dequant warps run the epilogue from TMEM (one lane = one weight row): chains added,
+//     scale, bias, store;
 //   * split-K: every item stores its fp32 partial tile in a private slice of the workspace (plain
-//     stores, no zero-fill needed); the last CTA to finish a tile (a per-tile counter, reset by
-//     that CTA) sums the slices in split order - a deterministic result - and writes the output.
+//     stores, no zero-fill needed).  When each CTA holds one item of the phase, the CTAs of a tile
+//     meet at the tile's counter and each sums its share of the token columns; otherwise the last
+//     CTA to finish a tile sums all of it.  Slices are added in split order: a deterministic result;
 //   * a launch executes a PROGRAM of up to 4 phases separated by grid-wide barriers (all CTAs are
 //     co-resident: grid <= #SMs, one CTA per SM, cooperative launch): the V and U factors of a
 //     low-rank layer, or the whole gated MLP (gate|up V, gate|up U with SiLU(g)*u in the epilogue,
 //     down V, down U), run in ONE launch; the rank-r intermediates never leave L2, and the
-//     producer already streams the next phase's weights while the barrier is pending.
+//     dequant warps already fill both A buffers of the next phase while the barrier is pending.
 // Every mbarrier / grid-barrier wait is bounded (see tc_common.cuh); on expiry the CTA records a
 // code in the status word, drains, frees its TMEM and returns.
 #include "tc_common.cuh"
