@@ -53,6 +53,8 @@ def parse():
     ap.add_argument("--parallel", default="replica", choices=["replica", "tp"],
                     help="N > 1: independent replicas (sequences sharded, no collective; the default the scaling run uses) "
                          "or tensor-parallel linears with an NCCL all-reduce (one batch shared by all ranks)")
+    ap.add_argument("--tp-allreduce", default="peer", choices=["peer", "nccl"],
+                    help="tensor parallel: the library's fused all-reduce + add + RMSNorm over NVLink peer memory, or NCCL")
     ap.add_argument("--sweep", default=None, choices=["linear", "attention"],
                     help="op-level sweeps (BASELINE.json configs[1] / configs[2]) instead of the decode step; "
                          "prints one JSON line per case")
@@ -294,6 +296,7 @@ def run_ours(a):
         ge.build()
     tp = a.parallel == "tp" and world > 1
     dec = build_engine(a, device, seed=1 if tp else 1 + rank, tp_world=world if tp else 1, tp_rank=rank if tp else 0)
+    peer_ar = tp and a.tp_allreduce == "peer" and dec.enable_peer_allreduce()
     dec.capture()
     B = a.batch
     tgen = torch.Generator().manual_seed(7 if tp else 7 + rank)     # tensor parallel: every rank feeds the same tokens
@@ -357,7 +360,8 @@ def run_ours(a):
                 "dtype": "bf16", "data": "synthetic",
                 "config": {"workload": "llama3-8b-arch decode: %d layers, MLP LRD r=%d, W%d per-channel, %s paged KV, "
                            "batch %d/GPU, context %d->%d" % (a.layers, a.rank, a.wbits, a.kv, B, ctx0, ctx0 + a.steps),
-                           "sharding": ("tensor parallel x%d: heads / MLP columns split, 2 NCCL all-reduces per layer, batch %d shared" % (world, B))
+                           "sharding": ("tensor parallel x%d: heads / MLP columns split, 2 all-reduces per layer (%s), batch %d shared"
+                                        % (world, "fused with add + RMSNorm over NVLink peer loads" if peer_ar else "NCCL", B))
                            if tp else "replicas, %d sequences per GPU, no collective" % B,
                            "l2": "inputs larger than L2 (%.1f GB read per step)" % (step_bytes / 1e9),
                            "cuda_graph": True},

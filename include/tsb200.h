@@ -285,6 +285,33 @@ int tsb200_add_rmsnorm(void* residual, const void* delta, const void* w, void* y
 int tsb200_swiglu(const void* gate, const void* up, void* y, int dtype, int64_t M, int64_t n,
                   int64_t gate_stride, int64_t up_stride, int64_t y_stride, void* stream);
 
+/* ---------------------------------------------------------------- tensor-parallel epilogue -----
+ * No reference counterpart (the reference is single-device).  One process per GPU; every rank's
+ * buffers are mapped into the other ranks' address spaces by the host (CUDA IPC) and described by: */
+typedef struct {
+  int32_t world, rank;           /* 2..8 ranks; this process's index                                   */
+  const void* partial[8];        /* partial[s]: rank s's [M, hidden] bf16 partial output ([rank] = local) */
+  uint32_t* flags[8];            /* flags[s]: rank s's flag block, tsb200_peer_flag_bytes(), zero at start */
+  uint32_t* epoch;               /* local: two uint32, zero at start                                     */
+  int32_t* status;               /* local: non-zero after a peer failed to show up within the bounded wait */
+} tsb200_peer_desc;
+size_t tsb200_peer_flag_bytes(void);
+/* cudaDeviceEnablePeerAccess from the current device to peer_device (idempotent). */
+int tsb200_enable_peer_access(int peer_device);
+/* Map / unmap an allocation that another process of this node exported with cudaIpcGetMemHandle
+ * (handle64 = the 64 handle bytes) into the CURRENT device's address space; *base_out is the
+ * address of the exported allocation's base. */
+int tsb200_ipc_open(const void* handle64, void** base_out);
+int tsb200_ipc_close(void* base);
+/* residual += sum over ranks of partial_s (ranks in index order, fp32, rounded to bf16), then
+ * y = RMSNorm(residual) * w (Hugging Face variant): the all-reduce that follows a row-parallel
+ * LinearCompressed (o_proj, down_proj) fused with tsb200_add_rmsnorm, over NVLink peer loads.
+ * bf16, hidden % 8 == 0, hidden <= 8192, M <= 1024.  Every rank must make the same sequence of calls
+ * on the group, and must alternate between two partial buffers on consecutive calls (a buffer may be
+ * rewritten only after the following call has started on every rank). */
+int tsb200_peer_allreduce_add_rmsnorm(const tsb200_peer_desc* pd, void* residual, const void* w, void* y,
+                                      int dtype, int64_t M, int64_t hidden, float eps, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

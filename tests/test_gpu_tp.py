@@ -101,3 +101,87 @@ def test_two_rank_engine_matches_single_gpu(tmp_path):
     outs = torch.load(out)
     torch.testing.assert_close(outs[2][1], outs[1][1], rtol=2e-4, atol=2e-4)
     assert torch.equal(outs[2][0], outs[1][0])
+
+
+def _peer_worker(rank, world, port, out_path):
+    import torch.distributed as dist
+    from transformer_surgeon_b200 import ops, surgeon, tensor_parallel as tp
+    from transformer_surgeon_b200.decoder import DecoderConfig
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    res = {}
+    try:
+        # ---- kernel level: fused all-reduce + add + RMSNorm against NCCL all-reduce + tsb200_add_rmsnorm
+        M, hidden = 32, 512
+        pb = tp.PeerBuffers(M, hidden, dev)
+        g = torch.Generator().manual_seed(40)                      # same stream of numbers on every rank
+        w = (1.0 + 0.1 * torch.randn(hidden, generator=g)).bfloat16().to(dev)
+        resid_a = torch.randn(M, hidden, generator=g).bfloat16().to(dev)
+        resid_b = resid_a.clone()
+        out_a, out_b = torch.empty_like(resid_a), torch.empty_like(resid_a)
+        same = True
+        for it in range(6):
+            parts = [torch.randn(M, hidden, generator=g).bfloat16() for _ in range(world)]
+            pb.partial(it % 2).copy_(parts[rank])
+            pb.allreduce_add_rmsnorm(it % 2, resid_a, w, 1e-6, out_a)
+            ref = parts[rank].to(dev)
+            dist.all_reduce(ref)
+            ops.add_rmsnorm(resid_b, ref, w, 1e-6, 0, out=out_b)
+            same = same and torch.equal(out_a, out_b) and torch.equal(resid_a, resid_b)
+        # replayed from a CUDA graph: the epoch advances on the device
+        s = torch.cuda.Stream()
+        with torch.cuda.stream(s):
+            gr = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(gr):
+                pb.allreduce_add_rmsnorm(0, resid_a, w, 1e-6, out_a)
+                pb.allreduce_add_rmsnorm(1, resid_a, w, 1e-6, out_a)
+            for _ in range(3):
+                gr.replay()
+        torch.cuda.synchronize()
+        for _ in range(3):
+            for i in (0, 1):
+                ref = pb.partial(i).clone()
+                dist.all_reduce(ref)
+                ops.add_rmsnorm(resid_b, ref, w, 1e-6, 0, out=out_b)
+        res["kernel_same"] = bool(same and torch.equal(out_a, out_b) and torch.equal(resid_a, resid_b))
+        res["status"] = pb.status()
+        # ---- engine level: bf16 TP engine with the fused kernel against the same engine over NCCL
+        g = torch.Generator().manual_seed(32)
+        sd = _state_dict(g)
+        ids = torch.randint(0, 128, (3, 10), generator=g)
+        cc = {k[:-7]: {"quantization": {"precision": 8, "granularity": "per_channel"}} for k in sd if "proj.weight" in k}
+        outs = {}
+        for mode in ("nccl", "peer"):
+            cfg = DecoderConfig(num_layers=2, hidden=256, num_heads=4, num_kv_heads=2, head_dim=64, intermediate=512,
+                                vocab=128, dtype=torch.bfloat16, kv_format="int8", max_positions=64, tp_world=world, tp_rank=rank)
+            dec = surgeon.decoder_from_state_dict(sd, cfg, cc, batch=3, max_seq_len=32, device=dev)
+            if mode == "peer":
+                assert dec.enable_peer_allreduce()
+            toks, logits = dec.generate(ids, max_new_tokens=4)
+            outs[mode] = (toks.cpu(), logits.float().cpu())
+            if mode == "peer":
+                res["engine_status"] = dec.peer.status()
+        res["outs"] = outs
+        if rank == 0:
+            torch.save(res, out_path)
+    finally:
+        dist.destroy_process_group()
+
+
+def test_peer_allreduce_matches_nccl(tmp_path):
+    """The fused all-reduce + residual add + RMSNorm over NVLink peer loads gives the bits of an NCCL
+    all-reduce followed by tsb200_add_rmsnorm (2 ranks), eagerly and replayed from a CUDA graph, and the
+    tensor-parallel engine produces the same tokens and logits with either."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    import torch.multiprocessing as mp
+    out = str(tmp_path / "peer.pt")
+    mp.spawn(_peer_worker, args=(2, _free_port(), out), nprocs=2, join=True)
+    res = torch.load(out)
+    assert res["status"] == 0 and res["engine_status"] == 0
+    assert res["kernel_same"]
+    assert torch.equal(res["outs"]["peer"][0], res["outs"]["nccl"][0])
+    torch.testing.assert_close(res["outs"]["peer"][1], res["outs"]["nccl"][1], rtol=0, atol=0)

@@ -34,8 +34,13 @@ class KVDesc(C.Structure):
                 ("k_scale", C.c_void_p), ("v_scale", C.c_void_p)]
 
 
+class PeerDesc(C.Structure):
+    _fields_ = [("world", C.c_int32), ("rank", C.c_int32), ("partial", C.c_void_p * 8), ("flags", C.c_void_p * 8),
+                ("epoch", C.c_void_p), ("status", C.c_void_p)]
+
+
 _i64, _i32, _f32, _vp, _sz = C.c_int64, C.c_int, C.c_float, C.c_void_p, C.c_size_t
-_LD, _KD = C.POINTER(LinearDesc), C.POINTER(KVDesc)
+_LD, _KD, _PD = C.POINTER(LinearDesc), C.POINTER(KVDesc), C.POINTER(PeerDesc)
 
 # name -> (restype, argtypes); mirrors include/tsb200.h one to one.
 SIGNATURES = {
@@ -65,6 +70,11 @@ SIGNATURES = {
     "tsb200_paged_decode_attn_static_capacity": (_sz, []),
     "tsb200_paged_decode_attn_static": (_i32, [_KD, _vp, _vp, _i32, _i64, _i64, _i32, _f32, _i64, _vp]),
     "tsb200_rope": (_i32, [_vp, _i32, _i64, _i64, _i64, _i32, _i32, _vp, _vp, _vp, _i64, _vp]),
+    "tsb200_peer_flag_bytes": (_sz, []),
+    "tsb200_enable_peer_access": (_i32, [_i32]),
+    "tsb200_ipc_open": (_i32, [C.c_char_p, C.POINTER(C.c_void_p)]),
+    "tsb200_ipc_close": (_i32, [_vp]),
+    "tsb200_peer_allreduce_add_rmsnorm": (_i32, [_PD, _vp, _vp, _vp, _i32, _i64, _i64, _f32, _vp]),
     "tsb200_add_rmsnorm": (_i32, [_vp, _vp, _vp, _vp, _i32, _i64, _i64, _f32, _i32, _vp]),
     "tsb200_swiglu": (_i32, [_vp, _vp, _vp, _i32, _i64, _i64, _i64, _i64, _i64, _vp]),
 }

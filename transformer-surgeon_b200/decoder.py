@@ -120,6 +120,20 @@ class CompressedDecoder:
         self.attn_ws = torch.zeros(ops.decode_attn_workspace_bytes(B, H, d, max_seq_len), dtype=torch.uint8, device=device)
         self.graph = None
         self.kernel_launches_per_step = 0
+        self.peer = None                    # tensor_parallel.PeerBuffers once enable_peer_allreduce() ran
+
+    def enable_peer_allreduce(self):
+        """Tensor parallel: sum the row-parallel partial outputs with the library's own kernel over NVLink
+        peer memory, fused with the residual add and RMSNorm that follow (`tsb200_peer_allreduce_add_rmsnorm`),
+        instead of an NCCL all-reduce plus a separate normalisation launch.  Call on every rank, before
+        `capture()`.  Returns False (and changes nothing) when the configuration is outside what the kernel takes."""
+        c = self.cfg
+        if c.tp_world < 2 or c.dtype != torch.bfloat16 or c.norm_variant != 0 or c.hidden % 8 or c.hidden > 8192 or self.B > 1024:
+            return False
+        from .tensor_parallel import PeerBuffers
+        self.peer = PeerBuffers(self.B, c.hidden, self.device, self.tp_group)
+        self.graph = None
+        return True
 
     @staticmethod
     def _shard_layer(L, c):
@@ -149,8 +163,12 @@ class CompressedDecoder:
         self.seq_lens.add_(1)
         delta = None
         rope = (self.cos, self.sin)
+        peer = self.peer if tp_on else None
         for li, L in enumerate(self.layers):
-            ops.add_rmsnorm(self.resid, delta, L.ln1, c.rms_eps, c.norm_variant, out=self.xn); n += 1
+            if peer is not None and li > 0:      # the previous layer's down_proj partials: summed, added, normalised
+                peer.allreduce_add_rmsnorm(1, self.resid, L.ln1, c.rms_eps, out=self.xn); n += 1
+            else:
+                ops.add_rmsnorm(self.resid, delta, L.ln1, c.rms_eps, c.norm_variant, out=self.xn); n += 1
             if L.qkv is not None:
                 L.qkv(self.xn, out=self.qkv, ws=self.lin_ws); n += 1
                 q4 = self.qkv[:, :H * d].unflatten(1, (H, d)).unsqueeze(1)                   # [B,1,H,d] views
@@ -165,6 +183,11 @@ class CompressedDecoder:
             self.kv[li].rope_append(q4, k4, v4, rope, seq_lens=self.write_pos); n += 1
             ops.paged_decode_attention(self.kv[li], q4[:, 0], self.max_seq_len, out=self.attn.view(B, H, d),
                                        ws=self.attn_ws, seq_lens=self.seq_lens); n += 2
+            if peer is not None:
+                L.o(self.attn, out=peer.partial(0), ws=self.lin_ws); n += 1
+                peer.allreduce_add_rmsnorm(0, self.resid, L.ln2, c.rms_eps, out=self.xn); n += 1
+                L.mlp(self.xn, out=peer.partial(1), ws=self.mlp_ws); n += 1
+                continue
             L.o(self.attn, out=self.delta, ws=self.lin_ws); n += 1
             if tp_on:
                 all_reduce_sum(self.delta, self.tp_group)       # row-parallel o_proj: sum of the partial outputs
@@ -173,7 +196,10 @@ class CompressedDecoder:
             if tp_on:
                 all_reduce_sum(self.delta, self.tp_group)       # row-parallel down_proj
             delta = self.delta
-        ops.add_rmsnorm(self.resid, delta, self.final_norm, c.rms_eps, c.norm_variant, out=self.xn); n += 1
+        if peer is not None:
+            peer.allreduce_add_rmsnorm(1, self.resid, self.final_norm, c.rms_eps, out=self.xn); n += 1
+        else:
+            ops.add_rmsnorm(self.resid, delta, self.final_norm, c.rms_eps, c.norm_variant, out=self.xn); n += 1
         self.lm_head(self.xn, out=self.logits, ws=self.lin_ws); n += 1
         torch.argmax(self.logits, dim=-1, out=self.next_tokens)
         self.kernel_launches_per_step = n

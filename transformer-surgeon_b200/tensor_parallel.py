@@ -11,10 +11,13 @@ column slice of V keeps the scale of the full row it was quantized with (the cod
 re-derived), so the sharded layers reconstruct exactly the same weights as the unsharded ones.
 The reference has no multi-GPU path (no torch.distributed import in the package).
 """
+import ctypes as C
+
 import torch
 import torch.distributed as dist
 
-from . import ops
+from . import _lib, ops
+from ._lib import check
 
 
 def _slice_factor_rows(f, begin, end):
@@ -62,3 +65,78 @@ def all_reduce_sum(t, group=None):
     if dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1:
         dist.all_reduce(t, op=dist.ReduceOp.SUM, group=group)
     return t
+
+
+# ---------------------------------------------------------------- all-reduce over peer memory
+# An exported allocator block can be imported once per process: several PeerBuffers whose tensors
+# share a block reuse the mapping, which then lives until the process exits.
+_ipc_bases = {}
+
+
+class PeerBuffers:
+    """Two [M, hidden] bf16 partial-output buffers per rank plus the flag blocks of
+    `tsb200_peer_allreduce_add_rmsnorm`, each mapped into every rank of the group.
+
+    The row-parallel projections write their partial outputs straight into `partial(i)`; the fused
+    kernel then reads every rank's copy over NVLink.  The buffer is a PyTorch allocation exported with
+    the CUDA IPC handle PyTorch produces for its own multiprocessing; the handles travel through the
+    process group and every rank imports them on ITS OWN device (`tsb200_ipc_open`; one process per GPU
+    on one node, every process seeing all GPUs)."""
+
+    def __init__(self, M, hidden, device, group=None):
+        lib = _lib.load()
+        self.group, self.M, self.hidden, self.device = group, M, hidden, torch.device(device)
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        if not 2 <= self.world <= 8:
+            raise ValueError("peer all-reduce serves 2..8 ranks")
+        part = (M * hidden * 2 + 255) // 256 * 256
+        flag = int(lib.tsb200_peer_flag_bytes())
+        self._off = {"p0": 0, "p1": part, "flags": 2 * part}
+        # one allocation per rank: [partial 0 | partial 1 | flags], zero-filled (flags must start at 0)
+        self.local = torch.zeros(2 * part + flag, dtype=torch.uint8, device=self.device)
+        self.state = torch.zeros(4, dtype=torch.int32, device=self.device)     # [epoch, finished CTAs, status, -]
+        # _share_cuda_(): (device, 64-byte cudaIpcMemHandle of the allocator block, size, offset of this storage, ...)
+        exported = self.local.untyped_storage()._share_cuda_()
+        meta = (bytes(exported[1]), int(exported[3]))
+        metas = [None] * self.world
+        dist.all_gather_object(metas, meta, group=group)
+        bases = []
+        with torch.cuda.device(self.device):
+            for s, (handle, offset) in enumerate(metas):
+                if s == self.rank:
+                    bases.append(self.local.data_ptr())
+                    continue
+                key = (self.device.index, handle)
+                if key not in _ipc_bases:
+                    base = C.c_void_p()
+                    check(lib.tsb200_ipc_open(handle, C.byref(base)), "tsb200_ipc_open")
+                    _ipc_bases[key] = base.value
+                bases.append(_ipc_bases[key] + offset)
+        self._desc = []
+        for i in range(2):
+            d = _lib.PeerDesc()
+            d.world, d.rank = self.world, self.rank
+            for s in range(self.world):
+                d.partial[s] = bases[s] + self._off["p%d" % i]
+                d.flags[s] = bases[s] + self._off["flags"]
+            d.epoch = self.state.data_ptr()
+            d.status = self.state.data_ptr() + 8
+            self._desc.append(d)
+        dist.barrier(group=group)          # every rank has mapped every buffer before anyone signals
+
+    def partial(self, i):
+        """This rank's partial-output buffer i (0 / 1) as a [M, hidden] bf16 tensor."""
+        off = self._off["p%d" % i]
+        return self.local[off:off + self.M * self.hidden * 2].view(torch.bfloat16).view(self.M, self.hidden)
+
+    def allreduce_add_rmsnorm(self, i, residual, weight, eps, out):
+        """residual += sum over ranks of partial(i); out = RMSNorm(residual) * weight."""
+        lib = _lib.load()
+        check(lib.tsb200_peer_allreduce_add_rmsnorm(C.byref(self._desc[i]), residual.data_ptr(), weight.data_ptr(),
+                                                    out.data_ptr(), ops.BF16, residual.shape[0], self.hidden, float(eps),
+                                                    ops._stream()), "tsb200_peer_allreduce_add_rmsnorm")
+        return out
+
+    def status(self):
+        """0, or the code recorded when a peer did not show up within the bounded wait (synchronises)."""
+        return int(self.state[2].item())
