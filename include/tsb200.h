@@ -298,6 +298,8 @@ typedef struct {
 size_t tsb200_peer_flag_bytes(void);
 /* cudaDeviceEnablePeerAccess from the current device to peer_device (idempotent). */
 int tsb200_enable_peer_access(int peer_device);
+/* IPC handle (64 bytes) of the cudaMalloc allocation that contains ptr, and ptr's byte offset in it. */
+int tsb200_ipc_export(const void* ptr, void* handle64_out, uint64_t* offset_out);
 /* Map / unmap an allocation that another process of this node exported with cudaIpcGetMemHandle
  * (handle64 = the 64 handle bytes) into the CURRENT device's address space; *base_out is the
  * address of the exported allocation's base. */

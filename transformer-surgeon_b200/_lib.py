@@ -72,6 +72,7 @@ SIGNATURES = {
     "tsb200_rope": (_i32, [_vp, _i32, _i64, _i64, _i64, _i32, _i32, _vp, _vp, _vp, _i64, _vp]),
     "tsb200_peer_flag_bytes": (_sz, []),
     "tsb200_enable_peer_access": (_i32, [_i32]),
+    "tsb200_ipc_export": (_i32, [_vp, C.c_char_p, C.POINTER(C.c_uint64)]),
     "tsb200_ipc_open": (_i32, [C.c_char_p, C.POINTER(C.c_void_p)]),
     "tsb200_ipc_close": (_i32, [_vp]),
     "tsb200_peer_allreduce_add_rmsnorm": (_i32, [_PD, _vp, _vp, _vp, _i32, _i64, _i64, _f32, _vp]),

@@ -21,6 +21,7 @@
 // The epoch lives in device memory and is advanced by the last CTA of each launch, so a captured
 // CUDA graph replays correctly.
 #include "common.cuh"
+#include <cuda.h>
 #include <cstring>
 
 namespace tsb {
@@ -171,6 +172,32 @@ extern "C" int tsb200_enable_peer_access(int peer_device) {
   const cudaError_t e = cudaDeviceEnablePeerAccess(peer_device, 0);
   if (e == cudaErrorPeerAccessAlreadyEnabled) { (void)cudaGetLastError(); return TSB200_OK; }
   TSB_CUDA(e);
+  return TSB200_OK;
+}
+
+// Export side: the IPC handle of the cudaMalloc allocation that contains `ptr`, and ptr's offset inside it (a
+// tensor library's allocator carves many tensors out of one allocation).  Memory from a virtual-memory
+// ("expandable") allocator has no such handle: the call then fails with the CUDA error.
+extern "C" int tsb200_ipc_export(const void* ptr, void* handle64_out, uint64_t* offset_out) {
+  TSB_REQUIRE_DEVICE();
+  if (!ptr || !handle64_out || !offset_out) return TSB200_ERR_ARG;
+  typedef CUresult (*RangeFn)(CUdeviceptr*, size_t*, CUdeviceptr);
+  static RangeFn range_fn = nullptr;
+  if (!range_fn) {
+    void* f = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuMemGetAddressRange", &f, cudaEnableDefault, &qres) != cudaSuccess ||
+        qres != cudaDriverEntryPointSuccess || !f)
+      return TSB200_ERR_CUDA;
+    range_fn = reinterpret_cast<RangeFn>(f);
+  }
+  CUdeviceptr base = 0;
+  size_t size = 0;
+  if (range_fn(&base, &size, (CUdeviceptr)(uintptr_t)ptr) != CUDA_SUCCESS) return TSB200_ERR_CUDA;
+  cudaIpcMemHandle_t h;
+  TSB_CUDA(cudaIpcGetMemHandle(&h, reinterpret_cast<void*>((uintptr_t)base)));
+  memcpy(handle64_out, &h, sizeof(h));
+  *offset_out = (uint64_t)((uintptr_t)ptr - (uintptr_t)base);
   return TSB200_OK;
 }
 

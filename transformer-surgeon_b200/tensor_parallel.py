@@ -78,10 +78,9 @@ class PeerBuffers:
     `tsb200_peer_allreduce_add_rmsnorm`, each mapped into every rank of the group.
 
     The row-parallel projections write their partial outputs straight into `partial(i)`; the fused
-    kernel then reads every rank's copy over NVLink.  The buffer is a PyTorch allocation exported with
-    the CUDA IPC handle PyTorch produces for its own multiprocessing; the handles travel through the
-    process group and every rank imports them on ITS OWN device (`tsb200_ipc_open`; one process per GPU
-    on one node, every process seeing all GPUs)."""
+    kernel then reads every rank's copy over NVLink.  The buffer is a PyTorch allocation; its CUDA IPC
+    handle (`tsb200_ipc_export`) travels through the process group and every rank imports it on ITS OWN
+    device (`tsb200_ipc_open`; one process per GPU on one node, every process seeing all GPUs)."""
 
     def __init__(self, M, hidden, device, group=None):
         lib = _lib.load()
@@ -95,9 +94,10 @@ class PeerBuffers:
         # one allocation per rank: [partial 0 | partial 1 | flags], zero-filled (flags must start at 0)
         self.local = torch.zeros(2 * part + flag, dtype=torch.uint8, device=self.device)
         self.state = torch.zeros(4, dtype=torch.int32, device=self.device)     # [epoch, finished CTAs, status, -]
-        # _share_cuda_(): (device, 64-byte cudaIpcMemHandle of the allocator block, size, offset of this storage, ...)
-        exported = self.local.untyped_storage()._share_cuda_()
-        meta = (bytes(exported[1]), int(exported[3]))
+        hbuf, off = C.create_string_buffer(64), C.c_uint64()
+        with torch.cuda.device(self.device):
+            check(lib.tsb200_ipc_export(self.local.data_ptr(), hbuf, C.byref(off)), "tsb200_ipc_export")
+        meta = (hbuf.raw, int(off.value))
         metas = [None] * self.world
         dist.all_gather_object(metas, meta, group=group)
         bases = []
