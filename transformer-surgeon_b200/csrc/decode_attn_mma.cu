@@ -27,8 +27,14 @@ int validate_attn_args(const tsb200_kv_desc* kv, const void* q, void* out, int d
 
 namespace {
 
-constexpr int kWarps = 4;
-constexpr int kStages = 4;
+#ifndef TSB_MMA_WARPS
+#define TSB_MMA_WARPS 4
+#endif
+#ifndef TSB_MMA_STAGES
+#define TSB_MMA_STAGES 4
+#endif
+constexpr int kWarps = TSB_MMA_WARPS;
+constexpr int kStages = TSB_MMA_STAGES;
 
 __device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc) {
   const unsigned s = (unsigned)__cvta_generic_to_shared(smem_dst);
