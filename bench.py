@@ -296,7 +296,13 @@ def run_ours(a):
         ge.build()
     tp = a.parallel == "tp" and world > 1
     dec = build_engine(a, device, seed=1 if tp else 1 + rank, tp_world=world if tp else 1, tp_rank=rank if tp else 0)
-    peer_ar = tp and a.tp_allreduce == "peer" and dec.enable_peer_allreduce()
+    peer_ar = False
+    if tp and a.tp_allreduce == "peer":
+        try:
+            peer_ar = dec.enable_peer_allreduce()
+        except RuntimeError as ex:           # raised on every rank alike: all of them stay on NCCL
+            if rank == 0:
+                print("peer all-reduce unavailable, using NCCL: %s" % ex, file=sys.stderr)
     dec.capture()
     B = a.batch
     tgen = torch.Generator().manual_seed(7 if tp else 7 + rank)     # tensor parallel: every rank feeds the same tokens

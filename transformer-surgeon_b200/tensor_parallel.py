@@ -94,24 +94,35 @@ class PeerBuffers:
         # one allocation per rank: [partial 0 | partial 1 | flags], zero-filled (flags must start at 0)
         self.local = torch.zeros(2 * part + flag, dtype=torch.uint8, device=self.device)
         self.state = torch.zeros(4, dtype=torch.int32, device=self.device)     # [epoch, finished CTAs, status, -]
+        # A failure on one rank (export or import) is turned into the same RuntimeError on EVERY rank, after the
+        # collectives have been matched, so that callers can fall back together.
         hbuf, off = C.create_string_buffer(64), C.c_uint64()
         with torch.cuda.device(self.device):
-            check(lib.tsb200_ipc_export(self.local.data_ptr(), hbuf, C.byref(off)), "tsb200_ipc_export")
-        meta = (hbuf.raw, int(off.value))
+            st = lib.tsb200_ipc_export(self.local.data_ptr(), hbuf, C.byref(off))
+        meta = (hbuf.raw, int(off.value)) if st == 0 else None
         metas = [None] * self.world
         dist.all_gather_object(metas, meta, group=group)
-        bases = []
-        with torch.cuda.device(self.device):
-            for s, (handle, offset) in enumerate(metas):
-                if s == self.rank:
-                    bases.append(self.local.data_ptr())
-                    continue
-                key = (self.device.index, handle)
-                if key not in _ipc_bases:
-                    base = C.c_void_p()
-                    check(lib.tsb200_ipc_open(handle, C.byref(base)), "tsb200_ipc_open")
-                    _ipc_bases[key] = base.value
-                bases.append(_ipc_bases[key] + offset)
+        bases, ok = [], all(m is not None for m in metas)
+        if ok:
+            with torch.cuda.device(self.device):
+                for s, (handle, offset) in enumerate(metas):
+                    if s == self.rank:
+                        bases.append(self.local.data_ptr())
+                        continue
+                    key = (self.device.index, handle)
+                    if key not in _ipc_bases:
+                        base = C.c_void_p()
+                        if lib.tsb200_ipc_open(handle, C.byref(base)) != 0:
+                            ok = False
+                            break
+                        _ipc_bases[key] = base.value
+                    bases.append(_ipc_bases[key] + offset)
+        oks = [None] * self.world
+        dist.all_gather_object(oks, ok, group=group)
+        if not all(oks):
+            raise RuntimeError("peer buffers could not be exported / imported on ranks %s (CUDA IPC needs one node, "
+                               "every process seeing all GPUs, and a cudaMalloc-backed allocator)"
+                               % [i for i, o in enumerate(oks) if not o])
         self._desc = []
         for i in range(2):
             d = _lib.PeerDesc()
