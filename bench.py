@@ -30,11 +30,11 @@ if ROOT not in sys.path:
 LLAMA3_8B = dict(num_layers=32, hidden=4096, num_heads=32, num_kv_heads=8, head_dim=128, intermediate=14336,
                  vocab=128256, rope_theta=5e5, rms_eps=1e-5)
 # Kernel that serves each KV format, and dram__bytes_read.sum + dram__bytes_write.sum per algorithmic
-# byte from an ncu capture of that kernel (profiles/decode_attn_fp8_mma_b32_ctx4096.md: 269.83 MB +
-# 4.09 MB against 268.4 MB algorithmic; profiles/decode_attn_mma_f16widen_fp8_b32_ctx4096.md for the
+# byte from an ncu capture of that kernel (profiles/decode_attn_fp8_mma_b32_ctx4096.md: 269.84 MB +
+# 5.07 MB against 268.4 MB algorithmic; profiles/decode_attn_mma_f16widen_fp8_b32_ctx4096.md for the
 # f16-widening kernel).  The traffic of these kernels grows in proportion to the KV bytes.
 ATTN_KERNEL = {"fp8": "decode_attn_fp8_kernel (split merge fused)", "int8": "decode_attn_mma_kernel (split merge fused)"}
-NCU_DRAM_PER_ALG_BYTE = {"fp8": (269.83 + 4.09) / 268.4}
+NCU_DRAM_PER_ALG_BYTE = {"fp8": (269.84 + 5.07) / 268.4}
 METRIC = "decode tokens/s (Llama-3-8B LRD+W4+FP8-KV)"
 
 
