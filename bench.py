@@ -206,6 +206,30 @@ def time_attention_kernel(dec, a, reps=5):
     return e0.elapsed_time(e1) / (reps * len(dec.kv))
 
 
+def time_mlp_kernel(dec, reps=5):
+    """CUDA-event time of one fused gated-MLP launch (linear_tcq_kernel, four phases), cycling through the
+    layers' weights inside one CUDA graph so that no launch finds its weights in L2 when the model is deep."""
+    import torch
+    x = torch.randn((dec.B, dec.cfg.hidden), device=dec.device).to(dec.cfg.dtype)
+    out = torch.empty_like(x)
+    for L in dec.layers[:2]:
+        L.mlp(x, out=out, ws=dec.mlp_ws)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        for L in dec.layers:
+            L.mlp(x, out=out, ws=dec.mlp_ws)
+    g.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        g.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / (reps * len(dec.layers))
+
+
 # ------------------------------------------------------------------------------ CPU reference arm
 def cpu_reference_sample(a, steps, warmup):
     """One decoder layer of the workload at full width on the host cores, the way the reference runs
@@ -349,6 +373,7 @@ def run_ours(a):
     # per-kernel timing captures a second CUDA graph; kept out of the tensor-parallel mode, whose ranks
     # must stay in lockstep on the NCCL communicator
     t_attn = time_attention_kernel(dec, a) if not tp else None   # tensor parallel: the kernel is not timed alone
+    t_mlp = time_mlp_kernel(dec) if not tp else None
     if world > 1:
         t = torch.tensor([ms, ms_e2e], device=device)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -382,6 +407,14 @@ def run_ours(a):
                              "ms_per_launch": t_attn,
                              "step_achieved": step_bytes / (ms / a.steps * 1e-3) / 1e9,
                              "step_frac": step_bytes / (ms / a.steps * 1e-3) / 1e9 / peak}}
+        if t_mlp:
+            # the other large kernel of the step, for the record: the fused gated MLP moves its packed weights once
+            # per launch and is bound by dependent latencies (phases, split-K rendezvous), not by HBM
+            c = LLAMA3_8B
+            mlp_bytes = 3 * (c["intermediate"] * a.rank + a.rank * c["hidden"]) * a.wbits / 8.0
+            line["roofline_mlp"] = {"kernel": "linear_tcq_kernel (gated MLP: 4 GEMM phases in one launch)", "bound": "hbm",
+                                    "achieved": mlp_bytes / (t_mlp * 1e-3) / 1e9, "peak": peak, "unit": "GB/s",
+                                    "frac": mlp_bytes / (t_mlp * 1e-3) / 1e9 / peak, "ms_per_launch": t_mlp}
         try:
             cpu_tps, _, sample = cpu_reference_sample(a, 2, 1) if world == 1 else (None, None, None)
             if cpu_tps is not None:
