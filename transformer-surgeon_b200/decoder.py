@@ -244,15 +244,72 @@ class CompressedDecoder:
         self.seq_lens.zero_()
 
     @torch.no_grad()
-    def generate(self, input_ids, max_new_tokens):
-        """Greedy decoding.  The prompt is fed one token at a time through the decode step (as the
-        reference's blocks path does, examples/04_cache_impl_export_interface.py:128-139)."""
+    def prefill(self, input_ids):
+        """Batched prompt pass (single GPU): all T prompt tokens of every sequence go through the packed
+        linears at once (M = B * T rows), K and V are rotated, quantized and appended for the whole chunk
+        (FP8: the per-sequence scales are taken over the prompt first, amax / 448, and then frozen), and the
+        causal attention of the chunk reads the DEQUANTIZED cache (`kv_gather`) through torch's
+        scaled-dot-product attention - a library kernel; a fused prefill attention is not built.  Leaves the
+        engine in the state the token-by-token prompt loop leaves it in: logits / next_tokens of the last
+        prompt token, seq_lens == T.  Starts from an empty cache."""
+        c = self.cfg
+        if c.tp_world > 1:
+            raise NotImplementedError("batched prefill is single-GPU; tensor-parallel engines feed the prompt stepwise")
+        ids = input_ids.to(self.device)
+        B, T = ids.shape
+        if B != self.B or T < 1 or T > self.max_seq_len:
+            raise ValueError("prompt does not fit the engine")
+        H, Hkv, d = self.H_local, self.Hkv_local, c.head_dim
+        self.reset()
+        zeros = torch.zeros_like(self.seq_lens)
+        rope = (self.cos, self.sin)
+        resid = self.embed[ids.reshape(-1)].contiguous()                # [B*T, hidden]
+        delta = None
+        for li, L in enumerate(self.layers):
+            xn = ops.add_rmsnorm(resid, delta, L.ln1, c.rms_eps, c.norm_variant)
+            if L.qkv is not None:
+                qkv = L.qkv(xn)
+                q4 = qkv[:, :H * d].unflatten(1, (H, d)).unflatten(0, (B, T))
+                k4 = qkv[:, H * d:(H + Hkv) * d].unflatten(1, (Hkv, d)).unflatten(0, (B, T))
+                v4 = qkv[:, (H + Hkv) * d:].unflatten(1, (Hkv, d)).unflatten(0, (B, T))
+            else:
+                q4, k4, v4 = L.q(xn).view(B, T, H, d), L.k(xn).view(B, T, Hkv, d), L.v(xn).view(B, T, Hkv, d)
+            q4, k4, v4 = q4.contiguous(), k4.contiguous(), v4.contiguous()
+            kv = self.kv[li]
+            if kv.k_scale is not None:
+                kv.set_fp8_scales(k4, v4, rope=rope, pos0=zeros)
+            kv.rope_append(q4, k4, v4, rope, seq_lens=zeros)            # q4 rotated in place
+            self.seq_lens.fill_(T)
+            kd, vd = ops.kv_gather(kv, T, dtype=c.dtype)                # what every attention read sees
+            att = torch.nn.functional.scaled_dot_product_attention(q4.transpose(1, 2), kd.transpose(1, 2), vd.transpose(1, 2),
+                                                                   is_causal=True, enable_gqa=True)
+            att = att.transpose(1, 2).reshape(B * T, H * d).contiguous()
+            delta = L.o(att)
+            xn = ops.add_rmsnorm(resid, delta, L.ln2, c.rms_eps, c.norm_variant)
+            delta = L.mlp(xn)
+        last = resid.view(B, T, -1)[:, -1].contiguous()
+        dl = delta.view(B, T, -1)[:, -1].contiguous()
+        self.resid.copy_(last)
+        ops.add_rmsnorm(self.resid, dl, self.final_norm, c.rms_eps, c.norm_variant, out=self.xn)
+        self.lm_head(self.xn, out=self.logits, ws=self.lin_ws)
+        torch.argmax(self.logits, dim=-1, out=self.next_tokens)
+        self.seq_lens.fill_(T)
+        return self.logits
+
+    @torch.no_grad()
+    def generate(self, input_ids, max_new_tokens, batched_prefill=False):
+        """Greedy decoding.  By default the prompt is fed one token at a time through the decode step (as
+        the reference's blocks path does, examples/04_cache_impl_export_interface.py:128-139);
+        `batched_prefill=True` runs `prefill()` instead."""
         ids = input_ids.to(self.device)
         B, T = ids.shape
         assert B == self.B
-        self.reset()
-        for t in range(T):
-            self.step(ids[:, t])
+        if batched_prefill:
+            self.prefill(ids)
+        else:
+            self.reset()
+            for t in range(T):
+                self.step(ids[:, t])
         prefill_logits = self.logits.clone()
         out = [ids]
         for _ in range(max_new_tokens):
