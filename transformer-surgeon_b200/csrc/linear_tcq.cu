@@ -48,7 +48,7 @@ constexpr unsigned kTmemCols = 512;
 template <int TN, int BITS> struct QLayout {
   static constexpr int kKbsFull = 1024 / BITS / BK;        // k-blocks in a 128-byte row of codes
   // A buffer = KBS * 32 TMEM columns <= 128; the 256-token tile keeps one k-block (32 KB of activations) per stage
-  static constexpr int kKbsCap = TN <= 32 ? 4 : (TN <= 128 ? 2 : 1);
+  static constexpr int kKbsCap = (TN <= 32 || TN == 128) ? 4 : (TN <= 128 ? 2 : 1);
   static constexpr unsigned kACol0 = 256;                   // TMEM column of A buffer 0 (accumulators sit below); buffer 1 at +128
   static constexpr int KBS = kKbsFull < kKbsCap ? kKbsFull : kKbsCap;
   static constexpr int kRawRow = BK * BITS / 8;            // bytes of one weight row per k-block
@@ -752,7 +752,7 @@ int launch_q_bits(int bits, const Program& prog, int grid, bool coresident, cuda
 // Inner extent (bytes) of the weight box: must equal QLayout<TN, BITS>::kRawStageRow.
 int raw_box_bytes(int tn, int bits) {
   const int full = 1024 / bits / BK;
-  const int cap = tn <= 32 ? 4 : (tn <= 128 ? 2 : 1);
+  const int cap = (tn <= 32 || tn == 128) ? 4 : (tn <= 128 ? 2 : 1);
   const int kbs = full < cap ? full : cap;
   return kbs * BK * bits / 8;
 }
