@@ -28,17 +28,19 @@ inline int choose_splits(int64_t B, int hkv, int64_t max_seq_len) {
   return (int)s;
 }
 
-// Split count of the fp8-MMA kernel: its per-CTA set-up (query expansion) is amortised over at
-// least 128 pages per split; more splits only when the (sequence, kv head) grid underfills the SMs.
+// Split count of the fp8-MMA kernel.  Two 6-warp CTAs fit an SM (296 slots): with that many (sequence, kv head)
+// pairs or more, one split each is fastest (a second wave of CTAs costs more than it saves); below that the pairs
+// are split so that the grid fills the slots without spilling into a second wave, each split keeping at least
+// 24 pages (two page pairs per warp) to amortise the per-CTA query expansion and merge.
 inline int choose_splits_fp8(int64_t B, int hkv, int64_t max_seq_len) {
 #ifdef TSB_TUNE
   if (const char* e = getenv("TSB_ATTN_SPLITS")) return atoi(e);
 #endif
   const int64_t base = B * hkv;
   const int64_t pages = (max_seq_len + 15) / 16;
-  int64_t s = (148 * 2 + base - 1) / (base > 0 ? base : 1);
-  if (base >= 148) s = 1;
-  const int64_t cap = pages / 128 > 0 ? pages / 128 : 1;
+  int64_t s = base > 0 ? 296 / base : 1;
+  if (s < 3) s = 1;              // two splits measured no faster than one (128 pairs, context 2k)
+  const int64_t cap = pages / 24 > 0 ? pages / 24 : 1;
   if (s > cap) s = cap;
   if (s < 1) s = 1;
   if (s > 64) s = 64;
