@@ -3,17 +3,26 @@
 Workload (BASELINE.json configs[3]): Llama-3-8B architecture (32 layers, hidden 4096, 32 query /
 8 KV heads, head_dim 128, MLP 14336, vocab 128256), bf16 activations; every MLP linear low-rank
 at 25% of full rank (r = 1024); every block linear 4-bit per-channel fixed point; lm_head dense
-bf16; FP8-e4m3 paged KV cache (page 16).  Batch 32 sequences PER GPU with a 2048-token context,
-greedy decode.  One "step" = one decode step of the whole batch (32 new tokens per GPU).
-Weights are seeded random factors and the prompt KV is seeded random data of that shape
-(`data: synthetic`): there is no checkpoint or dataset in this environment.
+bf16 (it is a separate `final_layer` scheme in the reference, utils/manager.py:1021-1046, which the
+configuration's "all linears" does not reach); FP8-e4m3 paged KV cache (page 16).  Batch 32 sequences
+PER GPU with a 2048-token context, greedy decode.  One "step" = one decode step of the whole batch
+(32 new tokens per GPU).  Weights are seeded random factors and the prompt KV is seeded random data
+of that shape (`data: synthetic`): there is no checkpoint or dataset in this environment.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
 
+JSON line of the GPU arm: `value` = device-resident graph-replayed steps, `e2e` = the same through
+`CompressedDecoder.step(host tokens)` with the copies inside the timed region; `roofline` = the kernel with
+the largest share of the step (the packed-weight GEMM kernel: its three launches per layer timed one by one),
+`roofline_attention` = the decode-attention launch; fractions against the measured copy bandwidth
+(`frac`) and against the 8 TB/s nominal figure (`frac_nominal`); `sweeps` = op-level cases of
+configs[1] / configs[2] (N = 1 only); `cpu_baseline` = a bounded sample of the reference's CPU path.
 Multi-GPU (torchrun, one rank per GPU): independent replicas, sequences sharded by rank, no
-data-path collective (weak scaling); time = max over ranks of the CUDA-event time.
-`--impl reference` times the reference's CPU path (PyTorch CPU ops restated in oracle/) on a
-bounded sample of the same workload on the host cores.
+data-path collective (weak scaling); time = max over ranks of the CUDA-event time; for N > 1 a `tp`
+record follows from a second, tensor-parallel engine over the same ranks (one batch of 32 shared:
+strong scaling).
+`--impl reference` times the reference's own CPU code (oracle/_ref; oracle/ref_decode.py) on the host
+cores: `--steps` full-depth decode steps of the same workload.
 """
 import argparse
 import json
@@ -29,12 +38,13 @@ if ROOT not in sys.path:
 
 LLAMA3_8B = dict(num_layers=32, hidden=4096, num_heads=32, num_kv_heads=8, head_dim=128, intermediate=14336,
                  vocab=128256, rope_theta=5e5, rms_eps=1e-5)
-# Kernel that serves each KV format, and dram__bytes_read.sum + dram__bytes_write.sum per algorithmic
-# byte from an ncu capture of that kernel (profiles/decode_attn_fp8_mma_b32_ctx4096.md: 269.84 MB +
-# 5.07 MB against 268.4 MB algorithmic; profiles/decode_attn_mma_f16widen_fp8_b32_ctx4096.md for the
-# f16-widening kernel).  The traffic of these kernels grows in proportion to the KV bytes.
+# Kernel that serves each KV format, and DRAM bytes (read + write) per algorithmic byte from one ncu capture
+# of that kernel on a smaller case (batch 32 x context 4096: 274.9 MB against 268.4 MB algorithmic; packed
+# GEMMs of one layer: 50.5 MB against 49.3 MB).  The traffic of these kernels grows in proportion to the bytes.
 ATTN_KERNEL = {"fp8": "decode_attn_fp8_kernel (split merge fused)", "int8": "decode_attn_mma_kernel (split merge fused)"}
 NCU_DRAM_PER_ALG_BYTE = {"fp8": (269.84 + 5.07) / 268.4}
+NCU_DRAM_PER_ALG_BYTE_LINEAR = (12.940 + 8.738 + 28.788) / (12.58 + 8.39 + 28.31)
+HBM_NOMINAL_GBS = 8000.0
 METRIC = "decode tokens/s (Llama-3-8B LRD+W4+FP8-KV)"
 
 
@@ -61,6 +71,7 @@ def parse():
     ap.add_argument("--sweep-m", default="1,16,128,2048", help="token counts of the linear sweep")
     ap.add_argument("--sweep-ctx", default="4096,16384,32768", help="contexts of the attention sweep")
     ap.add_argument("--sweep-batch", type=int, default=64)
+    ap.add_argument("--no-sweeps", action="store_true", help="N = 1: leave the op-level `sweeps` records out of the line")
     return ap.parse_args()
 
 
@@ -165,8 +176,7 @@ def build_engine(a, device, seed, tp_world=1, tp_rank=0):
         outl[h, torch.randperm(d, generator=g, device=device)[:4]] = 20.0
     for kv in dec.kv:
         if a.kv == "fp8":
-            kv.k_scale.fill_(20.0 * 5.5 / 448.0)
-            kv.v_scale.fill_(20.0 * 5.5 / 448.0)
+            kv.fill_fp8_scales(20.0 * 5.5 / 448.0, 20.0 * 5.5 / 448.0)
         dec.seq_lens.zero_()
         for t0 in range(0, a.context, chunk):
             n = min(chunk, a.context - t0)
@@ -178,23 +188,22 @@ def build_engine(a, device, seed, tp_world=1, tp_rank=0):
     return dec
 
 
-def time_attention_kernel(dec, a, reps=5):
-    """CUDA-event time of one decode-attention call (split kernel + reducer).  The calls for all
-    layers are captured in one CUDA graph (so the host launch rate does not limit the measurement)
-    and cycle through the layers' caches, so no launch finds its pages in L2 (one layer's cache is
-    larger than L2)."""
+def _graph_time_us(fn, copies, reps=5, pdl=True):
+    """Average time (us) of fn(i), i = 0..copies-1, replayed from one CUDA graph, CUDA events on the replay stream.
+    The calls are captured with programmatic dependent launch, as the decode step captures them."""
     import torch
     from transformer_surgeon_b200 import ops
-    c = dec.cfg
-    q = torch.randn((dec.B, dec.H_local, c.head_dim), device=dec.device).to(c.dtype)
-    out = torch.empty_like(q)
-    for kv in dec.kv[:2]:
-        ops.paged_decode_attention(kv, q, dec.max_seq_len, out=out, ws=dec.attn_ws)
+    for i in range(min(2, copies)):
+        fn(i)
     torch.cuda.synchronize()
-    g = torch.cuda.CUDAGraph()
-    with torch.cuda.graph(g):
-        for kv in dec.kv:
-            ops.paged_decode_attention(kv, q, dec.max_seq_len, out=out, ws=dec.attn_ws)
+    old = ops.set_pdl(pdl)
+    try:
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for i in range(copies):
+                fn(i)
+    finally:
+        ops.set_pdl(old)
     g.replay()
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -203,107 +212,161 @@ def time_attention_kernel(dec, a, reps=5):
         g.replay()
     e1.record()
     torch.cuda.synchronize()
-    return e0.elapsed_time(e1) / (reps * len(dec.kv))
+    return e0.elapsed_time(e1) * 1000.0 / (reps * copies)
 
 
-def time_mlp_kernel(dec, reps=5):
-    """CUDA-event time of one fused gated-MLP launch (linear_tcq_kernel, four phases), cycling through the
-    layers' weights inside one CUDA graph so that no launch finds its weights in L2 when the model is deep."""
+def time_layer_kernels(dec, a):
+    """CUDA-event time per launch of the four large kernels of a decoder layer, each replayed from a CUDA graph that
+    cycles through ALL layers' weights / caches, so that no launch finds its operands in L2 (one layer's cache and
+    the weights of a few layers exceed it): the three packed-weight GEMM launches (q|k|v, o_proj, the gated MLP) and
+    the decode attention.  Returns microseconds."""
     import torch
-    x = torch.randn((dec.B, dec.cfg.hidden), device=dec.device).to(dec.cfg.dtype)
-    out = torch.empty_like(x)
-    for L in dec.layers[:2]:
-        L.mlp(x, out=out, ws=dec.mlp_ws)
-    torch.cuda.synchronize()
-    g = torch.cuda.CUDAGraph()
-    with torch.cuda.graph(g):
-        for L in dec.layers:
-            L.mlp(x, out=out, ws=dec.mlp_ws)
-    g.replay()
-    torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(reps):
-        g.replay()
-    e1.record()
-    torch.cuda.synchronize()
-    return e0.elapsed_time(e1) / (reps * len(dec.layers))
+    c = dec.cfg
+    B, H, d = dec.B, dec.H_local, c.head_dim
+    x = torch.randn((B, c.hidden), device=dec.device).to(c.dtype)
+    att = torch.randn((B, H * d), device=dec.device).to(c.dtype)
+    q = torch.randn((B, H, d), device=dec.device).to(c.dtype)
+    out = torch.empty_like(q)
+    n = len(dec.layers)
+    from transformer_surgeon_b200 import ops
+    t = {}
+    if dec.layers[0].qkv is not None:
+        t["qkv"] = _graph_time_us(lambda i: dec.layers[i].qkv(x, out=dec.qkv, ws=dec.lin_ws), n)
+    t["o_proj"] = _graph_time_us(lambda i: dec.layers[i].o(att, out=dec.delta, ws=dec.lin_ws), n)
+    t["mlp"] = _graph_time_us(lambda i: dec.layers[i].mlp(x, out=dec.delta, ws=dec.mlp_ws), n)
+    t["attention"] = _graph_time_us(lambda i: ops.paged_decode_attention(dec.kv[i], q, dec.max_seq_len, out=out, ws=dec.attn_ws), n)
+    return t
 
 
 # ------------------------------------------------------------------------------ CPU reference arm
-def cpu_reference_sample(a, steps, warmup):
-    """One decoder layer of the workload at full width on the host cores, the way the reference runs
-    it: LinearCompressed.forward on dequantized bf16 factors (blocks/linear_compressed.py:81-105),
-    attention() over a dense cache per sequence (blocks/mha.py:9-103), RMSNorm, SwiGLU, plus the
-    lm_head; per-layer time is scaled to the full depth.  Returns (tokens/s, sample description)."""
-    import torch
-    from oracle import linear as olin, attention as oatt
-    torch.set_num_threads(os.cpu_count() or 1)
+def cpu_decode(a):
+    """The workload's decode step on the host cores (oracle/ref_decode.py: the reference's own classes from
+    oracle/_ref when installed, else the port)."""
+    from oracle import ref_decode
     c = LLAMA3_8B
-    H, Hkv, d, hid, inter = c["num_heads"], c["num_kv_heads"], c["head_dim"], c["hidden"], c["intermediate"]
-    B, L, r = a.batch, a.context, a.rank
-    g = torch.Generator().manual_seed(0)
-    dt = torch.bfloat16
-    rn = lambda *s: (torch.randn(*s, generator=g) * 0.02).to(dt)
-    wq, wk, wv, wo = rn(H * d, hid), rn(Hkv * d, hid), rn(Hkv * d, hid), rn(hid, H * d)
-    ug, vg, uu, vu, ud, vd = rn(inter, r), rn(r, hid), rn(inter, r), rn(r, hid), rn(hid, r), rn(r, inter)
-    lm = rn(c["vocab"], hid)
-    w1 = torch.ones(hid, dtype=dt)
-    kc = torch.randn(B, L + 1, Hkv, d, generator=g).to(dt)
-    vc = torch.randn(B, L + 1, Hkv, d, generator=g).to(dt)
-    cos, sin = oatt.rope_tables(d, c["rope_theta"], torch.arange(L, L + 1))
-    x = torch.randn(B, hid, generator=g).to(dt)
+    return ref_decode, ref_decode.make_decode(hidden=c["hidden"], heads=c["num_heads"], kv_heads=c["num_kv_heads"],
+                                              inter=c["intermediate"], vocab=c["vocab"], rank=a.rank, batch=a.batch,
+                                              context=a.context, theta=c["rope_theta"], eps=c["rms_eps"])
 
-    def layer(x):
-        xn = oatt.rmsnorm_hf(x, w1, c["rms_eps"])
-        q = olin.linear_compressed_forward(xn, wq).view(B, 1, H, d)
-        k = olin.linear_compressed_forward(xn, wk).view(B, 1, Hkv, d)
-        v = olin.linear_compressed_forward(xn, wv).view(B, 1, Hkv, d)
-        q, k = oatt.apply_rope(q, cos, sin), oatt.apply_rope(k, cos, sin)
-        kc[:, L] = k[:, 0]
-        vc[:, L] = v[:, 0]
-        att = torch.stack([oatt.attention(q[b], kc[b], vc[b])[:, 0] for b in range(B)]).to(dt)
-        h = x + olin.linear_compressed_forward(att.reshape(B, H * d), wo)
-        hn = oatt.rmsnorm_hf(h, w1, c["rms_eps"])
-        m = oatt.swiglu(olin.linear_compressed_forward(hn, ug, None, vg), olin.linear_compressed_forward(hn, uu, None, vu))
-        return h + olin.linear_compressed_forward(m, ud, None, vd)
 
-    def head(x):
-        return torch.argmax(olin.linear_compressed_forward(oatt.rmsnorm_hf(x, w1, c["rms_eps"]), lm), dim=-1)
-
-    with torch.no_grad():
-        for _ in range(warmup):
-            layer(x); head(x)
-        t0 = time.perf_counter()
-        for _ in range(steps):
-            layer(x)
-        t_layer = (time.perf_counter() - t0) / steps
-        t0 = time.perf_counter()
-        for _ in range(steps):
-            head(x)
-        t_head = (time.perf_counter() - t0) / steps
-    step_s = a.layers * t_layer + t_head
-    sample = (f"1 decoder layer (batch {B}, context {L}, dense bf16 KV, dequantized bf16 factors) x{steps} "
-              f"+ lm_head, scaled to {a.layers} layers; torch CPU, {os.cpu_count()} threads")
-    return B / step_s, step_s * 1e3, sample
+def cpu_baseline_sample(a):
+    """Bounded sample for the GPU arm's line: 2 steps of 4 layers + lm_head, the per-layer share scaled to full depth."""
+    rd, dec = cpu_decode(a)
+    t_head = rd.time_steps(dec, 2, 1, 0)
+    t_4 = rd.time_steps(dec, 2, 1, 4)
+    step_s = (t_4 - t_head) / 4 * a.layers + t_head
+    return {"value": a.batch / step_s, "unit": "tokens/s", "cores": os.cpu_count(), "kind": dec.kind,
+            "sample": "2 decode steps of 4 decoder layers + lm_head (batch %d, context %d, dense bf16 KV, bf16 fake-quantized "
+                      "factors), per-layer time scaled to %d layers; %d threads" % (a.batch, a.context, a.layers, os.cpu_count())}
 
 
 def run_reference(a):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    steps, warmup = min(a.steps, 3), min(a.warmup, 1)
-    tps, ms, sample = cpu_reference_sample(a, steps, max(warmup, 1))
+    rd, dec = cpu_decode(a)
+    step_s = rd.time_steps(dec, a.steps, a.warmup, a.layers)          # every step at full depth, as many as asked for
+    tps = a.batch / step_s
+    sample = ("%d full-depth decode steps (%d layer calls each, one layer's weights and cache reused; batch %d, context %d, "
+              "dense bf16 KV); %d threads" % (a.steps, a.layers, a.batch, a.context, os.cpu_count()))
     line = {"impl": "reference", "metric": METRIC, "value": tps, "unit": "tokens/s", "n_gpus": a.gpus, "steps": a.steps,
-            "warmup": a.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "warmup": a.warmup, "ms_per_step": step_s * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": "llama3-8b-arch decode, MLP LRD r=%d, W%d, batch %d, context %d (CPU: dense bf16 KV)" % (a.rank, a.wbits, a.batch, a.context)},
-            "cpu_baseline": {"value": tps, "unit": "tokens/s", "cores": os.cpu_count(), "kind": "port", "sample": sample},
+            "config": {"workload": "llama3-8b-arch decode: %d layers, MLP LRD r=%d, W%d fake-quantized factors, lm_head bf16, batch %d, "
+                                   "context %d (the reference has no quantized KV cache: dense bf16 KV)"
+                                   % (a.layers, a.rank, a.wbits, a.batch, a.context)},
+            "cpu_baseline": {"value": tps, "unit": "tokens/s", "cores": os.cpu_count(), "kind": dec.kind, "sample": sample},
             "e2e": {"value": tps, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line))
 
 
 # ------------------------------------------------------------------------------ GPU arm
+def layer_weight_bytes(a):
+    """Algorithmic bytes of the three packed-weight GEMM launches of a layer: codes + fp32 row scales + bf16 in/out."""
+    c = LLAMA3_8B
+    H, Hkv, d, hid, inter, r, B = c["num_heads"], c["num_kv_heads"], c["head_dim"], c["hidden"], c["intermediate"], a.rank, a.batch
+    wb = a.wbits / 8.0
+    act = lambda k, n: 2.0 * B * (k + n)
+    qkv_n = (H + 2 * Hkv) * d
+    return {"qkv": qkv_n * hid * wb + 4 * qkv_n + act(hid, qkv_n),
+            "o_proj": hid * H * d * wb + 4 * hid + act(H * d, hid),
+            "mlp": 3 * (inter * r + r * hid) * wb + 4 * (2 * (inter + r) + hid + r) + act(hid, hid)}
+
+
+def timed_steps(dec, a, tok_host, out_host, barrier, sampler=None):
+    """(ms of K device-resident steps, ms of K end-to-end steps, context at the start)."""
+    import torch
+    dec.tokens.copy_(tok_host)
+    for _ in range(a.warmup):
+        dec.step()
+    barrier()
+    if sampler is not None:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ctx0 = int(dec.seq_lens[0].item())
+    e0.record()
+    for _ in range(a.steps):
+        dec.step()
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1)
+    # ---- end to end through the public call: host tokens in, host tokens out, every step
+    saved = dec.seq_lens.clone()
+    dec.seq_lens.fill_(ctx0)               # rewind: same contexts as the device-timed steps
+    barrier()
+    e2, e3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e2.record()
+    for _ in range(a.steps):
+        dec.step(tok_host)                                  # H2D of the step's input tokens
+        out_host.copy_(dec.next_tokens, non_blocking=True)  # D2H of the step's result
+        torch.cuda.current_stream().synchronize()
+        tok_host.copy_(out_host)                            # greedy feedback on the host
+    e3.record()
+    barrier()
+    ms_e2e = e2.elapsed_time(e3)
+    dec.seq_lens.copy_(saved)
+    return ms, ms_e2e, ctx0
+
+
+def tp_leg(a, device, world, rank, barrier):
+    """Tensor-parallel engine over the same ranks (one batch of `a.batch` sequences shared: strong scaling).
+    Returns the record for the JSON line (rank 0) - time = max over ranks of the CUDA-event time."""
+    import torch
+    import torch.distributed as dist
+    dec = build_engine(a, device, seed=1, tp_world=world, tp_rank=rank)
+    mode = "nccl"
+    if a.tp_allreduce == "peer":
+        try:
+            if dec.enable_peer_allreduce():
+                mode = "peer"
+        except RuntimeError as ex:           # raised on every rank alike: all of them stay on NCCL
+            if rank == 0:
+                print("peer all-reduce unavailable, using NCCL: %s" % ex, file=sys.stderr)
+    dec.capture()
+    tgen = torch.Generator().manual_seed(7)                 # every rank feeds the same tokens
+    tok_host = torch.randint(0, dec.cfg.vocab, (a.batch,), generator=tgen, dtype=torch.int64).pin_memory()
+    out_host = torch.empty(a.batch, dtype=torch.int64).pin_memory()
+    ms, ms_e2e, ctx0 = timed_steps(dec, a, tok_host, out_host, barrier)
+    status = dec.peer.status() if dec.peer is not None else 0
+    t = torch.tensor([ms, ms_e2e, float(status)], device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    rec = {"ranks": world, "batch_total": a.batch, "scaling": "strong", "ms_per_step": float(t[0]) / a.steps,
+           "tokens_per_s": a.batch * a.steps / (float(t[0]) * 1e-3), "e2e_tokens_per_s": a.batch * a.steps / (float(t[1]) * 1e-3),
+           "allreduce": ("tsb200_peer_allreduce_add_rmsnorm: all-reduce + residual add + RMSNorm in one kernel over NVLink peer loads"
+                         if mode == "peer" else "NCCL all-reduce (captured in the step graph)"),
+           "collectives_per_step": 2 * a.layers, "allreduce_bytes": a.batch * LLAMA3_8B["hidden"] * 2,
+           "peer_status": int(t[2]), "context": ctx0}
+    # Teardown order matters: a captured graph that holds NCCL kernels keeps the communicator referenced, and tearing
+    # the process group down while such a graph is alive blocks.  So: drop the graph, collect, synchronise, and only
+    # then let the caller destroy the group.
+    dec.graph = None
+    del dec
+    import gc
+    gc.collect()
+    torch.cuda.synchronize()
+    return rec
+
+
 def run_ours(a):
     import torch
     import torch.distributed as dist
@@ -318,219 +381,218 @@ def run_ours(a):
     import __graft_entry__ as ge
     if not os.path.exists(os.path.join(ROOT, "transformer-surgeon_b200", "libtsb200.so")):
         ge.build()
-    tp = a.parallel == "tp" and world > 1
-    dec = build_engine(a, device, seed=1 if tp else 1 + rank, tp_world=world if tp else 1, tp_rank=rank if tp else 0)
-    peer_ar = False
-    if tp and a.tp_allreduce == "peer":
-        try:
-            peer_ar = dec.enable_peer_allreduce()
-        except RuntimeError as ex:           # raised on every rank alike: all of them stay on NCCL
-            if rank == 0:
-                print("peer all-reduce unavailable, using NCCL: %s" % ex, file=sys.stderr)
-    dec.capture()
-    B = a.batch
-    tgen = torch.Generator().manual_seed(7 if tp else 7 + rank)     # tensor parallel: every rank feeds the same tokens
-    tok_host = torch.randint(0, dec.cfg.vocab, (B,), generator=tgen, dtype=torch.int64).pin_memory()
-    out_host = torch.empty(B, dtype=torch.int64).pin_memory()
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
-    # ---- device-resident steps (inputs already in HBM): `value`
-    dec.tokens.copy_(tok_host)
-    for _ in range(a.warmup):
-        dec.step()
-    sampler = ClockSampler(local)
-    barrier()
-    if rank == 0:
-        sampler.start()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    ctx0 = int(dec.seq_lens[0].item())
-    e0.record()
-    for _ in range(a.steps):
-        dec.step()
-    e1.record()
-    barrier()
-    ms = e0.elapsed_time(e1)
+    if a.parallel == "tp" and world > 1:                     # tensor parallel only (development runs)
+        rec = tp_leg(a, device, world, rank, barrier)
+        if rank == 0:
+            print(json.dumps({"metric": METRIC, "value": rec["tokens_per_s"], "unit": "tokens/s", "n_gpus": world, "steps": a.steps,
+                              "warmup": a.warmup, "ms_per_step": rec["ms_per_step"], "higher_is_better": True, "scaling": "strong",
+                              "tp": rec}))
+        barrier()
+        dist.destroy_process_group()
+        return
+    dec = build_engine(a, device, seed=1 + rank)
+    dec.capture()
+    B = a.batch
+    tgen = torch.Generator().manual_seed(7 + rank)
+    tok_host = torch.randint(0, dec.cfg.vocab, (B,), generator=tgen, dtype=torch.int64).pin_memory()
+    out_host = torch.empty(B, dtype=torch.int64).pin_memory()
+    sampler = ClockSampler(local) if rank == 0 else None
+    ms, ms_e2e, ctx0 = timed_steps(dec, a, tok_host, out_host, barrier, sampler)
+    t_k = time_layer_kernels(dec, a)                          # still under the clock sampler: more samples under load
     clocks = sampler.stop() if rank == 0 else None
-    # ---- end to end through the public call: host tokens in, host tokens out, every step
-    saved = dec.seq_lens.clone()
-    dec.seq_lens.fill_(a.context)          # rewind: same contexts as the device-timed steps
-    barrier()
-    e2, e3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e2.record()
-    for _ in range(a.steps):
-        dec.step(tok_host)                                  # H2D of the step's input tokens
-        out_host.copy_(dec.next_tokens, non_blocking=True)  # D2H of the step's result
-        torch.cuda.current_stream().synchronize()
-        tok_host.copy_(out_host)                            # greedy feedback on the host
-    e3.record()
-    barrier()
-    ms_e2e = e2.elapsed_time(e3)
-    dec.seq_lens.copy_(saved)
-    # per-kernel timing captures a second CUDA graph; kept out of the tensor-parallel mode, whose ranks
-    # must stay in lockstep on the NCCL communicator
-    t_attn = time_attention_kernel(dec, a) if not tp else None   # tensor parallel: the kernel is not timed alone
-    t_mlp = time_mlp_kernel(dec) if not tp else None
+    dec.check_status()
+    launches = dec.kernel_launches_per_step
     if world > 1:
         t = torch.tensor([ms, ms_e2e], device=device)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms, ms_e2e = float(t[0]), float(t[1])
+    line, rec, done = None, None, threading.Event()
     if rank == 0:
         peak, which = peaks()
         ctx_mid = ctx0 + a.steps // 2
-        step_bytes, attn_bytes = algorithmic_bytes(a, ctx_mid)
+        step_bytes, _ = algorithmic_bytes(a, ctx_mid)
         attn_alg = algorithmic_bytes(a, int(dec.seq_lens[0].item()))[1]
-        achieved = attn_alg / (t_attn * 1e-3) / 1e9 if t_attn else None
-        seqs = B if tp else world * B                  # tensor parallel: one batch shared by all ranks
-        tps = seqs * a.steps / (ms * 1e-3)
+        tps = world * B * a.steps / (ms * 1e-3)
+        wbytes = layer_weight_bytes(a)
+        lin_names = [k for k in ("qkv", "o_proj", "mlp") if k in t_k]
+        lin_us = sum(t_k[k] for k in lin_names)
+        lin_bytes = sum(wbytes[k] for k in lin_names)
+        step_us = ms / a.steps * 1e3
+
+        def hbm(bytes_, us):
+            gbs = bytes_ / us / 1e3
+            return {"achieved": gbs, "peak": peak, "unit": "GB/s", "frac": gbs / peak, "peak_source": which,
+                    "frac_nominal": gbs / HBM_NOMINAL_GBS, "peak_nominal": HBM_NOMINAL_GBS}
+
+        lin_rec = {"kernel": "linear_tcq_kernel (packed-weight GEMM; 3 launches per layer: q|k|v, o_proj, gated MLP)", "bound": "hbm",
+                   **hbm(lin_bytes, lin_us), "traffic": lin_bytes * NCU_DRAM_PER_ALG_BYTE_LINEAR / len(lin_names),
+                   "traffic_source": "dram bytes of one ncu capture of the three launches (4-layer case), per launch, scaled by algorithmic bytes",
+                   "algorithmic_bytes_per_launch": lin_bytes / len(lin_names), "ms_per_launch": lin_us / len(lin_names) * 1e-3,
+                   "share_of_step": a.layers * lin_us / step_us,
+                   "launches": {k: {"us": t_k[k], "bytes": wbytes[k], **hbm(wbytes[k], t_k[k])} for k in lin_names},
+                   "step_achieved": step_bytes / (step_us * 1e-6) / 1e9, "step_frac": step_bytes / (step_us * 1e-6) / 1e9 / peak}
+        att_rec = {"kernel": ATTN_KERNEL.get(a.kv, "decode_attn_simt_kernel"), "bound": "hbm", **hbm(attn_alg, t_k["attention"]),
+                   "traffic": (attn_alg * NCU_DRAM_PER_ALG_BYTE[a.kv]) if a.kv in NCU_DRAM_PER_ALG_BYTE else None,
+                   "traffic_source": "dram bytes of one ncu capture (batch 32 x context 4096) scaled by algorithmic bytes",
+                   "ms_per_launch": t_k["attention"] * 1e-3, "share_of_step": a.layers * t_k["attention"] / step_us,
+                   "parity": "KV formats are this project's definitions: parity unpinned"}
+        dominant_linear = lin_us >= t_k["attention"]
         line = {"metric": METRIC, "value": tps, "unit": "tokens/s", "n_gpus": world, "steps": a.steps, "warmup": a.warmup,
-                "ms_per_step": ms / a.steps, "higher_is_better": True, "scaling": "strong" if tp else "weak", "vs_baseline": None,
+                "ms_per_step": ms / a.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
                 "dtype": "bf16", "data": "synthetic",
-                "config": {"workload": "llama3-8b-arch decode: %d layers, MLP LRD r=%d, W%d per-channel, %s paged KV, "
-                           "batch %d/GPU, context %d->%d" % (a.layers, a.rank, a.wbits, a.kv, B, ctx0, ctx0 + a.steps),
-                           "sharding": ("tensor parallel x%d: heads / MLP columns split, 2 all-reduces per layer (%s), batch %d shared"
-                                        % (world, "fused with add + RMSNorm over NVLink peer loads" if peer_ar else "NCCL", B))
-                           if tp else "replicas, %d sequences per GPU, no collective" % B,
+                "config": {"workload": "llama3-8b-arch decode: %d layers, MLP LRD r=%d, W%d per-channel block linears, lm_head bf16, "
+                           "%s paged KV, batch %d/GPU, context %d->%d" % (a.layers, a.rank, a.wbits, a.kv, B, ctx0, ctx0 + a.steps),
+                           "sharding": "replicas, %d sequences per GPU, no collective" % B,
                            "l2": "inputs larger than L2 (%.1f GB read per step)" % (step_bytes / 1e9),
                            "cuda_graph": True},
-                "e2e": {"value": seqs * a.steps / (ms_e2e * 1e-3), "unit": "tokens/s",
+                "e2e": {"value": world * B * a.steps / (ms_e2e * 1e-3), "unit": "tokens/s",
                         "h2d_bytes_per_step": B * 8, "d2h_bytes_per_step": B * 8},
-                "gpu_launches": dec.kernel_launches_per_step * a.steps,
+                "gpu_launches": launches * a.steps,
                 "clocks": clocks,
-                "roofline": {"kernel": ATTN_KERNEL.get(a.kv, "decode_attn_simt_kernel"), "bound": "hbm", "achieved": achieved,
-                             "peak": peak, "unit": "GB/s", "frac": achieved / peak if achieved else None, "peak_source": which,
-                             "traffic": (attn_alg * NCU_DRAM_PER_ALG_BYTE[a.kv]) if a.kv in NCU_DRAM_PER_ALG_BYTE else None,
-                             "traffic_source": "dram bytes of one ncu capture (batch 32 x context 4096) scaled by algorithmic bytes",
-                             "ms_per_launch": t_attn,
-                             "step_achieved": step_bytes / (ms / a.steps * 1e-3) / 1e9,
-                             "step_frac": step_bytes / (ms / a.steps * 1e-3) / 1e9 / peak}}
-        if t_mlp:
-            # the other large kernel of the step, for the record: the fused gated MLP moves its packed weights once
-            # per launch and is bound by dependent latencies (phases, split-K rendezvous), not by HBM
-            c = LLAMA3_8B
-            mlp_bytes = 3 * (c["intermediate"] * a.rank + a.rank * c["hidden"]) * a.wbits / 8.0
-            line["roofline_mlp"] = {"kernel": "linear_tcq_kernel (gated MLP: 4 GEMM phases in one launch)", "bound": "hbm",
-                                    "achieved": mlp_bytes / (t_mlp * 1e-3) / 1e9, "peak": peak, "unit": "GB/s",
-                                    "frac": mlp_bytes / (t_mlp * 1e-3) / 1e9 / peak, "ms_per_launch": t_mlp}
+                "roofline": lin_rec if dominant_linear else att_rec,
+                ("roofline_attention" if dominant_linear else "roofline_linear"): att_rec if dominant_linear else lin_rec}
+    if world == 1 and rank == 0:
+        del dec
+        torch.cuda.empty_cache()
+        if not a.no_sweeps:
+            try:
+                line["sweeps"] = {"linear": sweep_linear(a, ranks=(1024,), precisions=(4,), ms=(1, 128, 2048), copies=4),
+                                  "attention": sweep_attention(a, contexts=(4096,))}
+            except Exception as ex:          # a sweep must not hide the headline
+                line["sweeps"] = {"error": repr(ex)}
         try:
-            cpu_tps, _, sample = cpu_reference_sample(a, 2, 1) if world == 1 else (None, None, None)
-            if cpu_tps is not None:
-                line["cpu_baseline"] = {"value": cpu_tps, "unit": "tokens/s", "cores": os.cpu_count(), "kind": "port",
-                                        "sample": sample}
-        except Exception as ex:  # the CPU leg must not hide the GPU result
+            line["cpu_baseline"] = cpu_baseline_sample(a)
+        except Exception as ex:              # the CPU leg must not hide the GPU result
             line["cpu_baseline"] = {"value": None, "error": repr(ex)}
-        print(json.dumps(line))
+    elif world > 1:
+        # second engine over the same ranks: tensor parallel, one shared batch.  A watchdog bounds the leg so that the
+        # replica result is printed whatever happens to it.
+        del dec
+        torch.cuda.empty_cache()
+
+        def watchdog():
+            if not done.wait(240.0):
+                if rank == 0:
+                    line["tp"] = {"error": "tensor-parallel leg did not finish within 240 s"}
+                    print(json.dumps(line), flush=True)
+                os._exit(0)
+        threading.Thread(target=watchdog, daemon=True).start()
+        try:
+            rec = tp_leg(a, device, world, rank, barrier)
+        except Exception as ex:
+            rec = {"error": repr(ex)}
+        if rank == 0:
+            line["tp"] = rec
+    if rank == 0:
+        print(json.dumps(line), flush=True)
     if world > 1:
-        if tp:
-            # the captured step holds NCCL work: drop the graph and leave without tearing the communicator
-            # down (destroying the group with a live graph has been seen to block at exit)
-            dec.graph = None
-            torch.cuda.synchronize()
-            sys.stdout.flush()
-            os._exit(0)
+        if rec is not None and "error" in rec:
+            os._exit(0)                      # a failed leg may have left collectives unmatched: leave without a teardown
+        barrier()
         dist.destroy_process_group()
+        done.set()
 
 
-def _graph_time_us(fn, copies, reps=5):
-    """Average time of fn(i), i = 0..copies-1, replayed from one CUDA graph (CUDA events)."""
-    import torch
-    for i in range(min(2, copies)):
-        fn(i)
-    torch.cuda.synchronize()
-    g = torch.cuda.CUDAGraph()
-    with torch.cuda.graph(g):
-        for i in range(copies):
-            fn(i)
-    g.replay()
-    torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(reps):
-        g.replay()
-    e1.record()
-    torch.cuda.synchronize()
-    return e0.elapsed_time(e1) * 1000.0 / (reps * copies)
-
-
-def sweep_linear(a):
-    """configs[1]: x [M, 4096] bf16, W 4096x4096 factored at r in {256, 1024}, factors at 8 / 4 bits and
-    binary; time of LinearCompressed.forward per call, TFLOP/s and GB/s against the measured peaks."""
+def sweep_linear(a, ranks=(256, 1024), precisions=(8, 4, "binary"), ms=None, copies=8):
+    """configs[1]: x [M, 4096] bf16, W 4096x4096 factored at rank r, factors at 8 / 4 bits and binary; time of
+    LinearCompressed.forward per call, TFLOP/s and GB/s against the measured peaks.  Returns a list of records."""
     import torch
     from transformer_surgeon_b200 import ops
-    dev = torch.device("cuda", 0)
+    dev = torch.device("cuda", torch.cuda.current_device())
     g = torch.Generator(device=dev).manual_seed(2)
     peak_bw, _ = peaks()
-    for r in (256, 1024):
-        for p in (8, 4, "binary"):
-            n_copies = 8          # distinct weight copies: 8 x (r x 8192 codes) > L2 only for the larger cases; stated per line
+    ms = ms or [int(v) for v in a.sweep_m.split(",")]
+    out = []
+    for r in ranks:
+        for p in precisions:
             lins = []
-            for _ in range(n_copies):
+            for _ in range(copies):       # distinct weight copies cycled by the graph; their total size is stated per record
                 U = (torch.randn((4096, r), generator=g, device=dev) * 0.02).bfloat16()
                 V = (torch.randn((r, 4096), generator=g, device=dev) * 0.02).bfloat16()
                 lins.append(ops.PackedLinear(ops.Factor.quantize(U, p), ops.Factor.quantize(V, p), None, torch.bfloat16))
             bits = lins[0].u.bits
-            for M in [int(v) for v in a.sweep_m.split(",")]:
+            for M in ms:
                 x = torch.randn((M, 4096), generator=g, device=dev).bfloat16()
                 y = torch.empty((M, 4096), dtype=torch.bfloat16, device=dev)
                 ws = torch.zeros(lins[0].workspace_bytes(M), dtype=torch.uint8, device=dev)
-                us = _graph_time_us(lambda i: lins[i](x, out=y, ws=ws), n_copies)
+                us = _graph_time_us(lambda i: lins[i](x, out=y, ws=ws), copies)
                 flops = 2.0 * M * r * 8192
                 byts = r * 8192 * bits / 8 + (4096 + r) * 4 + 2 * M * 4096 * 2
-                print(json.dumps({"sweep": "linear", "M": M, "rank": r, "precision": p, "container_bits": bits,
-                                  "us_per_call": us, "tflops": flops / us / 1e6, "gbs": byts / us / 1e3,
-                                  "frac_hbm": byts / us / 1e3 / peak_bw, "frac_tensor_burst": flops / us / 1e6 / 1671.9,
-                                  "weights_mb_cycled": n_copies * r * 8192 * bits / 8 / 1e6}))
+                out.append({"sweep": "linear", "M": M, "rank": r, "precision": p, "container_bits": bits,
+                            "us_per_call": us, "tflops": flops / us / 1e6, "gbs": byts / us / 1e3,
+                            "frac_hbm": byts / us / 1e3 / peak_bw, "frac_tensor_burst": flops / us / 1e6 / 1671.9,
+                            "weights_mb_cycled": copies * r * 8192 * bits / 8 / 1e6})
+    return out
 
 
-def sweep_attention(a):
-    """configs[2]: 32 q heads / 8 kv heads / d 128, batch 64, page 16, seeded random block table, K/V
-    N(0,1) with 4 outlier channels per head (x20); decode attention and single-token append per format."""
+def sweep_attention(a, contexts=None, formats=("int8", "fp8", "nvfp4")):
+    """configs[2]: 32 q heads / 8 kv heads / d 128, batch 64, page 16, seeded random block table, K/V N(0,1) with 4
+    outlier channels per head (x20); per format: decode attention, single-token append, bulk append of 2048 tokens per
+    sequence.  KV formats are this project's definitions (parity unpinned).  Returns a list of records."""
     import torch
     from transformer_surgeon_b200 import ops
-    dev = torch.device("cuda", 0)
+    dev = torch.device("cuda", torch.cuda.current_device())
     g = torch.Generator(device=dev).manual_seed(3)
     peak_bw, _ = peaks()
     B, H, Hkv, d = a.sweep_batch, 32, 8, 128
     outl = torch.ones((Hkv, d), device=dev)
     for h in range(Hkv):
         outl[h, torch.randperm(d, generator=g, device=dev)[:4]] = 20.0
-    for L in [int(v) for v in a.sweep_ctx.split(",")]:
-        for fmt in ("int8", "fp8", "nvfp4"):
+    out = []
+    contexts = contexts or [int(v) for v in a.sweep_ctx.split(",")]
+    for L in contexts:
+        for fmt in formats:
             pages = L // 16 + 1
             rec = ops.kv_record_bytes(ops.KV_FORMATS[fmt], d)
             layers = max(1, min(4, int(3e9 // (B * pages * Hkv * rec * 2))))     # a few GB on the device at most
             kvs = []
             seq = torch.zeros(B, dtype=torch.int32, device=dev)
             bt = torch.randperm(B * pages, generator=g, device=dev).to(torch.int32).reshape(B, pages)
+            bulk_us = []
             for _ in range(layers):
                 kv = ops.PagedKV(fmt, B * pages, Hkv, d, bt, seq, dev)
                 if fmt == "fp8":
-                    kv.k_scale.fill_(110.0 / 448)
-                    kv.v_scale.fill_(110.0 / 448)
+                    kv.fill_fp8_scales(110.0 / 448, 110.0 / 448)
                 seq.zero_()
-                for t0 in range(0, L, 1024):
-                    n = min(1024, L - t0)
+                for t0 in range(0, L, 2048):
+                    n = min(2048, L - t0)
                     k = (torch.randn((B, n, Hkv, d), generator=g, device=dev) * outl).bfloat16()
                     v = (torch.randn((B, n, Hkv, d), generator=g, device=dev) * outl).bfloat16()
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    e0.record()
                     kv.append(k, v)
+                    e1.record()
+                    torch.cuda.synchronize()
+                    if n == 2048 and len(kvs) + t0 > 0:          # skip the very first call (module load, cold caches)
+                        bulk_us.append(e0.elapsed_time(e1) * 1e3)
                     seq += n
                 kvs.append(kv)
             q = torch.randn((B, H, d), generator=g, device=dev).bfloat16()
-            out = torch.empty_like(q)
+            o = torch.empty_like(q)
             ws = torch.zeros(ops.decode_attn_workspace_bytes(B, H, d, L + 16), dtype=torch.uint8, device=dev)
-            us = _graph_time_us(lambda i: ops.paged_decode_attention(kvs[i], q, L + 16, out=out, ws=ws), layers, reps=4)
+            us = _graph_time_us(lambda i: ops.paged_decode_attention(kvs[i], q, L + 16, out=o, ws=ws), layers, reps=4)
             byts = B * (L // 16) * Hkv * rec * 2 + B * (L // 16) * 4 + 2 * B * H * d * 2
             k1 = torch.randn((B, 1, Hkv, d), generator=g, device=dev).bfloat16()
             us_app = _graph_time_us(lambda i: kvs[i].append(k1, k1), layers, reps=4)
             app_bytes = B * 2 * Hkv * d * (2 + rec / (16.0 * d))
-            print(json.dumps({"sweep": "attention", "format": fmt, "batch": B, "context": L, "decode_us": us,
-                              "decode_gbs": byts / us / 1e3, "decode_frac_hbm": byts / us / 1e3 / peak_bw,
-                              "pages_mb": byts / 1e6, "append_us": us_app, "append_gbs": app_bytes / us_app / 1e3,
-                              "layers_cycled": layers}))
+            r = {"sweep": "attention", "format": fmt, "batch": B, "context": L, "decode_us": us,
+                 "decode_gbs": byts / us / 1e3, "decode_frac_hbm": byts / us / 1e3 / peak_bw,
+                 "decode_frac_nominal": byts / us / 1e3 / HBM_NOMINAL_GBS, "pages_mb": byts / 1e6,
+                 "append_us": us_app, "append_gbs": app_bytes / us_app / 1e3, "layers_cycled": layers}
+            if bulk_us:
+                bu = sorted(bulk_us)[len(bulk_us) // 2]
+                bulk_bytes = B * 2048 * 2 * Hkv * d * (2 + rec / (16.0 * d))
+                r.update(bulk_append_tokens=2048, bulk_append_us=bu, bulk_append_gbs=bulk_bytes / bu / 1e3,
+                         bulk_append_frac_hbm=bulk_bytes / bu / 1e3 / peak_bw)
+            out.append(r)
             del kvs
+    return out
 
 
 if __name__ == "__main__":
@@ -538,7 +600,8 @@ if __name__ == "__main__":
     if args.sweep:
         import torch
         torch.cuda.set_device(0)
-        (sweep_linear if args.sweep == "linear" else sweep_attention)(args)
+        for rec in (sweep_linear if args.sweep == "linear" else sweep_attention)(args):
+            print(json.dumps(rec))
     elif args.impl == "reference":
         run_reference(args)
     else:

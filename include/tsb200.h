@@ -234,8 +234,13 @@ int tsb200_kv_gather(const tsb200_kv_desc* kv, void* k_out, void* v_out, int dty
  * q, out [B, H, d] act dtype; attends over seq_lens[b] tokens (0 -> zeros).
  * max_seq_len bounds seq_lens (sizes the split grid; lengths above it are clamped).
  * q_batch_stride: elements between consecutive sequences of q (0 = H*d); out is dense.
- * The first 16384 bytes of the workspace hold split counters: zero-fill them ONCE before the
- * first use; every call leaves them zero.  One workspace must not serve overlapping calls. */
+ * max_seq_len must not exceed bt_stride * 16 (the block table covers it) and num_pages must be positive,
+ * else TSB200_ERR_ARG.
+ * The first 16384 bytes of the workspace hold split counters and, in the last 4 of them (byte 16380), a
+ * status word: zero-fill them ONCE before the first use; every completed call leaves the counters zero.
+ * The status word becomes non-zero when a kernel gave up on a bounded wait for its own copies (the output
+ * of that call is then not to be trusted); the caller reads and clears it.  One workspace must not serve
+ * overlapping calls. */
 size_t tsb200_paged_decode_attn_workspace_bytes(int64_t B, int H, int head_dim, int64_t max_seq_len);
 int tsb200_paged_decode_attn(const tsb200_kv_desc* kv, const void* q, void* out, int dtype,
                              int64_t q_batch_stride, int64_t B, int H, float sm_scale, int64_t max_seq_len,
@@ -251,13 +256,18 @@ int tsb200_paged_decode_attn_simt(const tsb200_kv_desc* kv, const void* q, void*
  * workspace and performs no allocation of any kind.  It is meant for callers that cannot call
  * cudaMalloc on their serving path (fixed-budget plugins, runtimes whose allocator must not be
  * re-entered, code already inside a stream capture).
- *   - capacity: tsb200_paged_decode_attn_static_capacity() bytes (8 MiB); a problem whose
- *     tsb200_paged_decode_attn_workspace_bytes(...) exceeds it is refused with
- *     TSB200_ERR_WORKSPACE.  Each GPU that loads the library holds the array until exit.
+ *   - capacity: tsb200_paged_decode_attn_static_capacity() bytes (8 MiB); a problem whose split
+ *     partials (16 KB + B * H * splits * (2 + head_dim) floats, splits as the library picks them for
+ *     this B, hkv and max_seq_len - never more than tsb200_paged_decode_attn_workspace_bytes(...))
+ *     exceed it is refused with TSB200_ERR_WORKSPACE.  Each GPU that loads the library holds the array
+ *     until exit.
  *   - the first call on a device resolves the array's device address (cudaGetSymbolAddress with
  *     that device current); make that first call before any stream capture begins.
  *   - all calls on a device share the array: two calls that may overlap on the GPU (different
- *     streams) race; the array keeps the previous call's contents and nothing needs clearing. */
+ *     streams) race.  The array keeps the previous call's contents.  Its first 16 KB (split counters and
+ *     status word) have to be zero when the kernels start; since an overlapped or interrupted call could
+ *     leave a counter stuck and the caller cannot reach the array, every call clears that head itself
+ *     with a cudaMemsetAsync on `stream` ahead of its kernels (no allocation involved). */
 size_t tsb200_paged_decode_attn_static_capacity(void);
 int tsb200_paged_decode_attn_static(const tsb200_kv_desc* kv, const void* q, void* out, int dtype,
                                     int64_t q_batch_stride, int64_t B, int H, float sm_scale,

@@ -33,20 +33,25 @@ def attention(query, key, value, attn_mask=None):
     return torch.matmul(p, v)
 
 
-def paged_decode_attention(kv, q):
+def paged_decode_attention(kv, q, with_abs=False):
     """kv: oracle.kv_cache.PagedKV, q: fp32 array [B,H,d] -> fp32 [B,H,d].
-    A sequence of length 0 yields zeros."""
+    A sequence of length 0 yields zeros.  with_abs: also return sum_t p_t |V_t,e| per output element (the
+    same softmax weights applied to |V|) - the natural scale of an element's rounding error, which the
+    tests use as the error bound instead of a global max |V|."""
     from .kv_cache import gather_all
     B, H, d = q.shape
     out = np.zeros((B, H, d), dtype=np.float32)
+    out_abs = np.zeros((B, H, d), dtype=np.float32)
     Ks, Vs = gather_all(kv)
     for b in range(B):
         if kv.seq_lens[b] == 0:
             continue
         K, V = Ks[b], Vs[b]
-        o = attention(torch.from_numpy(q[b:b + 1]), torch.from_numpy(K), torch.from_numpy(V))
-        out[b] = o[:, 0].numpy()
-    return out
+        qb = torch.from_numpy(q[b:b + 1])
+        out[b] = attention(qb, torch.from_numpy(K), torch.from_numpy(V))[:, 0].numpy()
+        if with_abs:
+            out_abs[b] = attention(qb, torch.from_numpy(K), torch.from_numpy(np.abs(V)))[:, 0].numpy()
+    return (out, out_abs) if with_abs else out
 
 
 def rope_tables(head_dim, base, positions):

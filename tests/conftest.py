@@ -47,3 +47,14 @@ def cuda():
     if not torch.cuda.is_available():
         pytest.skip("no CUDA device")
     return torch.device("cuda:0")
+
+
+@pytest.fixture(scope="session")
+def reference():
+    """The reference package itself, from oracle/_ref (placed there by `python oracle/make_ref.py`; it ships
+    with the working tree but is never committed).  Tests that need it are skipped when it is absent."""
+    from oracle import make_ref
+    try:
+        return make_ref.import_reference()
+    except ImportError as ex:
+        pytest.skip(str(ex))

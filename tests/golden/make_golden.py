@@ -166,7 +166,7 @@ def gen_model(family):
     ids = torch.randint(0, 256, (2, 12), generator=g)
     with torch.no_grad():
         logits = model(input_ids=ids).logits
-        toks = model.generate(ids, attention_mask=torch.ones_like(ids), max_new_tokens=8,
+        toks = model.generate(ids, attention_mask=torch.ones_like(ids), max_new_tokens=32,
                               do_sample=False, pad_token_id=0, eos_token_id=None)
     put(out, "ids", ids); put(out, "logits", logits); put(out, "tokens", toks)
     out["rope_theta"] = np.float64(getattr(cfg, "rope_theta", None) or cfg.rope_parameters["rope_theta"])

@@ -11,10 +11,20 @@ from oracle import attention as oatt
 pytestmark = pytest.mark.gpu
 DT = {"fp32": torch.float32, "bf16": torch.bfloat16}
 FMTS = ["int8", "fp8", "nvfp4"]
-# decode-attention tolerance: |out - oracle| <= ATOL_V*max|V| + RTOL*|oracle| (+2e-2*|oracle| for bf16
-# outputs).  Accumulation is fp32; in the tensor-core kernel the softmax weights P pass through f16
-# (relative step 2^-11 = 4.9e-4), which bounds the absolute error by ~5e-4 * sum_t p_t |V_t|.
-ATOL_V, RTOL = 6e-4, 1e-2
+# Decode-attention tolerance, per output element e of head h:
+#     |out - oracle| <= C_P * sum_t p_t |V_t,e|  +  C_OUT * |oracle|
+# The first term is the element's own error scale (softmax weights applied to |V|, from the oracle): an
+# outlier channel (values x20) gets a 20x larger allowance than a normal channel, and no element borrows the
+# allowance of another.  C_P covers the relative error of the softmax weights: q and P pass through f16
+# (2^-11) or three e4m3 terms (2^-12) in the tensor-core kernels, and the score error of a d=128 dot
+# product with outlier channels reaches ~1e-2 before the exponential.  The CUDA-core kernel computes in
+# fp32 on the dequantized values.  C_OUT is the rounding of the stored output (bf16: 2^-9).
+C_P_TC, C_P_SIMT = 2e-2, 2e-4
+C_OUT = {"fp32": 1e-5, "bf16": 4e-3}
+
+
+def attn_tol(ref, ref_abs, name, simt):
+    return (C_P_SIMT if simt else C_P_TC) * ref_abs + C_OUT[name] * np.abs(ref) + 1e-6
 
 
 def outlier_kv(rng, B, T, Hkv, d, dtype):
@@ -164,11 +174,11 @@ def test_decode_attention_against_oracle(cuda, fmt, name, H, Hkv, d, simt):
     o.append(k.float().numpy(), v.float().numpy(), new_lens=lens)
     assert np.array_equal(g.k_pool.cpu().numpy(), o.k_pool)
     q = torch.from_numpy(rng.standard_normal((B, H, d)).astype(np.float32)).to(DT[name])
-    ref = oatt.paged_decode_attention(o, q.float().numpy())
+    ref, ref_abs = oatt.paged_decode_attention(o, q.float().numpy(), with_abs=True)
     out = ops.paged_decode_attention(g, q.to(cuda), max_seq_len=144, simt=simt).float().cpu().numpy()
     assert np.all(out[4] == 0)
-    tol = ATOL_V * float(v.float().abs().max()) + RTOL * np.abs(ref) + (2e-2 * np.abs(ref) if name == "bf16" else 0)
-    assert np.all(np.abs(out - ref) <= tol), np.abs(out - ref).max()
+    tol = attn_tol(ref, ref_abs, name, simt)
+    assert np.all(np.abs(out - ref) <= tol), (np.abs(out - ref) / tol).max()
 
 
 @pytest.mark.parametrize("fmt", FMTS)
@@ -187,12 +197,12 @@ def test_decode_attention_config3_shape(cuda, fmt):
     assert np.array_equal(g.k_pool.cpu().numpy(), o.k_pool)
     assert np.array_equal(g.v_pool.cpu().numpy(), o.v_pool)
     q = torch.from_numpy(rng.standard_normal((B, H, d)).astype(np.float32)).bfloat16()
-    ref = oatt.paged_decode_attention(o, q.float().numpy())
+    ref, ref_abs = oatt.paged_decode_attention(o, q.float().numpy(), with_abs=True)
     out = ops.paged_decode_attention(g, q.to(cuda), max_seq_len=L).float().cpu().numpy()
     out_simt = ops.paged_decode_attention(g, q.to(cuda), max_seq_len=L, simt=True).float().cpu().numpy()
-    tol = ATOL_V * float(v.float().abs().max()) + (RTOL + 2e-2) * np.abs(ref)
-    assert np.all(np.abs(out - ref) <= tol), np.abs(out - ref).max()
-    assert np.all(np.abs(out_simt - ref) <= tol)
+    tol, tol_simt = attn_tol(ref, ref_abs, "bf16", False), attn_tol(ref, ref_abs, "bf16", True)
+    assert np.all(np.abs(out - ref) <= tol), (np.abs(out - ref) / tol).max()
+    assert np.all(np.abs(out_simt - ref) <= tol_simt), (np.abs(out_simt - ref) / tol_simt).max()
 
 
 @pytest.mark.parametrize("fmt", FMTS)
@@ -255,6 +265,14 @@ def test_argument_errors(cuda):
     small = torch.empty(16, dtype=torch.uint8, device=cuda)
     with pytest.raises(Tsb200Error):
         ops.paged_decode_attention(g, torch.zeros((2, 4, 64), device=cuda), max_seq_len=32, ws=small)
+    # max_seq_len beyond what the block table covers (2 pages = 32 tokens): refused, nothing is launched
+    with pytest.raises(Tsb200Error) as ei:
+        ops.paged_decode_attention(g, torch.zeros((2, 4, 64), device=cuda), max_seq_len=33)
+    assert ei.value.status == -1
+    empty = ops.PagedKV("int8", 4, 2, 64, g.block_table, g.seq_lens, cuda)
+    empty.num_pages = 0                                         # a descriptor with no pages is refused too
+    with pytest.raises(Tsb200Error):
+        ops.paged_decode_attention(empty, torch.zeros((2, 4, 64), device=cuda), max_seq_len=32)
 
 
 @pytest.mark.parametrize("name", ["fp32", "bf16"])

@@ -36,9 +36,10 @@ def rel(a, b):
 @pytest.mark.parametrize("family", ["qwen2", "llama"])
 def test_fp32_dense_kv_logits_and_greedy_tokens(cuda, family):
     """Config-1 style run (fp32, dense fp32 KV): prompt logits within 1e-3 max-rel-err of the
-    reference and the greedy continuation identical token for token."""
+    reference and the greedy continuation identical token for token over 32 new tokens."""
     g, dec = build(family, cuda, "fp32")
-    toks, logits = dec.generate(g["ids"], max_new_tokens=8)
+    assert g["tokens"].shape[1] == g["ids"].shape[1] + 32
+    toks, logits = dec.generate(g["ids"], max_new_tokens=32)
     assert rel(logits.cpu(), g["logits"][:, -1]) < 1e-3
     assert torch.equal(toks.cpu(), g["tokens"])
 
@@ -47,7 +48,7 @@ def test_fp32_dense_kv_logits_and_greedy_tokens(cuda, family):
 def test_unquantized_weights_path(cuda, family):
     """The stored factors used as dense fp32 matrices (no repacking) give the same result."""
     g, dec = build(family, cuda, "fp32", quantized=False)
-    toks, logits = dec.generate(g["ids"], max_new_tokens=8)
+    toks, logits = dec.generate(g["ids"], max_new_tokens=32)
     assert rel(logits.cpu(), g["logits"][:, -1]) < 1e-3
     assert torch.equal(toks.cpu(), g["tokens"])
 
@@ -58,12 +59,38 @@ def test_quantized_kv_logits_close(cuda, family, kv, tol):
     """Quantized KV changes the numbers (the reference has no such cache): logits stay within a
     format-dependent max-rel-err of the dense-cache reference."""
     g, dec = build(family, cuda, kv)
-    if kv == "fp8":
-        for c in dec.kv:
-            c.k_scale.fill_(16.0 / 448)
-            c.v_scale.fill_(4.0 / 448)
-    _, logits = dec.generate(g["ids"], max_new_tokens=1)
+    _, logits = dec.generate(g["ids"], max_new_tokens=1)     # FP8: one-pass prefill, scales = amax / 448 over the prompt
     assert rel(logits.cpu(), g["logits"][:, -1]) < tol
+    if kv == "fp8":
+        assert all(c.fp8_scales_set for c in dec.kv)
+        assert all(float(c.k_scale.min()) > 0 and float(c.k_scale.max()) < 1.0 for c in dec.kv)
+
+
+def test_fp8_stepwise_prompt_needs_scales(cuda):
+    """The token-by-token prompt loop cannot take amax over the prompt: it is refused while the FP8 scales are
+    the constructor's placeholders, and runs once they have been set."""
+    g, dec = build("llama", cuda, "fp8")
+    with pytest.raises(ValueError):
+        dec.generate(g["ids"], max_new_tokens=1, batched_prefill=False)
+    for c in dec.kv:
+        c.fill_fp8_scales(16.0 / 448, 4.0 / 448)
+    _, logits = dec.generate(g["ids"], max_new_tokens=1, batched_prefill=False)
+    assert rel(logits.cpu(), g["logits"][:, -1]) < 6e-2
+
+
+def test_status_word_raises_on_the_host(cuda):
+    """A non-zero status word (what a kernel leaves behind when a bounded wait ran out) makes the engine raise
+    at its next check; the check clears it.  Nothing is made to time out on the device."""
+    from transformer_surgeon_b200 import ops, Tsb200Error
+    g, dec = build("llama", cuda, "int8")
+    dec.check_status()
+    dec.attn_ws[ops.ATTN_STATUS_OFFSET:ops.ATTN_STATUS_OFFSET + 4].view(torch.int32).fill_(8)
+    with pytest.raises(Tsb200Error):
+        dec.check_status()
+    dec.check_status()
+    dec.lin_ws[:4].view(torch.int32).fill_(2)
+    with pytest.raises(Tsb200Error):
+        dec.generate(g["ids"], max_new_tokens=1)
 
 
 @pytest.mark.parametrize("family", ["qwen2", "llama"])

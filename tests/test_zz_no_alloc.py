@@ -30,7 +30,8 @@ def _setup(cuda, fmt, seed, B=4, H=8, Hkv=2, d=128, L=300):
         kv.set_fp8_scales(k, v)
     kv.append(k, v)
     seq += L
-    seq[1] = L - 37                      # ragged lengths
+    if B > 1:
+        seq[1] = L - 37                  # ragged lengths
     q = torch.randn((B, H, d), generator=g, device=cuda).bfloat16()
     return ops, kv, q, L
 
@@ -47,10 +48,18 @@ def _static_call(ops, kv, q, L):
     return st, out
 
 
+# Shapes chosen so that BOTH kernels split their sequences (only then do the partials and the split counters in
+# the array come into play): the int8 kernel splits 4 ways at 4 sequences x 2 kv heads x 300 tokens, the FP8
+# kernel needs at least 24 pages per split and few (sequence, head) pairs: 1 x 2 x 1200 tokens -> 3 splits.
+SHAPES = {"int8": dict(B=4, L=300), "fp8": dict(B=1, L=1200)}
+
+
 @pytest.mark.parametrize("fmt", ["fp8", "int8"])
 def test_static_scratch_matches_workspace_entry_point_twice(cuda, fmt):
     for seed in (1, 2):                  # second call: the array still holds the first call's partials
-        ops, kv, q, L = _setup(cuda, fmt, seed)
+        ops, kv, q, L = _setup(cuda, fmt, seed, **SHAPES[fmt])
+        if seed == 2:
+            kv.seq_lens[0] = L - 37      # another ragged length on the second round
         st, out = _static_call(ops, kv, q, L)
         assert st == 0
         ref = ops.paged_decode_attention(kv, q, max_seq_len=L)

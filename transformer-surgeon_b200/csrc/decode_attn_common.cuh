@@ -2,7 +2,6 @@
 // (m, l, acc) workspace layout and the cross-split reduction.
 #pragma once
 #include "common.cuh"
-#include <cstdlib>
 
 namespace tsb {
 
@@ -10,14 +9,14 @@ namespace tsb {
 // head chunk), used by the tensor-core kernel to let the last split merge the partials), then
 // float [B][H][S][2 + d]  ->  m, l, acc[d] per (sequence, q head, split).
 constexpr size_t kAttnCounterBytes = 16384;
+// The last int32 of the counter block is a status word: a kernel that gave up on a bounded wait for its own
+// copies records a non-zero code there (the result of that call is then not to be trusted).
+constexpr int kAttnStatusIndex = (int)(kAttnCounterBytes / sizeof(int)) - 1;
 struct AttnSplit {
   int splits;
 };
 
 inline int choose_splits(int64_t B, int hkv, int64_t max_seq_len) {
-#ifdef TSB_TUNE
-  if (const char* e = getenv("TSB_ATTN_SPLITS")) return atoi(e);
-#endif
   const int64_t base = B * hkv;
   const int64_t pages = (max_seq_len + 15) / 16;
   int64_t s = (148 * 8 + base - 1) / (base > 0 ? base : 1);
@@ -33,9 +32,6 @@ inline int choose_splits(int64_t B, int hkv, int64_t max_seq_len) {
 // are split so that the grid fills the slots without spilling into a second wave, each split keeping at least
 // 24 pages (two page pairs per warp) to amortise the per-CTA query expansion and merge.
 inline int choose_splits_fp8(int64_t B, int hkv, int64_t max_seq_len) {
-#ifdef TSB_TUNE
-  if (const char* e = getenv("TSB_ATTN_SPLITS")) return atoi(e);
-#endif
   const int64_t base = B * hkv;
   const int64_t pages = (max_seq_len + 15) / 16;
   int64_t s = base > 0 ? 296 / base : 1;

@@ -160,7 +160,7 @@ decode_attn_fp8_kernel(tsb200_kv_desc kv, const T* __restrict__ q, int64_t qs, i
     for (int j = 0; j < 2; ++j) oacc[i][j][0] = oacc[i][j][1] = oacc[i][j][2] = oacc[i][j][3] = 0.f;
   float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
 
-  // this warp's pages: pb + w, pb + w + 4, ...; consecutive two form a pair (one ring stage)
+  // this warp's pages: pb + w, pb + w + kWarps, ...; consecutive two form a pair (one ring stage)
   const int n_pages = (pe - pb - w + kWarps - 1) / kWarps > 0 ? (pe - pb - w + kWarps - 1) / kWarps : 0;
   const int n_pairs = (n_pages + 1) / 2;
   const int64_t rec_stride = (int64_t)kv.hkv * REC;
@@ -401,7 +401,7 @@ decode_attn_fp8_kernel(tsb200_kv_desc kv, const T* __restrict__ q, int64_t qs, i
 // uses the f16 tensor-core kernel).  `counters` may be null: partials only, a reducer launch follows.
 template <typename T>
 int launch_attn_fp8(const tsb200_kv_desc& kv, const void* q, int64_t qs, int H, float sm_scale, int64_t max_seq_len, int S,
-                    int64_t B, float* ws, int* counters, void* out, cudaStream_t st) {
+                    int64_t B, float* ws, int* counters, void* out, int* status, cudaStream_t st) {
   constexpr size_t pipe = (size_t)kWarps * WARP_SMEM + 4 * D * 4 + 64;   // rings + expanded q
   constexpr size_t merge = (size_t)(kWarps * 16 + kWarps * 8 * D) * sizeof(float);
   constexpr size_t smem = pipe > merge ? pipe : merge;
@@ -415,12 +415,12 @@ int launch_attn_fp8(const tsb200_kv_desc& kv, const void* q, int64_t qs, int H, 
   }
   dim3 grid((unsigned)(B * kv.hkv), (unsigned)S, 1);
   TSB_CUDA(launch_kernel(decode_attn_fp8_kernel<T>, grid, dim3(kWarps * 32), smem, st, kv, (const T*)q, qs, H, sm_scale, max_seq_len,
-                         S, ws, counters, (T*)out, (int*)nullptr));
+                         S, ws, counters, (T*)out, status));
   return TSB200_OK;
 }
 template int launch_attn_fp8<float>(const tsb200_kv_desc&, const void*, int64_t, int, float, int64_t, int, int64_t, float*, int*,
-                                    void*, cudaStream_t);
+                                    void*, int*, cudaStream_t);
 template int launch_attn_fp8<__nv_bfloat16>(const tsb200_kv_desc&, const void*, int64_t, int, float, int64_t, int, int64_t, float*,
-                                            int*, void*, cudaStream_t);
+                                            int*, void*, int*, cudaStream_t);
 
 }  // namespace tsb

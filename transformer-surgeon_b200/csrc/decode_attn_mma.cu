@@ -1,7 +1,7 @@
 // Split-K paged decode attention on tensor cores (int8, FP8-e4m3 and NVFP4 pages).
 //
 // Replaces transformersurgeon/blocks/mha.py:9-103 (attention(): GQA, softmax, @V) for the
-// decode step.  One CTA = one (sequence, kv head, split); its 4 warps take pages
+// decode step.  One CTA = one (sequence, kv head, split); its warps (4, or 6 for int8 pages) take pages
 // round-robin.  Each warp streams its pages through a private ring of shared-memory
 // stages with 16-byte cp.async copies (K record placed with an XOR swizzle so the
 // fragment reads are bank-conflict free), and computes, per 16-token page,
@@ -21,9 +21,9 @@ namespace tsb {
 template <typename T, int D> int launch_reduce(const float* ws, int64_t BH, int S, void* out, cudaStream_t st);
 template <typename T>
 int launch_attn_fp8(const tsb200_kv_desc& kv, const void* q, int64_t qs, int H, float sm_scale, int64_t max_seq_len, int S,
-                    int64_t B, float* ws, int* counters, void* out, cudaStream_t st);
+                    int64_t B, float* ws, int* counters, void* out, int* status, cudaStream_t st);
 int validate_attn_args(const tsb200_kv_desc* kv, const void* q, void* out, int dtype, int64_t B, int H,
-                       int64_t max_seq_len, void* workspace, size_t workspace_bytes, bool& noop);
+                       int64_t max_seq_len, void* workspace, size_t workspace_bytes, bool& noop, size_t need_bytes);
 
 namespace {
 
@@ -422,12 +422,19 @@ int launch_mma(const tsb200_kv_desc& kv, const void* q, int64_t qs, int H, float
 
 using namespace tsb;
 
-extern "C" int tsb200_paged_decode_attn(const tsb200_kv_desc* kv, const void* q, void* out, int dtype, int64_t q_batch_stride, int64_t B, int H,
-                                        float sm_scale, int64_t max_seq_len, void* workspace, size_t workspace_bytes,
-                                        void* stream) {
+// Bytes the dispatch below really uses for a problem: counters + partials of the split count it will pick
+// (tsb200_paged_decode_attn_workspace_bytes is the hkv-independent upper bound of this).
+static size_t attn_exact_workspace_bytes(const tsb200_kv_desc* kv, int64_t B, int H, int64_t max_seq_len) {
+  const int S = choose_splits(B, kv->hkv, max_seq_len);
+  return kAttnCounterBytes + (size_t)(B * H * S * (2 + kv->head_dim)) * sizeof(float);
+}
+
+static int decode_attn_dispatch(const tsb200_kv_desc* kv, const void* q, void* out, int dtype, int64_t q_batch_stride, int64_t B,
+                                int H, float sm_scale, int64_t max_seq_len, void* workspace, size_t workspace_bytes,
+                                size_t need_bytes, void* stream) {
   TSB_REQUIRE_DEVICE();
   bool noop;
-  int st = validate_attn_args(kv, q, out, dtype, B, H, max_seq_len, workspace, workspace_bytes, noop);
+  int st = validate_attn_args(kv, q, out, dtype, B, H, max_seq_len, workspace, workspace_bytes, noop, need_bytes);
   if (st != TSB200_OK || noop) return st;
   const int64_t qs = q_batch_stride ? q_batch_stride : (int64_t)H * kv->head_dim;
   if (qs < (int64_t)H * kv->head_dim) return TSB200_ERR_ARG;
@@ -439,14 +446,16 @@ extern "C" int tsb200_paged_decode_attn(const tsb200_kv_desc* kv, const void* q,
   float* ws = (float*)((char*)workspace + kAttnCounterBytes);
   const int D = kv->head_dim;
   const int64_t n_ctr = B * kv->hkv * ((H / kv->hkv + 7) / 8);
-  const bool fused = n_ctr * (int64_t)sizeof(int) <= (int64_t)kAttnCounterBytes;   // else: separate reduction launch
+  // the last int of the counter block is the status word of the bounded waits, so one counter fewer is usable
+  const bool fused = n_ctr < (int64_t)(kAttnCounterBytes / sizeof(int));           // else: separate reduction launch
+  int* status = counters + kAttnStatusIndex;
   int r;
   if (kv->format == TSB200_KV_FP8 && D == 128 && H / kv->hkv <= 4) {
     // e4m3 pages go to the tensor cores as FP8 (decode_attn_fp8.cu)
     int* ctr = fused ? counters : nullptr;
     const int S8 = choose_splits_fp8(B, kv->hkv, max_seq_len);   // never more than choose_splits(): the workspace fits
-    if (dtype == TSB200_F32) r = launch_attn_fp8<float>(*kv, q, qs, H, sm_scale, max_seq_len, S8, B, ws, ctr, out, s);
-    else r = launch_attn_fp8<__nv_bfloat16>(*kv, q, qs, H, sm_scale, max_seq_len, S8, B, ws, ctr, out, s);
+    if (dtype == TSB200_F32) r = launch_attn_fp8<float>(*kv, q, qs, H, sm_scale, max_seq_len, S8, B, ws, ctr, out, status, s);
+    else r = launch_attn_fp8<__nv_bfloat16>(*kv, q, qs, H, sm_scale, max_seq_len, S8, B, ws, ctr, out, status, s);
     if (r != TSB200_OK || fused) return r;
     return dtype == TSB200_F32 ? launch_reduce<float, 128>(ws, B * H, S8, out, s) : launch_reduce<__nv_bfloat16, 128>(ws, B * H, S8, out, s);
   }
@@ -469,6 +478,12 @@ extern "C" int tsb200_paged_decode_attn(const tsb200_kv_desc* kv, const void* q,
 #undef TSB_GO
 }
 
+extern "C" int tsb200_paged_decode_attn(const tsb200_kv_desc* kv, const void* q, void* out, int dtype, int64_t q_batch_stride, int64_t B, int H,
+                                        float sm_scale, int64_t max_seq_len, void* workspace, size_t workspace_bytes,
+                                        void* stream) {
+  return decode_attn_dispatch(kv, q, out, dtype, q_batch_stride, B, H, sm_scale, max_seq_len, workspace, workspace_bytes, 0, stream);
+}
+
 
 // ---------------------------------------------------------------------------------------------
 // Allocation-free variant.
@@ -484,7 +499,7 @@ extern "C" int tsb200_paged_decode_attn(const tsb200_kv_desc* kv, const void* q,
 // is current, and that pointer is what is passed to the launches.
 namespace tsb {
 namespace {
-constexpr size_t kStaticScratchBytes = 8u << 20;     // 8 MiB: e.g. batch 64 x 32 heads x 8 splits x (2 + 128) floats
+constexpr size_t kStaticScratchBytes = 8u << 20;     // 8 MiB: e.g. batch 32 x 32 heads x 15 splits x (2 + 128) floats
 static __device__ __align__(256) unsigned char g_attn_scratch[kStaticScratchBytes];
 
 int static_scratch_ptr(void** out) {
@@ -512,14 +527,20 @@ extern "C" int tsb200_paged_decode_attn_static(const tsb200_kv_desc* kv, const v
   TSB_REQUIRE_DEVICE();
   if (!kv || B < 0 || H <= 0) return TSB200_ERR_ARG;
   if (B == 0) return TSB200_OK;
-  const size_t need = tsb200_paged_decode_attn_workspace_bytes(B, H, kv->head_dim, max_seq_len);
-  if (need == 0) return TSB200_ERR_ARG;
+  if (validate_kv(kv, true) != TSB200_OK || max_seq_len < 0) return TSB200_ERR_ARG;
+  // sized by the split count this problem will really use, not by the hkv-independent bound that sizes a
+  // caller's workspace: more problems fit the fixed array
+  const size_t need = attn_exact_workspace_bytes(kv, B, H, max_seq_len);
   if (need > kStaticScratchBytes) return TSB200_ERR_WORKSPACE;   // problem too large for the built-in scratch
   void* scratch = nullptr;
   const int st = static_scratch_ptr(&scratch);
   if (st != TSB200_OK) return st;
-  // Nothing in the scratch has to start at zero: every (sequence, head, split) record that the
-  // reducer reads is written by the split kernel of the same call.
-  return tsb200_paged_decode_attn(kv, q, out, dtype, q_batch_stride, B, H, sm_scale, max_seq_len, scratch, kStaticScratchBytes,
-                                  stream);
+  // The head of the array (split counters + status word) MUST be zero when the kernels start.  A finished call
+  // leaves it zero, but a call that overlapped another one on the GPU, or was cut short, can leave a counter
+  // stuck, after which the fused merge of that (sequence, head) would never fire again.  The caller cannot
+  // reach the array, so every call clears the head itself, on its stream, ahead of its kernels.  The partials
+  // behind the head need no clearing: each record the merge reads is written by the same call.
+  TSB_CUDA(cudaMemsetAsync(scratch, 0, kAttnCounterBytes, as_stream(stream)));
+  return decode_attn_dispatch(kv, q, out, dtype, q_batch_stride, B, H, sm_scale, max_seq_len, scratch, kStaticScratchBytes, need,
+                              stream);
 }

@@ -122,16 +122,20 @@ template int launch_reduce<__nv_bfloat16, 64>(const float*, int64_t, int, void*,
 template int launch_reduce<__nv_bfloat16, 128>(const float*, int64_t, int, void*, cudaStream_t);
 
 int validate_attn_args(const tsb200_kv_desc* kv, const void* q, void* out, int dtype, int64_t B, int H,
-                       int64_t max_seq_len, void* workspace, size_t workspace_bytes, bool& noop) {
+                       int64_t max_seq_len, void* workspace, size_t workspace_bytes, bool& noop, size_t need_bytes) {
   noop = false;
   int st = validate_kv(kv, true);
   if (st != TSB200_OK) return st;
   if (B < 0 || H <= 0 || max_seq_len < 0) return TSB200_ERR_ARG;
   if (H % kv->hkv) return TSB200_ERR_ARG;
+  // the kernels walk block_table[b][0 .. ceil(min(seq_lens[b], max_seq_len) / 16)) and clamp page ids into
+  // [0, num_pages): both bounds must lie inside what the caller handed over
+  if (kv->num_pages <= 0 || max_seq_len > kv->bt_stride * 16) return TSB200_ERR_ARG;
   if (dtype != TSB200_F32 && dtype != TSB200_BF16) return TSB200_ERR_UNSUPPORTED;
   if (B == 0) { noop = true; return TSB200_OK; }
   if (!q || !out || !workspace || !aligned(workspace, 16)) return TSB200_ERR_ARG;
-  if (workspace_bytes < tsb200_paged_decode_attn_workspace_bytes(B, H, kv->head_dim, max_seq_len)) return TSB200_ERR_WORKSPACE;
+  if (need_bytes == 0) need_bytes = tsb200_paged_decode_attn_workspace_bytes(B, H, kv->head_dim, max_seq_len);
+  if (workspace_bytes < need_bytes) return TSB200_ERR_WORKSPACE;
   if (B * kv->hkv > 0x7fffffffLL) return TSB200_ERR_UNSUPPORTED;
   return TSB200_OK;
 }
@@ -156,7 +160,7 @@ int tsb200_paged_decode_attn_simt(const tsb200_kv_desc* kv, const void* q, void*
                                   void* stream) {
   TSB_REQUIRE_DEVICE();
   bool noop;
-  int st = validate_attn_args(kv, q, out, dtype, B, H, max_seq_len, workspace, workspace_bytes, noop);
+  int st = validate_attn_args(kv, q, out, dtype, B, H, max_seq_len, workspace, workspace_bytes, noop, 0);
   if (st != TSB200_OK || noop) return st;
   const int64_t qs = q_batch_stride ? q_batch_stride : (int64_t)H * kv->head_dim;
   if (qs < (int64_t)H * kv->head_dim) return TSB200_ERR_ARG;

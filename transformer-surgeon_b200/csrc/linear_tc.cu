@@ -1,22 +1,15 @@
-// LinearCompressed.forward on the 5th-generation tensor cores (tcgen05 / TMEM / TMA).
+// tcgen05 GEMM for LinearCompressed with DENSE bf16 factors (e.g. an unquantized lm_head):
+//   Y[M, N] = X[M, K] . W[N, K]^T + bias[N]
+// restating transformersurgeon/blocks/linear_compressed.py:96-100.  Packed (quantized) factors are served by
+// the persistent kernel in linear_tcq.cu; this file also holds the dispatch between the two (linear_tc()).
 //
-// Replaces transformersurgeon/blocks/linear_compressed.py:96-100 for bf16 activations:
-//   Y[M, N] = (X[M, K] . Wq[N, K]^T) * scale[N] + bias[N]
-// called once for the V factor (N = rank, result rounded to bf16 = the rank-r intermediate)
-// and once for the U factor.  The GEMM is issued "swapped": the weight tile is the MMA A
-// operand (M_mma = 128 weight rows), the activations are the B operand (N_mma = token tile),
-// so decode batches of 16..128 tokens still fill the 128-row datapath, and the per-row
-// dequantization scale and bias are per-TMEM-lane constants in the epilogue.
-//
-// Warp roles (6 warps):
-//   warp 0      TMA producer: activation tile (TN x 64 bf16, 128-byte swizzle) and the packed
-//               weight tile (128 rows x 64 codes, raw bytes) per k-block into a 4-stage ring
-//   warp 1      TMEM allocation; one lane issues tcgen05.mma (4 x K=16 per k-block) and
-//               tcgen05.commit to release stages / publish the accumulator
-//   warps 2..5  dequantize: raw codes -> bf16 (exact integers) written in the 128-byte-swizzled
-//               K-major layout the MMA descriptor expects; afterwards the epilogue:
-//               tcgen05.ld the fp32 accumulator (one TMEM lane = one weight row per thread),
-//               scale, bias, store (or fp32 atomics into a split-K buffer)
+// One CTA = one (128-row weight tile, token tile, K split).  Warp roles (6 warps):
+//   warp 0      TMA producer: activation tile (TN x 64 bf16) and weight tile (128 x 64 bf16), both with the
+//               128-byte swizzle, per k-block into a 4-stage ring
+//   warp 1      TMEM allocation; one lane issues tcgen05.mma (4 x K=16 per k-block, both operands from shared
+//               memory) and tcgen05.commit to release stages / publish the accumulator
+//   warps 2..5  epilogue: tcgen05.ld the fp32 accumulator (one TMEM lane = one weight row per thread), bias,
+//               store - or fp32 atomics into the split-K buffer, which a small kernel then rounds to bf16
 // Every mbarrier wait is bounded; on expiry the kernel records a code in the status word
 // (first 4 bytes of the workspace), drains and frees TMEM, and returns.
 #include "tc_common.cuh"
@@ -27,65 +20,6 @@ namespace {
 
 constexpr int NSTG = 4;
 constexpr int kThreads = 192;
-
-// ---------------------------------------------------------------- dequantization ---
-// One thread converts one weight row of the k-block: 64 codes -> 64 bf16.
-template <int BITS>
-__device__ __forceinline__ void dequant_row(const uint8_t* __restrict__ raw_row, uint8_t* a_tile, int r) {
-  if (BITS == 4) {
-    // word = 8 columns, field j -> column 2j, field j+4 -> column 2j+1.  (w ^ 0x88888888) biases every
-    // nibble by +8; 0x4300 | u is the bf16 128 + u; subtracting 136 leaves the signed code.
-    const uint4 q0 = *reinterpret_cast<const uint4*>(raw_row);
-    const uint4 q1 = *reinterpret_cast<const uint4*>(raw_row + 16);
-    const unsigned w[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
-#pragma unroll
-    for (int c = 0; c < 8; ++c) {
-      const unsigned t = w[c] ^ 0x88888888u;
-      uint4 o;
-      o.x = bf16x2_sub(((t)&0x000f000fu) | 0x43004300u, 0x43084308u);
-      o.y = bf16x2_sub(((t >> 4) & 0x000f000fu) | 0x43004300u, 0x43084308u);
-      o.z = bf16x2_sub(((t >> 8) & 0x000f000fu) | 0x43004300u, 0x43084308u);
-      o.w = bf16x2_sub(((t >> 12) & 0x000f000fu) | 0x43004300u, 0x43084308u);
-      store_chunk(a_tile, r, c, o);
-    }
-  } else if (BITS == 2) {
-    // word = 16 columns, field j -> column 2j, field j+8 -> column 2j+1; bias +2, subtract 130.
-    const uint4 q0 = *reinterpret_cast<const uint4*>(raw_row);
-    const unsigned w[4] = {q0.x, q0.y, q0.z, q0.w};
-#pragma unroll
-    for (int g = 0; g < 4; ++g) {
-      const unsigned t = w[g] ^ 0xAAAAAAAAu;
-#pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        uint4 o;
-        o.x = bf16x2_sub(((t >> (8 * h)) & 0x00030003u) | 0x43004300u, 0x43024302u);
-        o.y = bf16x2_sub(((t >> (8 * h + 2)) & 0x00030003u) | 0x43004300u, 0x43024302u);
-        o.z = bf16x2_sub(((t >> (8 * h + 4)) & 0x00030003u) | 0x43004300u, 0x43024302u);
-        o.w = bf16x2_sub(((t >> (8 * h + 6)) & 0x00030003u) | 0x43004300u, 0x43024302u);
-        store_chunk(a_tile, r, 2 * g + h, o);
-      }
-    }
-  } else {  // BITS == 8: natural byte order; int8 -> f32 by the 2^23 trick, then pack to bf16x2
-#pragma unroll
-    for (int c = 0; c < 8; ++c) {
-      const uint2 q = *reinterpret_cast<const uint2*>(raw_row + 8 * c);
-      const unsigned t0 = q.x ^ 0x80808080u, t1 = q.y ^ 0x80808080u;
-      float f[8];
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        f[i] = __uint_as_float(0x4B000000u | ((t0 >> (8 * i)) & 0xffu)) - 8388736.0f;       // 2^23 + 128
-        f[4 + i] = __uint_as_float(0x4B000000u | ((t1 >> (8 * i)) & 0xffu)) - 8388736.0f;
-      }
-      uint4 o;
-      __nv_bfloat162 p;
-      p = __floats2bfloat162_rn(f[0], f[1]); o.x = *reinterpret_cast<unsigned*>(&p);
-      p = __floats2bfloat162_rn(f[2], f[3]); o.y = *reinterpret_cast<unsigned*>(&p);
-      p = __floats2bfloat162_rn(f[4], f[5]); o.z = *reinterpret_cast<unsigned*>(&p);
-      p = __floats2bfloat162_rn(f[6], f[7]); o.w = *reinterpret_cast<unsigned*>(&p);
-      store_chunk(a_tile, r, c, o);
-    }
-  }
-}
 
 struct TcParams {
   int64_t M, N, K;
@@ -99,28 +33,25 @@ struct TcParams {
 };
 
 template <int TN> struct SmemLayout {
-  static constexpr int kA = BM * 128;            // 16 KB bf16 A tile
+  static constexpr int kA = BM * 128;            // 16 KB bf16 weight tile (the MMA's A operand)
   static constexpr int kX = TN * 128;            // activation tile
-  static constexpr int kRaw = BM * 64;           // raw codes (sized for 8-bit)
-  static constexpr int kStage = kA + kX + kRaw;
+  static constexpr int kStage = (kA + kX + 1023) / 1024 * 1024;
   static constexpr int kBytes = NSTG * kStage + 1024 /*alignment slack*/ + 256 /*barriers*/;
 };
 
-template <int TN, int BITS>
+template <int TN>
 __global__ void __launch_bounds__(kThreads, 1)
 linear_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, TcParams p) {
   using L = SmemLayout<TN>;
-  constexpr int RAW_ROW = BITS == 16 ? 0 : BK * BITS / 8;     // bytes of one weight row per k-block
-  constexpr unsigned TX_BYTES = (unsigned)(TN * 128 + (BITS == 16 ? BM * 128 : BM * RAW_ROW));
+  constexpr unsigned TX_BYTES = (unsigned)(TN * 128 + BM * 128);
   constexpr unsigned TMEM_COLS = TN < 32 ? 32 : TN;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   unsigned long long* bars = reinterpret_cast<unsigned long long*>(smem + NSTG * L::kStage);
   unsigned long long* full_bar = bars;                 // TMA landed            [NSTG]
-  unsigned long long* ready_bar = bars + NSTG;         // A tile dequantized    [NSTG]
-  unsigned long long* empty_bar = bars + 2 * NSTG;     // MMA done with stage   [NSTG]
-  unsigned long long* acc_bar = bars + 3 * NSTG;       // accumulator complete  [1]
-  unsigned* tmem_slot = reinterpret_cast<unsigned*>(bars + 3 * NSTG + 1);
+  unsigned long long* empty_bar = bars + NSTG;         // MMA done with stage   [NSTG]
+  unsigned long long* acc_bar = bars + 2 * NSTG;       // accumulator complete  [1]
+  unsigned* tmem_slot = reinterpret_cast<unsigned*>(bars + 2 * NSTG + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -132,7 +63,6 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
   if (threadIdx.x == 0) {
     for (int i = 0; i < NSTG; ++i) {
       mbar_init(&full_bar[i], 1);
-      mbar_init(&ready_bar[i], 4);                     // one arrival per dequant warp
       mbar_init(&empty_bar[i], 1);
     }
     mbar_init(acc_bar, 1);
@@ -157,8 +87,7 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
         mbar_expect_tx(&full_bar[s], TX_BYTES);
         const int kcol = (kb0 + i) * BK;
         tma_load_2d(st + L::kA, &map_x, kcol, m0, &full_bar[s]);
-        if (BITS == 16) tma_load_2d(st, &map_w, kcol, n0, &full_bar[s]);
-        else tma_load_2d(st + L::kA + L::kX, &map_w, kcol * BITS / 8, n0, &full_bar[s]);
+        tma_load_2d(st, &map_w, kcol, n0, &full_bar[s]);
       }
     }
   } else if (warp == 1) {
@@ -169,7 +98,7 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
       for (int i = 0; i < nkb && ok; ++i) {
         const int s = i % NSTG;
         const unsigned ph = (i / NSTG) & 1;
-        ok = mbar_wait(&full_bar[s], ph, abort_flag, 2) && mbar_wait(&ready_bar[s], ph, abort_flag, 3);
+        ok = mbar_wait(&full_bar[s], ph, abort_flag, 2);
         if (!ok) break;
         tc_fence_after();
         uint8_t* st = smem + s * L::kStage;
@@ -183,22 +112,8 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
       if (ok) umma_commit(acc_bar);
     }
   } else {
-    // ------------------------------------------------------------ dequant + epilogue
-    const int t = threadIdx.x - 64;                    // 0..127 = weight row inside the tile
+    // ------------------------------------------------------------ epilogue
     bool ok = true;
-    for (int i = 0; i < nkb && ok; ++i) {
-      const int s = i % NSTG;
-      const unsigned ph = (i / NSTG) & 1;
-      ok = mbar_wait(&full_bar[s], ph, abort_flag, 4);
-      if (!ok) break;
-      if (BITS != 16) {
-        uint8_t* st = smem + s * L::kStage;
-        dequant_row<BITS == 16 ? 8 : BITS>(st + L::kA + L::kX + t * RAW_ROW, st, t);
-        fence_async_proxy();                           // generic-proxy writes -> visible to the MMA (async proxy)
-      }
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&ready_bar[s]);
-    }
     // epilogue: TMEM lane quarter of this warp is (warp % 4)
     if (ok && nkb > 0) ok = mbar_wait(acc_bar, 0, abort_flag, 5);
     if (ok && nkb > 0) {
@@ -249,7 +164,7 @@ __global__ void splitk_finalize_kernel(float* __restrict__ partial, __nv_bfloat1
 }
 
 // ---------------------------------------------------------------- host side --------
-template <int TN, int BITS>
+template <int TN>
 int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, const TcParams& p, dim3 grid, cudaStream_t s) {
   using L = SmemLayout<TN>;
   static bool configured[64] = {false};
@@ -257,39 +172,22 @@ int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, const TcParams& p, d
   TSB_CUDA(cudaGetDevice(&dev));
   if (dev < 0 || dev >= 64) return TSB200_ERR_DEVICE;
   if (!configured[dev]) {
-    TSB_CUDA(cudaFuncSetAttribute(linear_tc_kernel<TN, BITS>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kBytes));
+    TSB_CUDA(cudaFuncSetAttribute(linear_tc_kernel<TN>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kBytes));
     configured[dev] = true;
   }
-  TSB_CUDA(launch_kernel(linear_tc_kernel<TN, BITS>, grid, dim3(kThreads), (size_t)L::kBytes, s, mw, mx, p));
+  TSB_CUDA(launch_kernel(linear_tc_kernel<TN>, grid, dim3(kThreads), (size_t)L::kBytes, s, mw, mx, p));
   return TSB200_OK;
 }
 
-template <int TN>
-int launch_tc_bits(int bits, const CUtensorMap& mw, const CUtensorMap& mx, const TcParams& p, dim3 grid, cudaStream_t s) {
-  switch (bits) {
-    case 2: return launch_tc<TN, 2>(mw, mx, p, grid, s);
-    case 4: return launch_tc<TN, 4>(mw, mx, p, grid, s);
-    case 8: return launch_tc<TN, 8>(mw, mx, p, grid, s);
-    case 16: return launch_tc<TN, 16>(mw, mx, p, grid, s);
-    default: return TSB200_ERR_UNSUPPORTED;
-  }
-}
-
-// One quantized GEMM: y[M, N] = x[M, K] . W[N, K]^T * scale + bias (bf16 in/out).
+// One dense GEMM: y[M, N] = x[M, K] . W[N, K]^T + bias (bf16 in/out; bits must be 16).
 int gemm_tc(const void* W, int bits, const float* scale, const void* bias, const void* x, void* y, int64_t M, int64_t K,
             int64_t N, float* partial, int* status, cudaStream_t s) {
   const int tn = M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : 128));
+  if (bits != 16) return TSB200_ERR_UNSUPPORTED;
   CUtensorMap mw, mx;
-  if (bits == 16) {
-    if (!make_map(&mw, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, W, (uint64_t)K, (uint64_t)N, (uint64_t)K * 2, BK, BM,
-                  CU_TENSOR_MAP_SWIZZLE_128B))
-      return TSB200_ERR_CUDA;
-  } else {
-    const uint64_t rb = tsb200_packed_row_bytes(K, bits);
-    if (!make_map(&mw, CU_TENSOR_MAP_DATA_TYPE_UINT8, W, rb, (uint64_t)N, rb, (uint32_t)(BK * bits / 8), BM,
-                  CU_TENSOR_MAP_SWIZZLE_NONE))
-      return TSB200_ERR_CUDA;
-  }
+  if (!make_map(&mw, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, W, (uint64_t)K, (uint64_t)N, (uint64_t)K * 2, BK, BM,
+                CU_TENSOR_MAP_SWIZZLE_128B))
+    return TSB200_ERR_CUDA;
   if (!make_map(&mx, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, x, (uint64_t)K, (uint64_t)M, (uint64_t)K * 2, BK, (uint32_t)tn,
                 CU_TENSOR_MAP_SWIZZLE_128B))
     return TSB200_ERR_CUDA;
@@ -308,10 +206,10 @@ int gemm_tc(const void* W, int bits, const float* scale, const void* bias, const
   dim3 grid((unsigned)n_tiles, (unsigned)m_tiles, (unsigned)splits);
   int st;
   switch (tn) {
-    case 16: st = launch_tc_bits<16>(bits, mw, mx, p, grid, s); break;
-    case 32: st = launch_tc_bits<32>(bits, mw, mx, p, grid, s); break;
-    case 64: st = launch_tc_bits<64>(bits, mw, mx, p, grid, s); break;
-    default: st = launch_tc_bits<128>(bits, mw, mx, p, grid, s); break;
+    case 16: st = launch_tc<16>(mw, mx, p, grid, s); break;
+    case 32: st = launch_tc<32>(mw, mx, p, grid, s); break;
+    case 64: st = launch_tc<64>(mw, mx, p, grid, s); break;
+    default: st = launch_tc<128>(mw, mx, p, grid, s); break;
   }
   if (st != TSB200_OK) return st;
   if (splits > 1) {

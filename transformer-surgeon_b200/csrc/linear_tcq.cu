@@ -187,31 +187,6 @@ __device__ __forceinline__ bool warps_rendezvous(unsigned long long* bar, int& u
 }
 
 
-// Optional phase trace (compile with -DTSB_TRACE): CTA 0 stores clock64 stamps in the last 512 bytes
-// of the workspace header (split counters that far up are not in use at traced sizes).
-#ifdef TSB_TRACE
-__device__ long long g_trace[160 * 32 * 2];     // per CTA: 32 slots of {clock64, globaltimer}
-__device__ long long g_trace_fine[4 * 512];     // CTAs 0..3: 512 clock64 slots each (per-stage stamps)
-__device__ __forceinline__ void trace_stamp(int i) {
-  if (blockIdx.x < 160 && i < 32) {
-    unsigned long long gt;
-    asm volatile("mov.u64 %0, %globaltimer;\n" : "=l"(gt));
-    g_trace[(blockIdx.x * 32 + i) * 2] = clock64();
-    g_trace[(blockIdx.x * 32 + i) * 2 + 1] = (long long)gt;
-  }
-}
-__device__ __forceinline__ void trace_fine(int i) {
-  if (blockIdx.x < 4 && i >= 0 && i < 512) g_trace_fine[blockIdx.x * 512 + i] = clock64();
-}
-#define TSB_FINE(i) trace_fine(i)
-#define TSB_STAMP(i) do { if (blockIdx.x == 0) reinterpret_cast<long long*>(reinterpret_cast<char*>(prog.status) + kWsHeader - 512)[i] = clock64(); trace_stamp(i); } while (0)
-#else
-#define TSB_STAMP(i) do { } while (0)
-#define TSB_FINE(i) do { } while (0)
-#endif
-// per-phase stamps of CTA 0: slot 8 + 4 * phase + k
-#define TSB_STAMP_P(p, k) TSB_STAMP(8 + 4 * (p) + (k))
-
 constexpr int kMaxPhases = 4;
 
 struct SubGemm {                 // one packed weight matrix and its operands
@@ -296,7 +271,6 @@ linear_tcq_kernel(const __grid_constant__ Program prog) {
   __syncthreads();
   tc_fence_after();
   const unsigned tmem_base = *tmem_slot;
-  if (threadIdx.x == 0) TSB_STAMP(0);
 
   // Work enumeration, identical in every role.  Phase -> items (round-robin over CTAs) -> passes
   // (one per matrix the item touches: 2 for a gated item) -> stages of KBS k-blocks.
@@ -350,7 +324,6 @@ linear_tcq_kernel(const __grid_constant__ Program prog) {
         while (ok) {
           const bool end = item >= ph.items;
           if (!released && (npend == NR || end)) {
-            TSB_STAMP_P(p, 0);
             prefetch_maps(p + 1);
             if (p == 0) {
               pdl_wait();
@@ -358,7 +331,6 @@ linear_tcq_kernel(const __grid_constant__ Program prog) {
               ok = grid_wait(&prog.grid_bar[p - 1], (int)gridDim.x, abort_flag);
               asm volatile("fence.proxy.async;\n" ::: "memory");  // other CTAs' stores -> visible to the copy engine
             }
-            TSB_STAMP_P(p, 1);
             released = true;
             if (!ok) break;
           }
@@ -386,7 +358,6 @@ linear_tcq_kernel(const __grid_constant__ Program prog) {
             if (gs >= NR && !mbar_wait(&stage_done[s], ((gs / NR) - 1) & 1, abort_flag, 1)) { ok = false; break; }
             mbar_expect_tx(&w_full[s], (unsigned)L::kRaw);
             tma_load_2d(r_ring + s * L::kStage + L::kX, &sg.map_w, kb * (BK * BITS / 8), it.nt * BM, &w_full[s]);
-            if (gs == 0) TSB_STAMP(1);
             pend[npend].map = &sg.map_x; pend[npend].y = it.mt * TN; pend[npend].kb = kb; pend[npend].s = s;
             ++npend;
           }
@@ -424,7 +395,6 @@ linear_tcq_kernel(const __grid_constant__ Program prog) {
               const int s = gs % NR, buf = gs & 1;
               ok = mbar_wait(&x_full[s], (gs / NR) & 1, abort_flag, 2);
               if (!ok) break;
-              TSB_FINE(8 * gs + 0);
               tc_fence_after();
               const unsigned a_tmem = tmem_base + L::kACol0 + buf * 128;
               const unsigned x_base = smem_u32(r_ring + s * L::kStage);
@@ -439,7 +409,6 @@ linear_tcq_kernel(const __grid_constant__ Program prog) {
                 }
               }
               umma_commit(&stage_done[s]);                     // arrives once the stage's MMAs are complete
-              TSB_FINE(8 * gs + 1);
             }
           }
           if (ok) umma_commit(acc_full);
@@ -475,12 +444,9 @@ linear_tcq_kernel(const __grid_constant__ Program prog) {
             const int i = jj * KBS;
             const int s = gs % NR, buf = gs & 1;
             ok = mbar_wait_relaxed(&w_full[s], (gs / NR) & 1, abort_flag, 4);
-            if (threadIdx.x == 64) TSB_FINE(8 * gs + 2);
             // the A buffer is free once the MMAs of the stage two back are complete
             if (ok && gs >= 2) ok = mbar_wait_relaxed(&stage_done[(gs - 2) % NR], ((gs - 2) / NR) & 1, abort_flag, 5);
             if (!ok) break;
-            if (threadIdx.x == 64) TSB_FINE(8 * gs + 3);
-            if (gs == 0 && threadIdx.x == 64) TSB_STAMP(2);
             tc_fence_after();
             const unsigned raw = smem_u32(r_ring + s * L::kStage + L::kX);
             const int nsub = min(KBS, it.nkb - i);
@@ -489,20 +455,15 @@ linear_tcq_kernel(const __grid_constant__ Program prog) {
               dequant_row_regs<BITS, L::kRawStageRow>(raw, row, j, regs);
               tmem_st32(lane_addr + L::kACol0 + buf * 128 + j * 32, regs);
             }
-            if (threadIdx.x == 64) TSB_FINE(8 * gs + 4);
             tmem_st_wait();
-            if (threadIdx.x == 64) TSB_FINE(8 * gs + 5);
-            if (lane == 0 && gs < 8) { TSB_FINE(128 + 8 * gs + (warp - 2)); }
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&x_full[s]);
-            if (threadIdx.x == 64) { if (gs == 0) TSB_STAMP(3); if (item == blockIdx.x && ps == 0 && jj == 0) TSB_STAMP_P(p, 2); }
           }
         }
         if (!ok) break;
         ok = mbar_wait_relaxed(acc_full, it_count & 1, abort_flag, 6);
         if (!ok) break;
-        if (threadIdx.x == 64) TSB_STAMP(5);
         tc_fence_after();
         if (!waited) { pdl_wait(); waited = true; }          // outputs / scratch may still be in use upstream
         const int64_t m0 = (int64_t)it.mt * TN;
@@ -656,10 +617,8 @@ linear_tcq_kernel(const __grid_constant__ Program prog) {
           if (!(ok = warps_rendezvous(ep_bar, ep_uses, lane, abort_flag))) break;   // last_flag is reused by the next item
         }
         tc_fence_after();
-        if (threadIdx.x == 64) TSB_STAMP(6);
       }
       if (!ok) break;
-      if (threadIdx.x == 64) TSB_STAMP_P(p, 3);
       // ---- end of phase: publish this CTA's outputs, then signal the grid barrier ------------------
       if (p + 1 < prog.n_phases) {
         if (!waited) { pdl_wait(); waited = true; }
@@ -680,7 +639,6 @@ linear_tcq_kernel(const __grid_constant__ Program prog) {
     tmem_dealloc(tmem_base, kTmemCols);
   }
   if (threadIdx.x == 0) {
-    TSB_STAMP(7);
     if (*abort_flag) atomicMax(prog.status, *abort_flag);
     if (prog.n_phases > 1) {
       // the last CTA to leave resets the grid-barrier counters for the next launch
@@ -866,12 +824,3 @@ int gemm_tcq(const void* W, int bits, const float* scale, const void* bias, cons
 }
 
 }  // namespace tsb
-
-#ifdef TSB_TRACE
-extern "C" int tsb200_trace_read(void* host, size_t nbytes) {
-  return (int)cudaMemcpyFromSymbol(host, tsb::g_trace, nbytes < sizeof(tsb::g_trace) ? nbytes : sizeof(tsb::g_trace));
-}
-extern "C" int tsb200_trace_read_fine(void* host, size_t nbytes) {
-  return (int)cudaMemcpyFromSymbol(host, tsb::g_trace_fine, nbytes < sizeof(tsb::g_trace_fine) ? nbytes : sizeof(tsb::g_trace_fine));
-}
-#endif

@@ -75,7 +75,7 @@ def rope_tables(head_dim, theta, max_positions, device):
 
 
 class CompressedDecoder:
-    def __init__(self, cfg, embed, layers, final_norm, lm_head, batch, max_seq_len, device, tp_group=None):
+    def __init__(self, cfg, embed, layers, final_norm, lm_head, batch, max_seq_len, device, tp_group=None, own_caches=True):
         self.cfg, self.embed, self.layers, self.final_norm, self.lm_head = cfg, embed, layers, final_norm, lm_head
         self.B, self.max_seq_len, self.device = batch, max_seq_len, device
         self.tp_group = tp_group
@@ -91,8 +91,9 @@ class CompressedDecoder:
         self.block_table = torch.arange(num_pages, dtype=torch.int32, device=device).reshape(batch, self.pages_per_seq)
         self.seq_lens = torch.zeros(batch, dtype=torch.int32, device=device)    # tokens in cache (after this step's append)
         self.write_pos = torch.zeros(batch, dtype=torch.int32, device=device)   # position of the token being appended
+        # own_caches=False: the caller brings the caches (bind_caches) before the first step
         self.kv = [ops.PagedKV(c.kv_format, num_pages, self.Hkv_local, c.head_dim, self.block_table, self.seq_lens, device)
-                   for _ in range(c.num_layers)]
+                   for _ in range(c.num_layers)] if own_caches else []
         self.cos, self.sin = rope_tables(c.head_dim, c.rope_theta, c.max_positions, device)
         H, Hkv, d = self.H_local, self.Hkv_local, c.head_dim
         dt = c.dtype
@@ -243,6 +244,41 @@ class CompressedDecoder:
     def reset(self):
         self.seq_lens.zero_()
 
+    def bind_caches(self, kv, block_table, seq_lens):
+        """Run on caller-owned caches (the blocks-path contract: the caller owns the caches and threads them
+        through every call, blocks/mha.py:608-612).  `kv`: one ops.PagedKV per layer sharing `block_table`
+        [B, pages] and `seq_lens` [B].  A captured graph holds the old addresses and is dropped."""
+        c = self.cfg
+        if len(kv) != c.num_layers or block_table.shape[0] != self.B or seq_lens.shape[0] != self.B:
+            raise ValueError("caches do not match the engine (layers / batch)")
+        fmt = ops.KV_FORMATS[c.kv_format]
+        for x in kv:
+            if x.fmt != fmt or x.hkv != self.Hkv_local or x.head_dim != c.head_dim:
+                raise ValueError("cache format / geometry differs from the engine's")
+            if x.block_table is not block_table or x.seq_lens is not seq_lens:
+                raise ValueError("all layers must share one block table and one seq_lens tensor")
+        self.kv, self.block_table, self.seq_lens = list(kv), block_table, seq_lens
+        self.pages_per_seq = block_table.shape[1]
+        self.max_seq_len = min(self.max_seq_len, self.pages_per_seq * ops.PAGE)
+        self.graph = None
+
+    def check_status(self):
+        """Raise if any bounded device-side wait of the step's kernels ran out since the last check
+        (the kernels then return early and the results of that step are not to be trusted).  Synchronises;
+        generate() calls it once at the end, long-running callers every so many steps."""
+        words = {"linear": self.lin_ws[:4], "mlp": self.mlp_ws[:4], "attention": self.attn_ws[ops.ATTN_STATUS_OFFSET:ops.ATTN_STATUS_OFFSET + 4]}
+        bad = {k: int(v.view(torch.int32).item()) for k, v in words.items()}
+        if self.peer is not None:
+            bad["peer all-reduce"] = int(self.peer.status())
+        bad = {k: v for k, v in bad.items() if v}
+        if bad:
+            for v in words.values():
+                v.zero_()
+            if self.peer is not None:
+                self.peer.clear_status()
+            raise ops.Tsb200Error(ops._lib.ERR_TIMEOUT, "a bounded device-side wait ran out: " +
+                                  ", ".join(f"{k} status {v}" for k, v in bad.items()))
+
     @torch.no_grad()
     def prefill(self, input_ids):
         """Batched prompt pass (single GPU): all T prompt tokens of every sequence go through the packed
@@ -297,16 +333,26 @@ class CompressedDecoder:
         return self.logits
 
     @torch.no_grad()
-    def generate(self, input_ids, max_new_tokens, batched_prefill=False):
-        """Greedy decoding.  By default the prompt is fed one token at a time through the decode step (as
-        the reference's blocks path does, examples/04_cache_impl_export_interface.py:128-139);
-        `batched_prefill=True` runs `prefill()` instead."""
+    def generate(self, input_ids, max_new_tokens, batched_prefill=None):
+        """Greedy decoding.  The prompt is fed one token at a time through the decode step (as the
+        reference's blocks path does, examples/04_cache_impl_export_interface.py:128-139) or, with
+        `batched_prefill=True`, in one pass by `prefill()`.  Default: stepwise, except for FP8 pages, whose
+        per-sequence scales are DEFINED as amax / 448 over the prompt - only the one-pass prefill can take
+        them layer by layer, so it is the default there.  Stepwise FP8 is refused unless the scales were set
+        beforehand (PagedKV.fill_fp8_scales / set_fp8_scales)."""
         ids = input_ids.to(self.device)
         B, T = ids.shape
-        assert B == self.B
+        if B != self.B:
+            raise ValueError(f"engine was built for batch {self.B}, got {B}")
+        fp8 = self.cfg.kv_format == "fp8"
+        if batched_prefill is None:
+            batched_prefill = fp8 and self.cfg.tp_world == 1 and not all(kv.fp8_scales_set for kv in self.kv)
         if batched_prefill:
             self.prefill(ids)
         else:
+            if fp8 and not all(kv.fp8_scales_set for kv in self.kv):
+                raise ValueError("FP8 pages: the per-sequence scales are unset (placeholders 1.0); use "
+                                 "batched_prefill=True or set them with PagedKV.fill_fp8_scales")
             self.reset()
             for t in range(T):
                 self.step(ids[:, t])
@@ -316,4 +362,5 @@ class CompressedDecoder:
             nxt = self.next_tokens.clone()
             out.append(nxt[:, None])
             self.step(nxt)
+        self.check_status()
         return torch.cat(out, dim=1), prefill_logits

@@ -17,8 +17,8 @@ Usage (generate() itself is untouched):
     cache = PagedQuantCache(model.config, batch, max_len, kv_format="int8")
     model.generate(ids, past_key_values=cache, do_sample=False, ...)
 
-Limits: every sequence of the batch has the same length (no padding mask on the decode step);
-no beam reordering, cropping or sliding windows.
+Limits: every sequence of the batch has the same length (a padded batch is refused on its first decode
+step); no beam reordering, cropping or sliding windows.
 """
 import torch
 from transformers import AttentionInterface
@@ -29,14 +29,18 @@ from transformers.masking_utils import AttentionMaskInterface, sdpa_mask
 from . import ops
 
 ATTN_NAME = "tsb200_paged"
+# Hand-over from `PagedCacheLayer.update` to the attention function of the same decoder layer, which runs right
+# after it: keyed by layer index (the attention module carries `layer_idx`), taken out when used.
+_PENDING = {}
 
 
 class PagedCacheLayer(CacheLayerMixin):
     """One layer's paged pools.  Sequence b owns pages [b * P, (b + 1) * P) in logical order."""
 
-    def __init__(self, kv_format, batch, max_len, hkv, head_dim, device):
+    def __init__(self, kv_format, batch, max_len, hkv, head_dim, device, layer_idx=0):
         super().__init__()
-        self.kv_format, self.batch, self.max_len = kv_format, batch, int(max_len)
+        self.kv_format, self.batch, self.max_len, self.layer_idx = kv_format, batch, int(max_len), layer_idx
+        self.mask_checked = False
         pages = (self.max_len + 15) // 16
         self.block_table = torch.arange(batch * pages, dtype=torch.int32, device=device).reshape(batch, pages)
         self.seq_lens = torch.zeros(batch, dtype=torch.int32, device=device)
@@ -64,13 +68,12 @@ class PagedCacheLayer(CacheLayerMixin):
         self.seq_lens += T
         self.cumulative_length += T
         if T == 1:
-            key_states._tsb_layer = self        # the attention function reads the pages directly
+            _PENDING[self.layer_idx] = self     # the attention function reads the pages directly
             return key_states, value_states
+        _PENDING.pop(self.layer_idx, None)
         L = self.cumulative_length
         kd, vd = ops.kv_gather(self.kv, L, dtype=key_states.dtype)
-        kd, vd = kd.transpose(1, 2), vd.transpose(1, 2)
-        kd._tsb_layer = self
-        return kd, vd
+        return kd.transpose(1, 2), vd.transpose(1, 2)
 
     def get_mask_sizes(self, query_length):
         return self.cumulative_length + query_length, 0
@@ -84,6 +87,7 @@ class PagedCacheLayer(CacheLayerMixin):
     def reset(self):
         self.seq_lens.zero_()
         self.cumulative_length = 0
+        self.mask_checked = False
 
 
 class PagedQuantCache(Cache):
@@ -97,14 +101,20 @@ class PagedQuantCache(Cache):
         hkv = getattr(text, "num_key_value_heads", None) or text.num_attention_heads
         head_dim = getattr(text, "head_dim", None) or text.hidden_size // text.num_attention_heads
         device = torch.device(device)
-        layers = [PagedCacheLayer(kv_format, batch, max_len, hkv, head_dim, device) for _ in range(text.num_hidden_layers)]
+        layers = [PagedCacheLayer(kv_format, batch, max_len, hkv, head_dim, device, i) for i in range(text.num_hidden_layers)]
         super().__init__(layers=layers)
 
 
 def paged_attention_forward(module, query, key, value, attention_mask, dropout=0.0, scaling=None, **kwargs):
     """Attention function for `ALL_ATTENTION_FUNCTIONS`: query [B, H, T, d] -> ([B, T, H, d], None)."""
-    layer = getattr(key, "_tsb_layer", None)
+    layer = _PENDING.pop(getattr(module, "layer_idx", None), None)
     if layer is not None and query.shape[2] == 1 and key.shape[2] == 1:
+        if not layer.mask_checked:              # once per generate(): all sequences share one length counter
+            if attention_mask is not None and not bool((attention_mask != 0).all() if attention_mask.dtype != torch.bool
+                                                       else attention_mask.all()):
+                raise NotImplementedError("PagedQuantCache: padded batches are unsupported (every sequence of the batch "
+                                          "must have the same length); left-padding would be attended over")
+            layer.mask_checked = True
         q = query[:, :, 0, :].contiguous()
         out = ops.paged_decode_attention(layer.kv, q, max_seq_len=layer.max_len, sm_scale=scaling)
         return out[:, None], None

@@ -10,6 +10,9 @@ import torch
 from . import _lib
 from ._lib import F32, BF16, KV_INT8, KV_FP8, KV_NVFP4, KV_F32, KV_BF16, LinearDesc, KVDesc, check
 
+from ._lib import Tsb200Error  # noqa: F401  (re-exported)
+
+ATTN_STATUS_OFFSET = 16380      # byte offset of the status word inside an attention workspace (last int of the counter block)
 KV_FORMATS = {"int8": KV_INT8, "fp8": KV_FP8, "nvfp4": KV_NVFP4, "fp32": KV_F32, "bf16": KV_BF16}
 PAGE = 16
 
@@ -318,12 +321,24 @@ class PagedKV:
         self.block_table = block_table     # int32 [B, pages_per_seq] (shared between layers)
         self.seq_lens = seq_lens           # int32 [B]               (shared between layers)
         B = block_table.shape[0]
+        # FP8 pages: one scale per (sequence, head), amax / 448 over the prompt, frozen for decode.  Until
+        # they are set (set_fp8_scales / fill_fp8_scales / constructor arguments) the placeholders are 1.0,
+        # which saturates anything above 448 - generate() refuses to run on placeholders.
+        self.fp8_scales_set = self.fmt != KV_FP8 or (k_scale is not None and v_scale is not None)
         if self.fmt == KV_FP8:
             self.k_scale = k_scale if k_scale is not None else torch.ones((B, hkv), dtype=torch.float32, device=device)
             self.v_scale = v_scale if v_scale is not None else torch.ones((B, hkv), dtype=torch.float32, device=device)
         else:
             self.k_scale = self.v_scale = None
         self._desc = None
+
+    def fill_fp8_scales(self, k_scale, v_scale):
+        """Set the FP8 scales from known values (floats or tensors broadcastable to [B, hkv])."""
+        if self.k_scale is None:
+            raise ValueError("only FP8 pages carry per-sequence scales")
+        self.k_scale.copy_(torch.as_tensor(k_scale, dtype=torch.float32).expand_as(self.k_scale))
+        self.v_scale.copy_(torch.as_tensor(v_scale, dtype=torch.float32).expand_as(self.v_scale))
+        self.fp8_scales_set = True
 
     def desc(self, seq_lens=None):
         # rebuilt on every call: block_table / seq_lens tensors may have been swapped
@@ -341,6 +356,7 @@ class PagedKV:
         check(lib.tsb200_kv_fp8_scales(_p(_cuda(k, "k")), _p(_cuda(v, "v")), _dt(k), B, T, self.hkv, self.head_dim,
                                        _p(pos0), _p(cos), _p(sin), 0 if cos is None else cos.shape[0],
                                        _p(self.k_scale), _p(self.v_scale), _stream()), "tsb200_kv_fp8_scales")
+        self.fp8_scales_set = True
 
     def rope_append(self, q, k, v, rope, new_lens=None, seq_lens=None):
         """One launch: RoPE on q [B, T, H, d] in place, RoPE on k, quantize-and-append k, v."""

@@ -151,3 +151,6 @@ class PeerBuffers:
     def status(self):
         """0, or the code recorded when a peer did not show up within the bounded wait (synchronises)."""
         return int(self.state[2].item())
+
+    def clear_status(self):
+        self.state[2:3].zero_()
