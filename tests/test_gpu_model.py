@@ -167,10 +167,15 @@ def test_packed_state_round_trip(cuda, tmp_path):
         net.config = type("Cfg", (), {})()
         net.config.compression_config = {"0": {"quantization": {"precision": 4, "granularity": "per_channel", "eps": 1e-6}},
                                          "1": {"quantization": {"precision": 8, "granularity": "per_channel", "eps": 1e-6}}}
+        with torch.no_grad():       # what the reference's soft quantization leaves in the parameters: dequantized codes
+            for m, p in ((net[0], 4), (net[1], 8)):
+                for prm in ([m.weight] + ([m.linear_V.weight] if m.linear_V is not None else [])):
+                    prm.copy_(ops.Factor.quantize(prm.data.contiguous(), p, "per_channel").reconstruct(prm.dtype))
         return net
 
     net = build()
     assert surgeon.pack_model(net, cuda) == 2
+    assert net[0]._tsb200.u.bits == 4 and net[0]._tsb200.v.bits == 4 and net[1]._tsb200.u.bits == 8
     x = torch.randn(16, 128, device=cuda).bfloat16()
     y = net[1](net[0](x))
     torch.save(surgeon.packed_state_dict(net), tmp_path / "packed.pt")
@@ -186,6 +191,15 @@ def test_packed_state_round_trip(cuda, tmp_path):
     bad["0._tsb200.u.data"] = bad["0._tsb200.u.data"][:, :-4]
     with pytest.raises(ValueError):
         surgeon.load_packed_state_dict(build(), bad, cuda)
+
+
+def test_pack_keeps_dense_when_codes_would_change_the_weights(cuda):
+    """A layer whose config says 4-bit but whose stored floats are NOT 4-bit values (never quantized, or mixed back
+    by a sparsity mask) stays dense: packing must never make the model compute with other weights."""
+    from transformer_surgeon_b200 import surgeon
+    w = torch.randn(64, 128, device=cuda)
+    lin = surgeon.pack_linear(w, quant=(4, "per_channel", 1e-6), dtype=torch.float32, device=cuda)
+    assert lin.u.bits == 32 and torch.equal(lin.u.data, w)
 
 
 @pytest.mark.parametrize("family", ["qwen2", "llama"])

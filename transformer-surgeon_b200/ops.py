@@ -254,6 +254,8 @@ class PackedLinear:
 
     def __call__(self, x, out=None, ws=None):
         lib = _lib.load()
+        if x.is_cuda and not x.is_contiguous():
+            x = x.contiguous()          # LinearCompressed.forward takes any view (e.g. hidden_states[:, -1:, :])
         x = _cuda(x, "x")
         if x.dtype != self.act_dtype:
             raise TypeError(f"x is {x.dtype}, layer was packed for {self.act_dtype}")
