@@ -160,3 +160,35 @@ def test_gated_mlp_block(cuda, name, p, M, K, I, r, N):
     yc = down(ops.swiglu(gate(x.to(cuda)), up(x.to(cuda))))
     assert rel_err(y, yc) < (1e-2 if name == "bf16" else 1e-5)
     assert ops.PackedLinear.device_status(ws=ops.workspace(cuda, 1, "mlp")) == 0
+
+
+@pytest.mark.parametrize("p", [4, 8, 2, "binary"])
+@pytest.mark.parametrize("M,K,N,r", [(32, 4096, 4096, 0),        # o_proj
+                                     (32, 4096, 6144, 0),        # q|k|v
+                                     (7, 3584, 4608, 0),         # config-5 q|k|v
+                                     (16, 4096, 14336, 1024),    # low-rank pair
+                                     (32, 14336, 4096, 1024),    # down_proj: long K
+                                     (32, 1792, 200, 0),         # rows not a multiple of 16 / 8
+                                     (3, 896, 72, 64)])          # K tail, tiny N
+def test_few_tokens_at_model_widths(cuda, p, M, K, N, r):
+    """Packed linears at decode token counts and the widths of the benchmark models (split-K over many CTAs, odd
+    row counts, K tails): against the fp32 oracle on the dequantized factors (bf16: max-rel-err <= 1e-2); the
+    result must not change from run to run (fixed summation order)."""
+    from transformer_surgeon_b200 import ops
+    g = torch.Generator(device=cuda).manual_seed(31)
+    rnd = lambda a, b, s: (torch.randn((a, b), generator=g, device=cuda) * s).bfloat16()
+    if r:
+        fu, fv = ops.Factor.quantize(rnd(N, r, 0.05), p), ops.Factor.quantize(rnd(r, K, 0.05), p)
+    else:
+        fu, fv = ops.Factor.quantize(rnd(N, K, 0.05), p), None
+    bias = rnd(1, N, 0.1)[0].contiguous()
+    lin = ops.PackedLinear(fu, fv, bias, torch.bfloat16)
+    x = rnd(M, K, 1.0)
+    Ud = fu.reconstruct(torch.bfloat16).float()
+    h = x.float() @ fv.reconstruct(torch.bfloat16).float().T if r else x.float()
+    ref = h @ Ud.T + bias.float()
+    y = lin(x)
+    y2 = lin(x)
+    assert torch.equal(y, y2)
+    assert rel_err(y, ref) < 1e-2, rel_err(y, ref)
+    assert ops.PackedLinear.device_status(device=cuda) == 0

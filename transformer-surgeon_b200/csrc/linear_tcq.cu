@@ -4,13 +4,14 @@
 //
 // Decode-time GEMMs stream a few MB of packed weights per call, so the kernel is built around
 // keeping many weight bytes in flight per SM, paying the set-up cost once per SM, and
-// synchronising once per 16 KB of weights rather than once per k-block.  Warp roles (11 warps):
-//   * warp 0, one lane: PRODUCER.  grid = min(#work items, #SMs); a work item = (128-row weight
-//     tile, token tile, K split); the lane walks the CTA's items and keeps issuing TMA loads across
+// synchronising once per 16 KB of weights rather than once per k-block.  Warp roles (12 warps):
+//   * warps 0 and 11, one lane each: PRODUCERS.  grid = min(#work items, #SMs); a work item = (128-row
+//     weight tile, token tile, K split); each lane walks the CTA's items and keeps issuing TMA loads across
 //     item and phase boundaries into a ring of STAGES.  A stage = KBS consecutive k-blocks: one
-//     weight box of 128 rows x up to 128 bytes of codes (swizzled) + the activation tiles of those
-//     k-blocks (one 3-D box).  Weight boxes of a phase's first stages are requested before the
-//     phase's activations exist; the matching activation loads are noted and fired when they do;
+//     weight box of 128 rows x up to 128 bytes of codes (swizzled, warp 0) + the activation tiles of those
+//     k-blocks (one 3-D box, warp 11).  Issuing one copy costs its lane several hundred cycles, hence a
+//     lane per operand; the weight lane runs ahead of the grid barrier that the activation lane must
+//     respect (weights are constants), so a phase's first weight boxes land before its activations exist;
 //   * warps 2-9: DEQUANT, two groups of 4 sharing every stage (even / odd k-blocks).  A thread owns
 //     one weight row: it reads the row's codes from shared memory, widens them to bf16 pairs in
 //     registers (exact integers) and stores them with tcgen05.st straight into TENSOR MEMORY, where
@@ -40,8 +41,9 @@ using namespace tc;
 namespace {
 
 constexpr int kDqWarps = 8;                 // two groups of four
-constexpr int kThreadsQ = 64 + kDqWarps * 32 + 32;   // producer, MMA issuer 0, 8 dequant warps, MMA issuer 1
+constexpr int kThreadsQ = 64 + kDqWarps * 32 + 64;   // weight producer, MMA issuer 0, 8 dequant warps, MMA issuer 1, activation producer
 constexpr int kIssuer1Warp = 2 + kDqWarps;
+constexpr int kXWarp = 3 + kDqWarps;
 constexpr int kSmemBudget = 208 * 1024;
 constexpr unsigned kTmemCols = 512;
 
@@ -49,7 +51,12 @@ template <int TN, int BITS> struct QLayout {
   static constexpr int kKbsFull = 1024 / BITS / BK;        // k-blocks in a 128-byte row of codes
   // A buffer = KBS * 32 TMEM columns <= 128; the 256-token tile keeps one k-block (32 KB of activations) per stage
   static constexpr int kKbsCap = (TN <= 32 || TN == 128) ? 4 : (TN <= 128 ? 2 : 1);
-  static constexpr unsigned kACol0 = 256;                   // TMEM column of A buffer 0 (accumulators sit below); buffer 1 at +128
+  // A buffers of 128 TMEM columns above the accumulators.  Token tiles up to 32 need at most 4 x 32 accumulator
+  // columns (two chains, gate and up), which leaves room for THREE buffers: the dequant warps may then run two
+  // stages ahead of the MMAs instead of one, and the chain "dequantize -> MMAs -> buffer free" no longer sets the
+  // pace of the main loop.
+  static constexpr int NBUF = TN <= 32 ? 3 : 2;
+  static constexpr unsigned kACol0 = TN <= 32 ? 128 : 256;  // TMEM column of A buffer 0; buffer b at + 128 b
   static constexpr int KBS = kKbsFull < kKbsCap ? kKbsFull : kKbsCap;
   static constexpr int kRawRow = BK * BITS / 8;            // bytes of one weight row per k-block
   static constexpr int kRawStageRow = KBS * kRawRow;       // bytes of one weight row per stage (32/64/128)
@@ -227,7 +234,6 @@ __device__ __forceinline__ bool grid_wait(const int* ctr, int target, volatile i
     asm volatile("ld.acquire.gpu.global.s32 %0, [%1];\n" : "=r"(v) : "l"(ctr) : "memory");
     if (v >= target) return true;
     if ((i & 63u) == 63u && *abort_flag) return false;
-    __nanosleep(64);
   }
   *abort_flag = 9;
   return false;
@@ -291,83 +297,73 @@ linear_tcq_kernel(const __grid_constant__ Program prog) {
   };
 
   if (warp == 0) {
-    // ---------------------------------------------------------------- TMA producer
+    // ---------------------------------------------------------------- TMA producer: packed weights
+    // The codes are constants, so this lane never waits for another kernel or phase: it keeps the ring full
+    // across item and phase boundaries, limited only by free stages.  (One lane needs several hundred cycles to
+    // issue one copy; weights and activations therefore have a lane each, in different warps.)
     if (lane == 0) {
-      // descriptor prefetches cost ~130 cycles each on this lane: a phase's descriptors are requested
-      // right after the first weight boxes of the phase BEFORE it are in flight
-      auto prefetch_maps = [&](int p) {
-        if (p < prog.n_phases)
-          for (int j = 0; j < prog.ph[p].nsub; ++j) {
-            asm volatile("prefetch.tensormap [%0];\n" ::"l"(&prog.ph[p].sub[j].map_w) : "memory");
-            asm volatile("prefetch.tensormap [%0];\n" ::"l"(&prog.ph[p].sub[j].map_x) : "memory");
-          }
-      };
-      // The packed weights are constants: for the first NR stages of a phase their boxes are
-      // requested BEFORE the phase's activations exist (before the wait on the preceding kernel
-      // for phase 0, before the grid barrier for later phases) and the matching activation loads are
-      // only noted down; once the dependency is met they are fired from that list - a handful of
-      // instructions on the critical path.  The two kinds of data complete separate barriers, so the
-      // dequant warps already fill both A buffers of the next phase while the barrier is pending.
-      struct Pending { const CUtensorMap* map; int y, kb, s; };
-      Pending pend[NR];
       bool ok = true;
       int gs = 0;                                             // absolute stage counter
 #pragma unroll 1
       for (int p = 0; p < prog.n_phases && ok; ++p) {
         const Phase& ph = prog.ph[p];
+        for (int j = 0; j < ph.nsub; ++j) asm volatile("prefetch.tensormap [%0];\n" ::"l"(&ph.sub[j].map_w) : "memory");
         const int passes = ph.gated ? 2 : 1;
-        int npend = 0;
-        bool released = false;                                // activations of this phase may be read
-        int item = blockIdx.x, ps = 0, jj = 0;
-        Item it = decode(ph, item < ph.items ? item : 0);
 #pragma unroll 1
-        while (ok) {
-          const bool end = item >= ph.items;
-          if (!released && (npend == NR || end)) {
-            prefetch_maps(p + 1);
-            if (p == 0) {
-              pdl_wait();
-            } else {
-              ok = grid_wait(&prog.grid_bar[p - 1], (int)gridDim.x, abort_flag);
-              asm volatile("fence.proxy.async;\n" ::: "memory");  // other CTAs' stores -> visible to the copy engine
+        for (int item = blockIdx.x; item < ph.items && ok; item += gridDim.x) {
+          const Item it = decode(ph, item);
+#pragma unroll 1
+          for (int ps = 0; ps < passes && ok; ++ps) {
+            const SubGemm& sg = ph.sub[ph.gated ? ps : it.sub];
+#pragma unroll 1
+            for (int jj = 0; jj < it.ns; ++jj, ++gs) {
+              const int s = gs % NR, kb = it.kb0 + jj * KBS;
+              // the stage is free once its previous user's MMAs are complete
+              if (gs >= NR && !mbar_wait(&stage_done[s], ((gs / NR) - 1) & 1, abort_flag, 1)) { ok = false; break; }
+              mbar_expect_tx(&w_full[s], (unsigned)L::kRaw);
+              tma_load_2d(r_ring + s * L::kStage + L::kX, &sg.map_w, kb * (BK * BITS / 8), it.nt * BM, &w_full[s]);
             }
-            released = true;
-            if (!ok) break;
           }
-          if (released) {                                     // fire the noted activation loads
+        }
+      }
+    }
+  } else if (warp == kXWarp) {
+    // ---------------------------------------------------------------- TMA producer: activations
+    // Same stage sequence; a phase's activations exist once the preceding kernel (phase 0) or the previous phase
+    // (grid barrier) has produced them.
+    if (lane == 0) {
+      bool ok = true;
+      int gs = 0;
 #pragma unroll 1
-            for (int q = 0; q < npend; ++q) {
-              const int s = pend[q].s;
+      for (int p = 0; p < prog.n_phases && ok; ++p) {
+        const Phase& ph = prog.ph[p];
+        for (int j = 0; j < ph.nsub; ++j) asm volatile("prefetch.tensormap [%0];\n" ::"l"(&ph.sub[j].map_x) : "memory");
+        if (p == 0) {
+          pdl_wait();
+        } else {
+          ok = grid_wait(&prog.grid_bar[p - 1], (int)gridDim.x, abort_flag);
+          asm volatile("fence.proxy.async;\n" ::: "memory");  // other CTAs' stores -> visible to the copy engine
+        }
+        const int passes = ph.gated ? 2 : 1;
+#pragma unroll 1
+        for (int item = blockIdx.x; item < ph.items && ok; item += gridDim.x) {
+          const Item it = decode(ph, item);
+#pragma unroll 1
+          for (int ps = 0; ps < passes && ok; ++ps) {
+            const SubGemm& sg = ph.sub[ph.gated ? ps : it.sub];
+#pragma unroll 1
+            for (int jj = 0; jj < it.ns; ++jj, ++gs) {
+              const int s = gs % NR, kb = it.kb0 + jj * KBS;
+              if (gs >= NR && !mbar_wait(&stage_done[s], ((gs / NR) - 1) & 1, abort_flag, 1)) { ok = false; break; }
               uint8_t* st = r_ring + s * L::kStage;
               mbar_expect_tx(&x_full[s], (unsigned)L::kX);
               if (ph.x3d) {                                   // k-blocks beyond K are zero-filled by the copy engine
-                tma_load_3d(st, pend[q].map, 0, pend[q].y, pend[q].kb, &x_full[s]);
+                tma_load_3d(st, &sg.map_x, 0, it.mt * TN, kb, &x_full[s]);
               } else {
 #pragma unroll 1
                 for (int j = 0; j < KBS; ++j)                 // columns beyond K are zero-filled by the copy engine
-                  tma_load_2d(st + j * L::kXTile, pend[q].map, (pend[q].kb + j) * BK, pend[q].y, &x_full[s]);
+                  tma_load_2d(st + j * L::kXTile, &sg.map_x, (kb + j) * BK, it.mt * TN, &x_full[s]);
               }
-            }
-            npend = 0;
-          }
-          if (end) break;
-          {
-            const SubGemm& sg = ph.sub[ph.gated ? ps : it.sub];
-            const int s = gs % NR, kb = it.kb0 + jj * KBS;
-            // the stage is free once its previous user's MMAs are complete
-            if (gs >= NR && !mbar_wait(&stage_done[s], ((gs / NR) - 1) & 1, abort_flag, 1)) { ok = false; break; }
-            mbar_expect_tx(&w_full[s], (unsigned)L::kRaw);
-            tma_load_2d(r_ring + s * L::kStage + L::kX, &sg.map_w, kb * (BK * BITS / 8), it.nt * BM, &w_full[s]);
-            pend[npend].map = &sg.map_x; pend[npend].y = it.mt * TN; pend[npend].kb = kb; pend[npend].s = s;
-            ++npend;
-          }
-          ++gs;
-          if (++jj == it.ns) {
-            jj = 0;
-            if (++ps == passes) {
-              ps = 0;
-              item += gridDim.x;
-              if (item < ph.items) it = decode(ph, item);
             }
           }
         }
@@ -392,7 +388,7 @@ linear_tcq_kernel(const __grid_constant__ Program prog) {
             for (int jj = 0; jj < it.ns; ++jj, ++gs) {
               if (!L::kSplitStage && (two ? (gs & 1) != me : me != 0)) continue;     // the other lane's stage
               const int i = jj * KBS;
-              const int s = gs % NR, buf = gs & 1;
+              const int s = gs % NR, buf = gs % L::NBUF;
               ok = mbar_wait(&x_full[s], (gs / NR) & 1, abort_flag, 2);
               if (!ok) break;
               tc_fence_after();
@@ -442,10 +438,10 @@ linear_tcq_kernel(const __grid_constant__ Program prog) {
         for (int ps = 0; ps < passes && ok; ++ps) {
           for (int jj = 0; jj < it.ns; ++jj, ++gs) {
             const int i = jj * KBS;
-            const int s = gs % NR, buf = gs & 1;
+            const int s = gs % NR, buf = gs % L::NBUF;
             ok = mbar_wait_relaxed(&w_full[s], (gs / NR) & 1, abort_flag, 4);
-            // the A buffer is free once the MMAs of the stage two back are complete
-            if (ok && gs >= 2) ok = mbar_wait_relaxed(&stage_done[(gs - 2) % NR], ((gs - 2) / NR) & 1, abort_flag, 5);
+            // the A buffer is free once the MMAs of the stage NBUF back are complete
+            if (ok && gs >= L::NBUF) ok = mbar_wait_relaxed(&stage_done[(gs - L::NBUF) % NR], ((gs - L::NBUF) / NR) & 1, abort_flag, 5);
             if (!ok) break;
             tc_fence_after();
             const unsigned raw = smem_u32(r_ring + s * L::kStage + L::kX);
@@ -623,9 +619,13 @@ linear_tcq_kernel(const __grid_constant__ Program prog) {
       if (p + 1 < prog.n_phases) {
         if (!waited) { pdl_wait(); waited = true; }
         asm volatile("fence.proxy.async;\n" ::: "memory");    // generic stores -> visible to other CTAs' copy engines
-        __threadfence();
         if (!(ok = warps_rendezvous(ep_bar, ep_uses, lane, abort_flag))) break;
-        if (threadIdx.x == 64) atomicAdd(&prog.grid_bar[p], 1);
+        if (threadIdx.x == 64) {
+          // one device-scope fence by the signalling thread: the stores of the other epilogue threads are ordered
+          // before it by the rendezvous, and the fence is cumulative
+          __threadfence();
+          atomicAdd(&prog.grid_bar[p], 1);
+        }
       }
     }
   }
