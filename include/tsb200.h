@@ -228,6 +228,23 @@ int tsb200_rope_append(const tsb200_kv_desc* kv, void* q, int q_heads, int64_t q
 int tsb200_kv_gather(const tsb200_kv_desc* kv, void* k_out, void* v_out, int dtype, int64_t B, int64_t L,
                      void* stream);
 
+/* Prompt (prefill) attention.
+ * Replaces blocks/mha.py:9-103 (attention()) for T > 1 query tokens per sequence - what the reference's model
+ * classes hand to torch's scaled-dot-product attention while a prompt is processed - with causal masking: query i
+ * of a sequence sits at position L - T + i and attends over positions 0 .. L - T + i of the cache.
+ * Two steps.  tsb200_kv_gather_heads dequantizes the first L cached positions of every sequence into the layout
+ * the attention kernel's copy engine wants: k_out [B, hkv, L, d] and vt_out [B, hkv, d, Lp] (V TRANSPOSED: the
+ * tokens of one element are contiguous; Lp >= L is the row pitch, a multiple of 8; zeros beyond seq_lens[b] and in
+ * [L, Lp)), both bf16.  tsb200_prefill_attn then runs the attention on tcgen05 (bf16 in, fp32 accumulation, bf16
+ * out): q, out [B, T, H, d]; q_token_stride = elements between consecutive tokens of q (0 = H * d; a multiple of
+ * 8), so q may be a column slice of a fused projection output; out is dense.  head_dim 64 or 128.  status: device
+ * int32, set non-zero when a bounded wait ran out (may be NULL). */
+int tsb200_kv_gather_heads(const tsb200_kv_desc* kv, void* k_out, void* vt_out, int64_t B, int64_t L, int64_t Lp,
+                           void* stream);
+int tsb200_prefill_attn(const void* q, int64_t q_token_stride, const void* k, const void* vt, void* out, int64_t B,
+                        int64_t T, int64_t L, int64_t Lp, int H, int hkv, int head_dim, float sm_scale,
+                        int32_t* status, void* stream);
+
 /* Split-K paged decode attention: one query token per sequence.
  * Replaces blocks/mha.py:9-103 (attention(): GQA, softmax(q k^T / sqrt(d)) v) for the
  * decode step, reading the quantized pages directly.

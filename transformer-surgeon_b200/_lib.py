@@ -64,6 +64,8 @@ SIGNATURES = {
     "tsb200_kv_append": (_i32, [_KD, _vp, _vp, _i32, _i64, _i64, _i64, _i64, _vp, _vp, _vp, _i64, _vp]),
     "tsb200_kv_gather": (_i32, [_KD, _vp, _vp, _i32, _i64, _i64, _vp]),
     "tsb200_rope_append": (_i32, [_KD, _vp, _i32, _i64, _vp, _vp, _i32, _i64, _i64, _i64, _i64, _vp, _vp, _vp, _i64, _vp]),
+    "tsb200_kv_gather_heads": (_i32, [_KD, _vp, _vp, _i64, _i64, _i64, _vp]),
+    "tsb200_prefill_attn": (_i32, [_vp, _i64, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i32, _i32, _i32, _f32, _vp, _vp]),
     "tsb200_paged_decode_attn_workspace_bytes": (_sz, [_i64, _i32, _i32, _i64]),
     "tsb200_paged_decode_attn": (_i32, [_KD, _vp, _vp, _i32, _i64, _i64, _i32, _f32, _i64, _vp, _sz, _vp]),
     "tsb200_paged_decode_attn_simt": (_i32, [_KD, _vp, _vp, _i32, _i64, _i64, _i32, _f32, _i64, _vp, _sz, _vp]),

@@ -284,10 +284,10 @@ class CompressedDecoder:
         """Batched prompt pass (single GPU): all T prompt tokens of every sequence go through the packed
         linears at once (M = B * T rows), K and V are rotated, quantized and appended for the whole chunk
         (FP8: the per-sequence scales are taken over the prompt first, amax / 448, and then frozen), and the
-        causal attention of the chunk reads the DEQUANTIZED cache (`kv_gather`) through torch's
-        scaled-dot-product attention - a library kernel; a fused prefill attention is not built.  Leaves the
-        engine in the state the token-by-token prompt loop leaves it in: logits / next_tokens of the last
-        prompt token, seq_lens == T.  Starts from an empty cache."""
+        causal attention of the chunk reads the DEQUANTIZED cache: bf16 engines on the tcgen05 prefill kernel
+        (`tsb200_kv_gather_heads` + `tsb200_prefill_attn`), fp32 engines on the paged decode kernel with one
+        one-token "sequence" per query.  Leaves the engine in the state the token-by-token prompt loop leaves it
+        in: logits / next_tokens of the last prompt token, seq_lens == T.  Starts from an empty cache."""
         c = self.cfg
         if c.tp_world > 1:
             raise NotImplementedError("batched prefill is single-GPU; tensor-parallel engines feed the prompt stepwise")
@@ -316,11 +316,9 @@ class CompressedDecoder:
                 kv.set_fp8_scales(k4, v4, rope=rope, pos0=zeros)
             kv.rope_append(q4, k4, v4, rope, seq_lens=zeros)            # q4 rotated in place
             self.seq_lens.fill_(T)
-            kd, vd = ops.kv_gather(kv, T, dtype=c.dtype)                # what every attention read sees
-            att = torch.nn.functional.scaled_dot_product_attention(q4.transpose(1, 2), kd.transpose(1, 2), vd.transpose(1, 2),
-                                                                   is_causal=True, enable_gqa=True)
-            att = att.transpose(1, 2).reshape(B * T, H * d).contiguous()
-            delta = L.o(att)
+            # causal attention of the chunk over the DEQUANTIZED cache (what every attention read sees)
+            att = ops.prefill_attention(kv, q4, T, status=self.attn_ws[ops.ATTN_STATUS_OFFSET:ops.ATTN_STATUS_OFFSET + 4])
+            delta = L.o(att.view(B * T, H * d))
             xn = ops.add_rmsnorm(resid, delta, L.ln2, c.rms_eps, c.norm_variant)
             delta = L.mlp(xn)
         last = resid.view(B, T, -1)[:, -1].contiguous()

@@ -8,8 +8,9 @@ attention function selected by `config._attn_implementation`.  This module suppl
   * `PagedQuantCache` - a `transformers.Cache` whose layers quantize-and-append into the paged pools
     (`tsb200_kv_append`) instead of concatenating tensors;
   * the attention function registered as `"tsb200_paged"`: one query token per sequence goes to the
-    paged decode kernel (`tsb200_paged_decode_attn`); a prompt (T > 1) attends over the cache's
-    DEQUANTIZED contents (`tsb200_kv_gather`) with torch's scaled-dot-product attention.
+    paged decode kernel (`tsb200_paged_decode_attn`); a prompt chunk (T > 1) attends causally over the
+    cache's DEQUANTIZED contents with the prefill kernel (`tsb200_kv_gather_heads` + `tsb200_prefill_attn`
+    on tcgen05 for bf16 models; fp32 models go through the paged decode kernel, one query token at a time).
 
 Usage (generate() itself is untouched):
 
@@ -17,13 +18,12 @@ Usage (generate() itself is untouched):
     cache = PagedQuantCache(model.config, batch, max_len, kv_format="int8")
     model.generate(ids, past_key_values=cache, do_sample=False, ...)
 
-Limits: every sequence of the batch has the same length (a padded batch is refused on its first decode
-step); no beam reordering, cropping or sliding windows.
+Limits: every sequence of the batch has the same length and the mask is the plain causal one (a padded
+batch is refused when first met); no beam reordering, cropping or sliding windows.
 """
 import torch
 from transformers import AttentionInterface
 from transformers.cache_utils import Cache, CacheLayerMixin
-from transformers.integrations.sdpa_attention import sdpa_attention_forward
 from transformers.masking_utils import AttentionMaskInterface, sdpa_mask
 
 from . import ops
@@ -53,8 +53,8 @@ class PagedCacheLayer(CacheLayerMixin):
         pass                                    # pools are allocated up front
 
     def update(self, key_states, value_states, *args, **kwargs):
-        """key_states, value_states [B, hkv, T, d] (keys after RoPE).  Appends; returns what the
-        attention function needs: the dense dequantized cache for T > 1, the tagged inputs for T = 1."""
+        """key_states, value_states [B, hkv, T, d] (keys after RoPE).  Quantizes and appends, and hands this
+        layer over to the attention function of the same decoder layer; the returned tensors are the inputs."""
         B, hkv, T, d = key_states.shape
         if B != self.batch:
             raise ValueError(f"cache was built for batch {self.batch}, got {B}")
@@ -67,13 +67,8 @@ class PagedCacheLayer(CacheLayerMixin):
         self.kv.append(k, v)
         self.seq_lens += T
         self.cumulative_length += T
-        if T == 1:
-            _PENDING[self.layer_idx] = self     # the attention function reads the pages directly
-            return key_states, value_states
-        _PENDING.pop(self.layer_idx, None)
-        L = self.cumulative_length
-        kd, vd = ops.kv_gather(self.kv, L, dtype=key_states.dtype)
-        return kd.transpose(1, 2), vd.transpose(1, 2)
+        _PENDING[self.layer_idx] = self         # the attention function reads the pages, not these tensors
+        return key_states, value_states
 
     def get_mask_sizes(self, query_length):
         return self.cumulative_length + query_length, 0
@@ -105,21 +100,35 @@ class PagedQuantCache(Cache):
         super().__init__(layers=layers)
 
 
+def _check_plain_causal(layer, attention_mask, T, L):
+    """Once per generate(): the kernels implement the plain causal mask over equal-length sequences."""
+    if layer.mask_checked:
+        return
+    if attention_mask is not None:
+        m = attention_mask if attention_mask.dtype == torch.bool else (attention_mask == 0)
+        m = m[..., -T:, :L]
+        q = torch.arange(L - T, L, device=m.device)[:, None]
+        k = torch.arange(L, device=m.device)[None, :]
+        if not bool((m == (k <= q)).all()):
+            raise NotImplementedError("PagedQuantCache: only the plain causal mask over equal-length sequences is "
+                                      "supported (a padded batch would attend over its padding)")
+    layer.mask_checked = True
+
+
 def paged_attention_forward(module, query, key, value, attention_mask, dropout=0.0, scaling=None, **kwargs):
     """Attention function for `ALL_ATTENTION_FUNCTIONS`: query [B, H, T, d] -> ([B, T, H, d], None)."""
     layer = _PENDING.pop(getattr(module, "layer_idx", None), None)
-    if layer is not None and query.shape[2] == 1 and key.shape[2] == 1:
-        if not layer.mask_checked:              # once per generate(): all sequences share one length counter
-            if attention_mask is not None and not bool((attention_mask != 0).all() if attention_mask.dtype != torch.bool
-                                                       else attention_mask.all()):
-                raise NotImplementedError("PagedQuantCache: padded batches are unsupported (every sequence of the batch "
-                                          "must have the same length); left-padding would be attended over")
-            layer.mask_checked = True
+    if layer is None:
+        raise RuntimeError(f'attention "{ATTN_NAME}" needs past_key_values=PagedQuantCache(...) (the cache layer of this '
+                           "decoder layer did not announce itself)")
+    T, L = query.shape[2], layer.cumulative_length
+    _check_plain_causal(layer, attention_mask, T, L)
+    if T == 1:
         q = query[:, :, 0, :].contiguous()
         out = ops.paged_decode_attention(layer.kv, q, max_seq_len=layer.max_len, sm_scale=scaling)
         return out[:, None], None
-    kwargs.pop("is_causal", None)
-    return sdpa_attention_forward(module, query, key, value, attention_mask, dropout=dropout, scaling=scaling, **kwargs)
+    out = ops.prefill_attention(layer.kv, query.transpose(1, 2).contiguous(), L, sm_scale=scaling)
+    return out, None
 
 
 AttentionInterface.register(ATTN_NAME, paged_attention_forward)

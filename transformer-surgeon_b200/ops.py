@@ -397,6 +397,44 @@ def kv_gather(kv, L, dtype=torch.bfloat16, seq_lens=None):
     return k, v
 
 
+def prefill_attention(kv, q, L, sm_scale=None, out=None, status=None, seq_lens=None):
+    """Causal attention of a prompt chunk: q [B, T, H, d] (heads dense, tokens evenly strided; bf16) over the first
+    L >= T positions of the cache `kv` (query i at position L - T + i), reading the dequantized cache
+    (blocks/mha.py:9-103 for T > 1).  bf16: head-major gather + tcgen05 kernel.  fp32: every query token becomes a
+    one-token "sequence" of the paged decode kernel (block-table rows repeated, lengths L - T + i + 1), which reads
+    the pages directly in fp32 math.  Returns out [B, T, H, d]."""
+    lib = _lib.load()
+    B, T, H, d = q.shape
+    if sm_scale is None:
+        sm_scale = d ** -0.5
+    if out is None:
+        out = torch.empty((B, T, H, d), dtype=q.dtype, device=q.device)
+    if q.dtype == torch.float32:
+        lens = (torch.arange(L - T + 1, L + 1, dtype=torch.int32, device=q.device)).repeat(B)          # [B * T]
+        base = kv.seq_lens if seq_lens is None else seq_lens
+        lens = torch.minimum(lens, base.repeat_interleave(T))
+        view = PagedKV.__new__(PagedKV)
+        view.__dict__.update(kv.__dict__)
+        view.block_table = kv.block_table.repeat_interleave(T, dim=0).contiguous()
+        view.seq_lens = lens
+        if kv.k_scale is not None:
+            view.k_scale, view.v_scale = kv.k_scale.repeat_interleave(T, dim=0).contiguous(), kv.v_scale.repeat_interleave(T, dim=0).contiguous()
+        qq = q.reshape(B * T, H, d) if q.is_contiguous() else q.contiguous().reshape(B * T, H, d)
+        paged_decode_attention(view, qq, max(int(L), 1), sm_scale=sm_scale, out=out.view(B * T, H, d))
+        return out
+    if q.dtype != torch.bfloat16:
+        raise TypeError("prefill attention takes bf16 (tcgen05) or fp32 (paged kernel) activations")
+    qs = _token_strided(q, "q")
+    Lp = (L + 63) // 64 * 64
+    kd = torch.empty((B, kv.hkv, L, d), dtype=torch.bfloat16, device=q.device)
+    vt = torch.empty((B, kv.hkv, d, Lp), dtype=torch.bfloat16, device=q.device)
+    desc = kv.desc(seq_lens)
+    check(lib.tsb200_kv_gather_heads(C.byref(desc), _p(kd), _p(vt), B, L, Lp, _stream()), "tsb200_kv_gather_heads")
+    check(lib.tsb200_prefill_attn(_p(q), qs, _p(kd), _p(vt), _p(out), B, T, L, Lp, H, kv.hkv, d, float(sm_scale), _p(status),
+                                  _stream()), "tsb200_prefill_attn")
+    return out
+
+
 def decode_attn_workspace_bytes(B, H, head_dim, max_seq_len):
     return int(_lib.load().tsb200_paged_decode_attn_workspace_bytes(B, H, head_dim, max_seq_len))
 
