@@ -166,16 +166,19 @@ def test_packed_state_round_trip(cuda, tmp_path):
         net = torch.nn.Sequential(LinearCompressed(128, 256, rank=64), LinearCompressed(256, 128, bias=False)).to(cuda).bfloat16()
         net.config = type("Cfg", (), {})()
         net.config.compression_config = {"0": {"quantization": {"precision": 4, "granularity": "per_channel", "eps": 1e-6}},
-                                         "1": {"quantization": {"precision": 8, "granularity": "per_channel", "eps": 1e-6}}}
-        with torch.no_grad():       # what the reference's soft quantization leaves in the parameters: dequantized codes
-            for m, p in ((net[0], 4), (net[1], 8)):
+                                         "1": {"quantization": {"precision": 2, "granularity": "per_channel", "eps": 1e-6}}}
+        # what the reference's soft quantization leaves in the parameters: dequantized codes.  (4- and 2-bit codes
+        # can be re-derived from bf16-stored values; 8-bit codes times a bf16 scale do not survive the rounding to
+        # bf16, so without codes captured at apply time such a layer stays dense - see the test below.)
+        with torch.no_grad():
+            for m, p in ((net[0], 4), (net[1], 2)):
                 for prm in ([m.weight] + ([m.linear_V.weight] if m.linear_V is not None else [])):
                     prm.copy_(ops.Factor.quantize(prm.data.contiguous(), p, "per_channel").reconstruct(prm.dtype))
         return net
 
     net = build()
     assert surgeon.pack_model(net, cuda) == 2
-    assert net[0]._tsb200.u.bits == 4 and net[0]._tsb200.v.bits == 4 and net[1]._tsb200.u.bits == 8
+    assert net[0]._tsb200.u.bits == 4 and net[0]._tsb200.v.bits == 4 and net[1]._tsb200.u.bits == 2
     x = torch.randn(16, 128, device=cuda).bfloat16()
     y = net[1](net[0](x))
     torch.save(surgeon.packed_state_dict(net), tmp_path / "packed.pt")
@@ -200,6 +203,15 @@ def test_pack_keeps_dense_when_codes_would_change_the_weights(cuda):
     w = torch.randn(64, 128, device=cuda)
     lin = surgeon.pack_linear(w, quant=(4, "per_channel", 1e-6), dtype=torch.float32, device=cuda)
     assert lin.u.bits == 32 and torch.equal(lin.u.data, w)
+    # 8-bit codes of a bf16 parameter: the stored RN_bf16(q * scale) does not give q back, so re-derivation is refused
+    # (dense), while the codes captured at apply time reconstruct the stored weights and are kept
+    from transformer_surgeon_b200 import ops
+    wb = (torch.randn(64, 128, device=cuda) * 0.02).bfloat16()
+    f = ops.Factor.quantize(wb, 8, "per_channel")
+    stored = f.reconstruct(torch.bfloat16)
+    assert surgeon.pack_linear(stored, quant=(8, "per_channel", 1e-6), dtype=torch.bfloat16, device=cuda).u.bits == 16
+    kept = surgeon.pack_linear(stored, quant=(8, "per_channel", 1e-6), dtype=torch.bfloat16, device=cuda, codes=(f.codes(), f.scales))
+    assert kept.u.bits == 8 and torch.equal(kept.u.reconstruct(torch.bfloat16), stored)
 
 
 @pytest.mark.parametrize("family", ["qwen2", "llama"])

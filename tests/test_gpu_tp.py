@@ -77,12 +77,17 @@ def _tp_worker(rank, world, port, out_path):
         sd = _state_dict(g)
         ids = torch.randint(0, 128, (3, 10), generator=g)
         cc = {k[:-7]: {"quantization": {"precision": 8, "granularity": "per_channel"}} for k in sd if "proj.weight" in k}
+        from transformer_surgeon_b200 import ops
+        for k in list(sd):          # store what the reference's soft quantization stores: the dequantized 8-bit codes
+            if "proj." in k and k.endswith("weight"):
+                sd[k] = ops.Factor.quantize(sd[k].to(dev).contiguous(), 8, "per_channel").reconstruct(torch.float32).cpu()
         outs = {}
         for tp_world in (1, world):
             cfg = DecoderConfig(num_layers=2, hidden=256, num_heads=4, num_kv_heads=2, head_dim=64, intermediate=512,
                                 vocab=128, dtype=torch.float32, kv_format="int8", max_positions=64,
                                 tp_world=tp_world, tp_rank=rank if tp_world > 1 else 0)
             dec = surgeon.decoder_from_state_dict(sd, cfg, cc, batch=3, max_seq_len=32, device=dev)
+            assert dec.layers[0].o.u.bits == 8 and dec.layers[0].gate.v.bits == 8       # packed, not the dense fallback
             toks, logits = dec.generate(ids, max_new_tokens=4)
             outs[tp_world] = (toks.cpu(), logits.float().cpu())
         if rank == 0:
@@ -152,12 +157,16 @@ def _peer_worker(rank, world, port, out_path):
         g = torch.Generator().manual_seed(32)
         sd = _state_dict(g)
         ids = torch.randint(0, 128, (3, 10), generator=g)
-        cc = {k[:-7]: {"quantization": {"precision": 8, "granularity": "per_channel"}} for k in sd if "proj.weight" in k}
+        cc = {k[:-7]: {"quantization": {"precision": 4, "granularity": "per_channel"}} for k in sd if "proj.weight" in k}
+        for k in list(sd):          # what the reference's soft quantization stores in a bf16 model: dequantized 4-bit codes
+            if "proj." in k and k.endswith("weight"):
+                sd[k] = ops.Factor.quantize(sd[k].to(dev).bfloat16().contiguous(), 4, "per_channel").reconstruct(torch.bfloat16).cpu()
         outs = {}
         for mode in ("nccl", "peer"):
             cfg = DecoderConfig(num_layers=2, hidden=256, num_heads=4, num_kv_heads=2, head_dim=64, intermediate=512,
                                 vocab=128, dtype=torch.bfloat16, kv_format="int8", max_positions=64, tp_world=world, tp_rank=rank)
             dec = surgeon.decoder_from_state_dict(sd, cfg, cc, batch=3, max_seq_len=32, device=dev)
+            assert dec.layers[0].o.u.bits == 4 and dec.layers[0].gate.v.bits == 4       # packed, not the dense fallback
             if mode == "peer":
                 assert dec.enable_peer_allreduce()
             toks, logits = dec.generate(ids, max_new_tokens=4)
