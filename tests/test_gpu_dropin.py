@@ -204,3 +204,43 @@ def test_config1_full_size_32_greedy_tokens(cuda, reference):
     toks, logits = dec.generate(ids, max_new_tokens=32)
     assert rel(logits.cpu(), ref_logits) < 1e-3
     assert torch.equal(toks.cpu(), ref_tokens)
+
+
+def test_config5_style_qwen25vl_text_tower_mixed_precision(cuda, reference):
+    """BASELINE config 5 in miniature on the reference's own class: the language tower of a
+    `Qwen2_5_VLForConditionalGenerationCompress` (models/qwen2_5_vl_c/define_qwen2_5_vl_c.py:44-50) with
+    NON-HOMOGENEOUS compression - per-layer weight precision 8 / 2 / 4, per-layer MLP rank 25% / full / 50% - set
+    through the reference's manager, text-only token ids (the three mrope position rows coincide, so the rotary
+    embedding is the 1-D one).  The engine built from the live model packs each layer at its own precision, gives
+    the reference's logits and 32 greedy tokens with unquantized pages, and stays close with NVFP4 pages."""
+    T = reference
+    from transformer_surgeon_b200 import surgeon
+    torch.manual_seed(2)
+    text = dict(vocab_size=256, hidden_size=256, intermediate_size=512, num_hidden_layers=3, num_attention_heads=2,
+                num_key_value_heads=1, max_position_embeddings=128, tie_word_embeddings=False,
+                rope_scaling={"type": "mrope", "mrope_section": [16, 24, 24]})
+    vis = dict(depth=1, hidden_size=64, intermediate_size=128, num_heads=2, out_hidden_size=256, fullatt_block_indexes=[0])
+    model = T.Qwen2_5_VLForConditionalGenerationCompress(T.Qwen2_5_VLConfigCompress(text_config=text, vision_config=vis, vocab_size=256)).eval()
+    mgr = T.Qwen2_5_VLCompressionSchemesManager(model)
+    bits, ranks = [8, 2, 4], [128, "full", 256]
+    for i in range(3):
+        mgr.set("quantization", "precision", bits[i], criteria=[[i, "language_model", "mlp"], [i, "language_model", "self_attn"]])
+        mgr.set("quantization", "granularity", "per_channel", criteria=[[i, "language_model"]])
+        if ranks[i] != "full":
+            mgr.set("lrd", "rank", ranks[i], criteria=[[i, "language_model", "mlp"]])
+    with surgeon.capture_quantization(model):
+        mgr.apply(hard=False)
+    ids = torch.randint(0, 256, (2, 12), generator=torch.Generator().manual_seed(3))
+    with torch.no_grad():
+        ref_logits = model(input_ids=ids).logits[:, -1]
+        ref_tokens = greedy(model, ids, 32)
+    dec = surgeon.decoder_from_model(model, batch=2, max_seq_len=64, kv_format="fp32")
+    got = [(L.o.u.bits, L.gate.u.bits, L.gate.rank) for L in dec.layers]
+    assert got == [(8, 8, 128), (2, 2, 0), (4, 4, 256)], got
+    assert dec.layers[0].qkv is not None and dec.layers[0].qkv.bias is not None          # Qwen2 q/k/v carry biases
+    toks, logits = dec.generate(ids, max_new_tokens=32)
+    assert rel(logits.cpu(), ref_logits) < 1e-3
+    assert torch.equal(toks.cpu(), ref_tokens)
+    dec4 = surgeon.decoder_from_model(model, batch=2, options={"max_cache_len": 64, "cache_impl": "paged_nvfp4"})
+    _, logits4 = dec4.generate(ids, max_new_tokens=1)
+    assert rel(logits4.cpu(), ref_logits) < 2.5e-1
