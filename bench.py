@@ -72,6 +72,9 @@ def parse():
     ap.add_argument("--sweep-ctx", default="4096,16384,32768", help="contexts of the attention sweep")
     ap.add_argument("--sweep-batch", type=int, default=64)
     ap.add_argument("--no-sweeps", action="store_true", help="N = 1: leave the op-level `sweeps` records out of the line")
+    ap.add_argument("--config", default="c4", choices=["c4", "c5"],
+                    help="c4 (default, the headline): Llama-3-8B architecture; c5: Qwen2.5-VL-7B text tower with per-layer "
+                         "precisions / ranks and an NVFP4 cache (one GPU, decode steps only; BASELINE.json configs[4])")
     return ap.parse_args()
 
 
@@ -499,6 +502,100 @@ def run_ours(a):
         done.set()
 
 
+QWEN25VL_7B_TEXT = dict(num_layers=28, hidden=3584, num_heads=28, num_kv_heads=4, head_dim=128, intermediate=18944,
+                        vocab=152064, rope_theta=1e6, rms_eps=1e-6)
+
+
+def run_c5(a):
+    """BASELINE.json configs[4] on one GPU: Qwen2.5-VL-7B language-tower shapes, bf16, per-layer weight precision drawn
+    with seed 2 from {2, 4, 8} (first and last layer 8) and per-layer MLP rank from {25%, 50%, 100%} of hidden, q/k/v
+    biases, NVFP4 paged KV, batch 8, synthetic cache of `--context` tokens (default 32768), greedy decode steps."""
+    import random
+    import torch
+    from transformer_surgeon_b200 import ops
+    from transformer_surgeon_b200.decoder import CompressedDecoder, DecoderConfig, LayerWeights, fuse_rows
+    torch.cuda.set_device(0)
+    device = torch.device("cuda", 0)
+    c = dict(QWEN25VL_7B_TEXT)
+    nl = a.layers if a.layers != LLAMA3_8B["num_layers"] else c["num_layers"]
+    c["num_layers"] = nl
+    B = a.batch if a.batch != 32 else 8
+    context = a.context if a.context != 2048 else 32768
+    rnd_ = random.Random(2)
+    bits = [8 if i in (0, nl - 1) else rnd_.choice([2, 4, 8]) for i in range(nl)]
+    ranks = [rnd_.choice([c["hidden"] // 4, c["hidden"] // 2, 0]) for _ in range(nl)]
+    max_seq = context + a.steps + a.warmup + 16
+    cfg = DecoderConfig(dtype=torch.bfloat16, kv_format="nvfp4", max_positions=max_seq + 16, **c)
+    g = torch.Generator(device=device).manual_seed(2)
+    dt = torch.bfloat16
+    H, Hkv, d, hid, inter = cfg.num_heads, cfg.num_kv_heads, cfg.head_dim, cfg.hidden, cfg.intermediate
+    rnd = lambda rows, cols, std: (torch.randn((rows, cols), generator=g, device=device) * std).to(dt)
+    wbytes = 0
+    layers = []
+    for i in range(nl):
+        qf = lambda rows, cols, std: ops.Factor.quantize(rnd(rows, cols, std), bits[i], "per_channel")
+
+        def lin(out, inn):
+            r = ranks[i]
+            if r:
+                return ops.PackedLinear(qf(out, r, 0.02 * (inn / r) ** 0.5 / 4), qf(r, inn, 0.25 / inn ** 0.5 * 4), None, dt)
+            return ops.PackedLinear(qf(out, inn, 0.02), None, None, dt)
+        fq, fk, fv = qf(H * d, hid, 0.02), qf(Hkv * d, hid, 0.02), qf(Hkv * d, hid, 0.02)
+        bias = [(torch.randn(n, generator=g, device=device) * 0.1).to(dt) for n in (H * d, Hkv * d, Hkv * d)]
+        ones = torch.ones(hid, dtype=dt, device=device)
+        L = LayerWeights(ones, ones.clone(), ops.PackedLinear(qf(hid, H * d, 0.02), None, None, dt), lin(inter, hid), lin(inter, hid),
+                         lin(hid, inter), qkv=fuse_rows([fq, fk, fv], bias, dt))
+        layers.append(L)
+        for pl in (L.qkv, L.o, L.gate, L.up, L.down):
+            for f in (pl.u, pl.v):
+                if f is not None:
+                    wbytes += f.data.numel() + 4 * f.rows
+    embed = rnd(cfg.vocab, hid, 0.02)
+    lm_head = ops.PackedLinear(ops.Factor.dense(rnd(cfg.vocab, hid, 0.02)), None, None, dt)
+    dec = CompressedDecoder(cfg, embed, layers, torch.ones(hid, dtype=dt, device=device), lm_head, B, max_seq, device)
+    outl = torch.ones((Hkv, d), device=device)
+    for h in range(Hkv):
+        outl[h, torch.randperm(d, generator=g, device=device)[:4]] = 20.0
+    for kv in dec.kv:
+        dec.seq_lens.zero_()
+        for t0 in range(0, context, 2048):
+            n = min(2048, context - t0)
+            k = (torch.randn((B, n, Hkv, d), generator=g, device=device) * outl).to(dt)
+            v = (torch.randn((B, n, Hkv, d), generator=g, device=device) * outl).to(dt)
+            kv.append(k, v)
+            dec.seq_lens.add_(n)
+    torch.cuda.synchronize()
+    dec.capture()
+    tok_host = torch.randint(0, cfg.vocab, (B,), dtype=torch.int64).pin_memory()
+    out_host = torch.empty(B, dtype=torch.int64).pin_memory()
+    sampler = ClockSampler(0)
+    ms, ms_e2e, ctx0 = timed_steps(dec, a, tok_host, out_host, torch.cuda.synchronize, sampler)
+    q = torch.randn((B, H, d), device=device).to(dt)
+    o = torch.empty_like(q)
+    t_attn = _graph_time_us(lambda i: ops.paged_decode_attention(dec.kv[i], q, dec.max_seq_len, out=o, ws=dec.attn_ws), nl)
+    clocks = sampler.stop()
+    dec.check_status()
+    peak, which = peaks()
+    kv_bytes = B * ctx0 * 2 * Hkv * d * 0.5625
+    step_bytes = wbytes + cfg.vocab * hid * 2 + nl * kv_bytes
+    step_us = ms / a.steps * 1e3
+    line = {"metric": "decode tokens/s (Qwen2.5-VL-7B text tower, per-layer LRD + W2/4/8 + NVFP4-KV)", "value": B * a.steps / (ms * 1e-3),
+            "unit": "tokens/s", "n_gpus": 1, "steps": a.steps, "warmup": a.warmup, "ms_per_step": ms / a.steps, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": "qwen2.5-vl-7b text-tower decode: %d layers, weight bits per layer %s, MLP rank per layer %s (0 = full), "
+                                   "lm_head bf16, nvfp4 paged KV, batch %d, context %d->%d" % (nl, bits, ranks, B, ctx0, ctx0 + a.steps),
+                       "l2": "inputs larger than L2 (%.1f GB read per step)" % (step_bytes / 1e9), "cuda_graph": True},
+            "e2e": {"value": B * a.steps / (ms_e2e * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": B * 8, "d2h_bytes_per_step": B * 8},
+            "gpu_launches": dec.kernel_launches_per_step * a.steps, "clocks": clocks,
+            "roofline": {"kernel": "decode_attn_mma_kernel (NVFP4 pages, group of 7 query heads; split merge fused)", "bound": "hbm",
+                         "achieved": kv_bytes / t_attn / 1e3, "peak": peak, "unit": "GB/s", "frac": kv_bytes / t_attn / 1e3 / peak,
+                         "peak_source": which, "frac_nominal": kv_bytes / t_attn / 1e3 / HBM_NOMINAL_GBS, "traffic": None,
+                         "ms_per_launch": t_attn * 1e-3, "share_of_step": nl * t_attn / step_us,
+                         "parity": "KV formats are this project's definitions: parity unpinned",
+                         "step_achieved": step_bytes / (step_us * 1e-6) / 1e9, "step_frac": step_bytes / (step_us * 1e-6) / 1e9 / peak}}
+    print(json.dumps(line), flush=True)
+
+
 def sweep_linear(a, ranks=(256, 1024), precisions=(8, 4, "binary"), ms=None, copies=8):
     """configs[1]: x [M, 4096] bf16, W 4096x4096 factored at rank r, factors at 8 / 4 bits and binary; time of
     LinearCompressed.forward per call, TFLOP/s and GB/s against the measured peaks.  Returns a list of records."""
@@ -604,5 +701,7 @@ if __name__ == "__main__":
             print(json.dumps(rec))
     elif args.impl == "reference":
         run_reference(args)
+    elif args.config == "c5":
+        run_c5(args)
     else:
         run_ours(args)

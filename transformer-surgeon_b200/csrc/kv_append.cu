@@ -1,7 +1,9 @@
 // Fused (RoPE on K +) quantize-and-append into the paged KV pools, and the FP8 scale
 // reduction over a prompt.  One warp owns one (token, kv head) vector of d elements:
 // lane l holds elements [l*d/32, (l+1)*d/32).  HBM-bound: reads 2*d*sizeof(act) bytes
-// and writes 2*d*b_elem (+ scales) per vector.
+// and writes 2*d*b_elem (+ scales) per vector.  Decode steps (one token per sequence) use
+// kv_append_kernel; prompt chunks of 16 tokens or more use kv_append_pages_kernel, in which
+// a CTA owns a whole page and writes the token-minor V record with 16-byte vectors.
 //
 // Quantization arithmetic (IEEE fp32, round-to-nearest-even) per format:
 //   int8  : s = amax/127, code = clamp(rint(x/(s+1e-6)), +-127)   (the reference's weight
@@ -22,13 +24,31 @@ template <> struct BytesN<1> { using type = uint8_t; };
 template <> struct BytesN<2> { using type = uint16_t; };
 template <> struct BytesN<4> { using type = uint32_t; };
 
+// This lane's EPL elements of a vector, as fp32 (one 8- or 16-byte load when the vector is aligned for it).
+template <typename T, int D>
+__device__ __forceinline__ void load_raw(const T* __restrict__ src, int lane, float (&x)[D / 32]) {
+  constexpr int EPL = D / 32;
+  const T* p = src + lane * EPL;
+  if (sizeof(T) * EPL == 8 && (reinterpret_cast<uintptr_t>(p) & 7) == 0) {
+    const uint2 r = *reinterpret_cast<const uint2*>(p);
+    const T* e = reinterpret_cast<const T*>(&r);
+#pragma unroll
+    for (int i = 0; i < EPL; ++i) x[i] = to_f32<T>(e[i]);
+  } else if (sizeof(T) * EPL == 16 && (reinterpret_cast<uintptr_t>(p) & 15) == 0) {
+    const uint4 r = *reinterpret_cast<const uint4*>(p);
+    const T* e = reinterpret_cast<const T*>(&r);
+#pragma unroll
+    for (int i = 0; i < EPL; ++i) x[i] = to_f32<T>(e[i]);
+  } else {
+#pragma unroll
+    for (int i = 0; i < EPL; ++i) x[i] = to_f32<T>(p[i]);
+  }
+}
 // Rotate (optional) and round to T; returns this lane's EPL elements as fp32.
 template <typename T, int D>
-__device__ __forceinline__ void load_vec(const T* __restrict__ src, int lane, float (&x)[D / 32], bool rope,
-                                         const float* __restrict__ cosr, const float* __restrict__ sinr) {
+__device__ __forceinline__ void rope_vec(int lane, float (&x)[D / 32], bool rope, const float* __restrict__ cosr,
+                                         const float* __restrict__ sinr) {
   constexpr int EPL = D / 32;
-#pragma unroll
-  for (int i = 0; i < EPL; ++i) x[i] = to_f32<T>(src[lane * EPL + i]);
   if (rope) {
 #pragma unroll
     for (int i = 0; i < EPL; ++i) {
@@ -40,6 +60,12 @@ __device__ __forceinline__ void load_vec(const T* __restrict__ src, int lane, fl
       x[i] = rnd<T>(lane < 16 ? __fsub_rn(a, b) : __fadd_rn(b, a));
     }
   }
+}
+template <typename T, int D>
+__device__ __forceinline__ void load_vec(const T* __restrict__ src, int lane, float (&x)[D / 32], bool rope,
+                                         const float* __restrict__ cosr, const float* __restrict__ sinr) {
+  load_raw<T, D>(src, lane, x);
+  rope_vec<T, D>(lane, x, rope, cosr, sinr);
 }
 
 // Unquantized pages (TSB200_KV_F32 / TSB200_KV_BF16): K and V records are both [16 tok][d] of T.
@@ -172,6 +198,107 @@ __global__ void kv_append_kernel(tsb200_kv_desc kv, T* __restrict__ q, int64_t q
   else quant_store<D, FMT, true>(x, lane, kv.v_pool + rec, slot, vscale);
 }
 
+// Bulk append (T >= 16 tokens per sequence, quantized formats): ONE CTA OWNS ONE PAGE of one (sequence, kv head).
+// Its 16 warps quantize the page's 16 tokens; K goes out token-major as above (one contiguous vector per warp).  V is
+// stored token-minor ([element][16 tokens], so that the decode kernels read consecutive tokens of one element from
+// consecutive bytes): written token by token that is one byte per 16-byte row and a partial sector per element.
+// Here the warps stage the page's V codes and scales in shared memory in the token-major form, and the CTA then
+// writes the record transposed, 16 bytes (one element row) per thread - whole sectors, fully coalesced.  A page the
+// append only partly covers (the first / last page of the range) keeps its other slots: those are written slot by slot.
+// Extra CTAs along x rotate the query heads in place.
+template <typename T, int D, int FMT>
+__global__ void __launch_bounds__(512)
+kv_append_pages_kernel(tsb200_kv_desc kv, T* __restrict__ q, int64_t qs, int qheads, const T* __restrict__ k,
+                       const T* __restrict__ v, int64_t ks, int64_t vs_, int64_t Tn, const int32_t* __restrict__ new_lens,
+                       const float* __restrict__ rope_cos, const float* __restrict__ rope_sin, int64_t rope_rows,
+                       int64_t rec_bytes, int page_blocks) {
+  constexpr int VB = FMT == TSB200_KV_NVFP4 ? D / 2 : D;                  // bytes of V codes per token
+  constexpr int REC = FMT == TSB200_KV_INT8 ? 16 * D + 64 : (FMT == TSB200_KV_FP8 ? 16 * D : 9 * D);
+  __shared__ __align__(16) uint8_t stage[REC];                            // the page's V record in token-major form
+  pdl_launch_dependents();
+  pdl_wait();
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  const int64_t b = blockIdx.z;
+  const int h = blockIdx.y;
+  const int64_t n_b = new_lens ? min((int64_t)new_lens[b], Tn) : Tn;
+  const int64_t start = kv.seq_lens[b];
+  if ((int)blockIdx.x >= page_blocks) {
+    // ---- query rotation: 16 (token, head) vectors per CTA
+    if (q == nullptr || rope_cos == nullptr) return;
+    const int64_t idx = (((int64_t)blockIdx.x - page_blocks) * gridDim.y + blockIdx.y) * 16 + w;
+    if (idx >= Tn * qheads) return;
+    const int64_t j = idx / qheads;
+    const int qh = (int)(idx - j * qheads);
+    if (j >= n_b) return;
+    int64_t qp = start + j;
+    qp = qp < 0 ? 0 : (qp >= rope_rows ? rope_rows - 1 : qp);
+    float xq[D / 32];
+    T* dst = q + (b * Tn + j) * qs + (int64_t)qh * D;
+    load_vec<T, D>(dst, lane, xq, true, rope_cos + qp * (D / 2), rope_sin + qp * (D / 2));
+#pragma unroll
+    for (int i = 0; i < D / 32; ++i) dst[lane * (D / 32) + i] = from_f32<T>(xq[i]);
+    return;
+  }
+  // ---- page blockIdx.x of the appended range: logical page (start / 16 + blockIdx.x), slot w
+  const int64_t lp = (start >> 4) + blockIdx.x;
+  const int64_t p = lp * 16 + w;                       // position of this warp's token
+  const int64_t j = p - start;
+  const bool valid = j >= 0 && j < n_b;
+  const bool page_ok = lp < kv.bt_stride;
+  int64_t page = page_ok ? kv.block_table[b * kv.bt_stride + lp] : -1;
+  const bool store = page >= 0 && page < kv.num_pages;
+  if (!store) page = 0;
+  // the page is covered completely when its first and last positions are both appended
+  const bool full = lp * 16 >= start && lp * 16 + 15 < start + n_b;
+  uint8_t* krec = kv.k_pool + (page * kv.hkv + h) * rec_bytes;
+  uint8_t* vrec = kv.v_pool + (page * kv.hkv + h) * rec_bytes;
+  float kscale = 1.f, vscale = 1.f;
+  if (FMT == TSB200_KV_FP8) {
+    kscale = kv.k_scale[b * kv.hkv + h];
+    vscale = kv.v_scale[b * kv.hkv + h];
+  }
+  if (valid && store) {
+    const bool rope = rope_cos != nullptr;
+    const int64_t rp = p >= rope_rows ? rope_rows - 1 : p;
+    float x[D / 32], xv[D / 32];
+    const int64_t bt = b * Tn + j;
+    load_raw<T, D>(k + bt * ks + (int64_t)h * D, lane, x);              // both vectors in flight before either is used
+    load_raw<T, D>(v + bt * vs_ + (int64_t)h * D, lane, xv);
+    rope_vec<T, D>(lane, x, rope, rope ? rope_cos + rp * (D / 2) : nullptr, rope ? rope_sin + rp * (D / 2) : nullptr);
+    quant_store<D, FMT, false>(x, lane, krec, w, kscale);
+    quant_store<D, FMT, false>(xv, lane, stage, w, vscale);             // token-major, into shared memory
+  }
+  __syncthreads();
+  if (!store) return;
+  if (full) {
+    // transposed record: row e (16 bytes) = the codes of element (pair) e for tokens 0..15
+    for (int e = threadIdx.x; e < VB; e += blockDim.x) {
+      unsigned wds[4];
+#pragma unroll
+      for (int c = 0; c < 4; ++c)
+        wds[c] = (unsigned)stage[(4 * c) * VB + e] | ((unsigned)stage[(4 * c + 1) * VB + e] << 8) |
+                 ((unsigned)stage[(4 * c + 2) * VB + e] << 16) | ((unsigned)stage[(4 * c + 3) * VB + e] << 24);
+      *reinterpret_cast<uint4*>(vrec + (int64_t)e * 16) = make_uint4(wds[0], wds[1], wds[2], wds[3]);
+    }
+    if constexpr (FMT == TSB200_KV_INT8) {              // fp32 scale per token: same place in both forms
+      if (threadIdx.x < 16) reinterpret_cast<float*>(vrec + 16 * D)[threadIdx.x] = reinterpret_cast<const float*>(stage + 16 * D)[threadIdx.x];
+    } else if constexpr (FMT == TSB200_KV_NVFP4) {      // block scales: [16 tokens][D/16] -> [D/16][16 tokens]
+      if (threadIdx.x < D) {
+        const int blk = threadIdx.x >> 4, t = threadIdx.x & 15;
+        vrec[16 * (D / 2) + blk * 16 + t] = stage[16 * (D / 2) + t * (D / 16) + blk];
+      }
+    }
+  } else if (valid) {
+    // partly covered page: only this warp's slot is written
+    for (int e = lane; e < VB; e += 32) vrec[(int64_t)e * 16 + w] = stage[w * VB + e];
+    if constexpr (FMT == TSB200_KV_INT8) {
+      if (lane == 0) reinterpret_cast<float*>(vrec + 16 * D)[w] = reinterpret_cast<const float*>(stage + 16 * D)[w];
+    } else if constexpr (FMT == TSB200_KV_NVFP4) {
+      if (lane < D / 16) vrec[16 * (D / 2) + lane * 16 + w] = stage[16 * (D / 2) + w * (D / 16) + lane];
+    }
+  }
+}
+
 // One CTA per (b, h): amax over the T tokens of the prompt -> scale = amax/448 (1 if 0).
 template <typename T, int D>
 __global__ void kv_fp8_scales_kernel(const T* __restrict__ k, const T* __restrict__ v, int64_t Tn, int hkv,
@@ -213,10 +340,28 @@ __global__ void kv_fp8_scales_kernel(const T* __restrict__ k, const T* __restric
 template <typename T, int D>
 int launch_append(const tsb200_kv_desc& kv, void* q, int64_t qs, int qheads, const void* k, const void* v, int64_t ks, int64_t vs, int64_t B, int64_t Tn, const int32_t* new_lens,
                   const float* rc, const float* rs, int64_t rr, cudaStream_t s) {
+  const int64_t rec = (int64_t)tsb200_kv_record_bytes(kv.format, D);
+  if (Tn >= 16 && kv.format <= TSB200_KV_NVFP4 && B <= 65535 && kv.hkv <= 65535) {
+    // bulk: one CTA per (sequence, kv head, page touched) + CTAs that rotate the query heads
+    const int page_blocks = (int)((Tn + 15) / 16) + 1;          // the range may straddle one more page than it fills
+    const int64_t q_blocks = q ? (Tn * qheads + 16 * kv.hkv - 1) / (16 * (int64_t)kv.hkv) : 0;
+    const dim3 grid((unsigned)(page_blocks + q_blocks), (unsigned)kv.hkv, (unsigned)B);
+    switch (kv.format) {
+      case TSB200_KV_INT8:
+        TSB_CUDA(launch_kernel(kv_append_pages_kernel<T, D, TSB200_KV_INT8>, grid, dim3(512), 0, s, kv, (T*)q, qs, qheads, (const T*)k, (const T*)v, ks, vs, Tn, new_lens, rc, rs, rr, rec, page_blocks));
+        break;
+      case TSB200_KV_FP8:
+        TSB_CUDA(launch_kernel(kv_append_pages_kernel<T, D, TSB200_KV_FP8>, grid, dim3(512), 0, s, kv, (T*)q, qs, qheads, (const T*)k, (const T*)v, ks, vs, Tn, new_lens, rc, rs, rr, rec, page_blocks));
+        break;
+      default:
+        TSB_CUDA(launch_kernel(kv_append_pages_kernel<T, D, TSB200_KV_NVFP4>, grid, dim3(512), 0, s, kv, (T*)q, qs, qheads, (const T*)k, (const T*)v, ks, vs, Tn, new_lens, rc, rs, rr, rec, page_blocks));
+    }
+    TSB_LAUNCH_CHECK();
+    return TSB200_OK;
+  }
   const int64_t warps = B * Tn * (kv.hkv + (q ? qheads : 0));
   const int64_t blocks = (warps + 7) / 8;
   if (blocks > 0x7fffffffLL) return TSB200_ERR_UNSUPPORTED;
-  const int64_t rec = (int64_t)tsb200_kv_record_bytes(kv.format, D);
   switch (kv.format) {
     case TSB200_KV_INT8:
       TSB_CUDA(launch_kernel(kv_append_kernel<T, D, TSB200_KV_INT8>, dim3((unsigned)blocks), dim3(256), 0, s, kv, (T*)q, qs, qheads, (const T*)k, (const T*)v, ks, vs, B, Tn, new_lens, rc, rs, rr, rec));
