@@ -138,6 +138,18 @@ int tsb200_linear(const tsb200_linear_desc* d, const void* x, void* y, int64_t M
 int tsb200_linear_simt(const tsb200_linear_desc* d, const void* x, void* y, int64_t M,
                        void* workspace, size_t workspace_bytes, void* stream);
 
+/* Greedy head: tokens[m] = argmax_n (x . W^T + bias)[m, n] with the logits rounded to the act dtype first, i.e. the
+ * token torch.argmax would pick from tsb200_linear's output (the first maximum on ties).
+ * Replaces the final layer + argmax of a greedy decode step (export/common.py:167,175 for the blocks path; the
+ * lm_head call and the argmax of Hugging Face's greedy search for the HF path).  For a dense bf16 full-rank head with
+ * M <= 128 the reduction happens in the GEMM's epilogue (per 128-column tile, then one small kernel): the
+ * [M, vocabulary] logits are never written or re-read.  Any other head (packed, low-rank, fp32) computes its logits
+ * into the workspace and reduces them.  tokens: device int64 [M].  The first 16640 bytes of the workspace follow the
+ * rules of tsb200_linear's workspace. */
+size_t tsb200_linear_argmax_workspace_bytes(const tsb200_linear_desc* d, int64_t M);
+int tsb200_linear_argmax(const tsb200_linear_desc* d, const void* x, int64_t* tokens, int64_t M,
+                         void* workspace, size_t workspace_bytes, void* stream);
+
 /* Gated MLP block: y = down(silu(gate(x)) * up(x)).
  * Replaces: blocks/mlp.py:171-185 (MLPGated.forward: up_proj, gate_proj, activation * up, down_proj)
  * with SiLU as the activation (the Qwen2 / Llama choice).  gate and up map in -> inter, down maps

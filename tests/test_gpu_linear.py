@@ -192,3 +192,40 @@ def test_few_tokens_at_model_widths(cuda, p, M, K, N, r):
     assert torch.equal(y, y2)
     assert rel_err(y, ref) < 1e-2, rel_err(y, ref)
     assert ops.PackedLinear.device_status(device=cuda) == 0
+
+
+@pytest.mark.parametrize("M,K,N", [(1, 512, 1000), (32, 1024, 50257), (100, 256, 4099)])
+def test_greedy_head_equals_argmax_of_logits(cuda, M, K, N):
+    """tsb200_linear_argmax on a dense bf16 head (reduction in the GEMM epilogue, logits never stored) picks the token
+    torch.argmax picks from tsb200_linear's logits - including ties, which go to the first maximum."""
+    from transformer_surgeon_b200 import ops
+    g = torch.Generator(device=cuda).manual_seed(41)
+    W = (torch.randn((N, K), generator=g, device=cuda) * 0.05).bfloat16()
+    W[N - 3] = W[7]                                      # duplicated rows: their logits tie exactly
+    W[N // 2] = W[7]
+    b = (torch.randn(N, generator=g, device=cuda) * 0.1).bfloat16()
+    b[N - 3] = b[7]
+    b[N // 2] = b[7]
+    x = torch.randn((M, K), generator=g, device=cuda).bfloat16()
+    x[0] = W[7].float().sign().bfloat16()                # make row 7 (and its copies) the winner for token 0
+    lin = ops.PackedLinear(ops.Factor.dense(W), None, b, torch.bfloat16)
+    logits = lin(x)
+    toks = lin.argmax(x)
+    assert torch.equal(toks, torch.argmax(logits, dim=-1))
+    assert int(toks[0]) == 7
+    assert torch.equal(lin.argmax(x), toks)
+
+
+def test_greedy_head_general_route(cuda):
+    """A packed low-rank head and an fp32 head: logits into the workspace, then the library's own argmax kernel."""
+    from transformer_surgeon_b200 import ops
+    g = torch.Generator(device=cuda).manual_seed(42)
+    U = (torch.randn((3000, 64), generator=g, device=cuda) * 0.05).bfloat16()
+    V = (torch.randn((64, 256), generator=g, device=cuda) * 0.05).bfloat16()
+    lin = ops.PackedLinear(ops.Factor.quantize(U, 4), ops.Factor.quantize(V, 4), None, torch.bfloat16)
+    x = torch.randn((9, 256), generator=g, device=cuda).bfloat16()
+    assert torch.equal(lin.argmax(x), torch.argmax(lin(x), dim=-1))
+    W = torch.randn((777, 96), generator=g, device=cuda)
+    lin32 = ops.PackedLinear(ops.Factor.dense(W), None, None, torch.float32)
+    x32 = torch.randn((5, 96), generator=g, device=cuda)
+    assert torch.equal(lin32.argmax(x32), torch.argmax(lin32(x32), dim=-1))

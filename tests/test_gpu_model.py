@@ -118,6 +118,27 @@ def test_cuda_graph_step_matches_eager(cuda):
     assert dec.kernel_launches_per_step > 0
 
 
+def test_greedy_head_step_gives_the_same_tokens(cuda):
+    """With `greedy_head` the step ends in the fused lm_head + argmax: same next tokens as logits -> argmax, eagerly
+    and replayed from a CUDA graph."""
+    g, dec = build("llama", cuda, "int8", dtype=torch.bfloat16, batch=2)
+    ids = g["ids"].to(cuda)
+    want = []
+    for t in range(9):
+        dec.step(ids[:, t])
+        want.append(dec.next_tokens.clone())
+    dec.reset()
+    dec.greedy_head = True
+    for t in range(5):
+        assert dec.step(ids[:, t]) is None
+        assert torch.equal(dec.next_tokens, want[t])
+    dec.capture()
+    for t in range(5, 9):
+        dec.step(ids[:, t])
+        assert torch.equal(dec.next_tokens, want[t])
+    dec.check_status()
+
+
 def test_pack_model_rebinds_per_instance(cuda):
     """pack_model keeps the class of each module (the reference checks `type(m) is LinearCompressed`)
     and routes forward through the kernels; unpack_model restores the class's forward."""

@@ -57,6 +57,8 @@ SIGNATURES = {
     "tsb200_linear_workspace_bytes": (_sz, [_LD, _i64]),
     "tsb200_linear": (_i32, [_LD, _vp, _vp, _i64, _vp, _sz, _vp]),
     "tsb200_linear_simt": (_i32, [_LD, _vp, _vp, _i64, _vp, _sz, _vp]),
+    "tsb200_linear_argmax_workspace_bytes": (_sz, [_LD, _i64]),
+    "tsb200_linear_argmax": (_i32, [_LD, _vp, _vp, _i64, _vp, _sz, _vp]),
     "tsb200_mlp_gated_workspace_bytes": (_sz, [_LD, _LD, _LD, _i64]),
     "tsb200_mlp_gated": (_i32, [_LD, _LD, _LD, _vp, _vp, _i64, _vp, _sz, _vp]),
     "tsb200_kv_record_bytes": (_sz, [_i32, _i32]),

@@ -30,6 +30,8 @@ struct TcParams {
   __nv_bfloat16* y;        // [M, N]
   float* partial;          // [M, N] fp32 accumulation buffer when gridDim.z > 1
   int* status;             // device status word
+  float* amax_val;         // greedy head: per (token, weight tile) maximum of the rounded logits [M][n_tiles] ...
+  int* amax_idx;           // ... and the column that holds it (the first one on ties)
 };
 
 template <int TN> struct SmemLayout {
@@ -39,7 +41,9 @@ template <int TN> struct SmemLayout {
   static constexpr int kBytes = NSTG * kStage + 1024 /*alignment slack*/ + 256 /*barriers*/;
 };
 
-template <int TN>
+// ARGMAX: the epilogue does not store y; it reduces every token's logits of this 128-column tile to (maximum, column)
+// - the greedy head: the [M, vocabulary] logits are never written.
+template <int TN, bool ARGMAX>
 __global__ void __launch_bounds__(kThreads, 1)
 linear_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, TcParams p) {
   using L = SmemLayout<TN>;
@@ -123,6 +127,43 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
       const int64_t n = (int64_t)n0 + row;
       const float sc = (p.scale && n < p.N) ? p.scale[n] : 1.0f;
       const float bv = (p.bias && n < p.N && blockIdx.z == 0) ? __bfloat162float(p.bias[n]) : 0.f;
+      if (ARGMAX) {
+        // logits of the tile -> shared memory [token][row] (the ring is idle: every MMA has completed), rounded to
+        // bf16 as the stored logits would be, so that the choice equals an argmax over them
+        float* vt = reinterpret_cast<float*>(smem);                  // [TN][129]
+        float* best_v = vt + TN * 129;                               // [TN][parts]
+        int* best_i = reinterpret_cast<int*>(best_v + 128);
+#pragma unroll 1
+        for (int c0 = 0; c0 < TN; c0 += 16) {
+          unsigned r[16];
+          tmem_ld16(tmem_base + ((unsigned)(q * 32) << 16) + (unsigned)c0, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 16; ++j)
+            vt[(c0 + j) * 129 + row] = n < p.N ? __bfloat162float(__float2bfloat16_rn(__uint_as_float(r[j]) * sc + bv)) : -INFINITY;
+        }
+        asm volatile("bar.sync 1, 128;\n" ::: "memory");
+        constexpr int PARTS = 128 / TN;                               // threads per token; each scans TN consecutive rows
+        const int tid = threadIdx.x - 64, col = tid % TN, part = tid / TN;
+        float bvv = -INFINITY;
+        int bii = part * TN;
+        for (int rr = 0; rr < TN; ++rr) {
+          const float v = vt[col * 129 + part * TN + rr];
+          if (v > bvv) { bvv = v; bii = part * TN + rr; }             // ascending scan, strict: the first maximum wins
+        }
+        best_v[col * PARTS + part] = bvv;
+        best_i[col * PARTS + part] = bii;
+        asm volatile("bar.sync 1, 128;\n" ::: "memory");
+        if (tid < TN && (int64_t)m0 + tid < p.M) {
+          float fv = best_v[tid * PARTS];
+          int fi = best_i[tid * PARTS];
+          for (int pp = 1; pp < PARTS; ++pp)
+            if (best_v[tid * PARTS + pp] > fv) { fv = best_v[tid * PARTS + pp]; fi = best_i[tid * PARTS + pp]; }
+          const int64_t o = ((int64_t)m0 + tid) * gridDim.x + blockIdx.x;
+          p.amax_val[o] = fv;
+          p.amax_idx[o] = n0 + fi;
+        }
+      } else {
 #pragma unroll 1
       for (int c0 = 0; c0 < TN; c0 += 16) {
         unsigned r[16];
@@ -140,6 +181,7 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
           }
         }
       }
+      }
     }
   }
   if (*abort_flag) {
@@ -155,6 +197,63 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
   if (threadIdx.x == 0 && *abort_flag) atomicMax(p.status, *abort_flag);
 }
 
+// Greedy head, second step: the per-tile (maximum, column) pairs of one token -> its token id.  Ties go to the
+// smaller column, as in an argmax that returns the first maximum.
+__global__ void argmax_finalize_kernel(const float* __restrict__ val, const int* __restrict__ idx, int n_tiles, int64_t* __restrict__ out) {
+  pdl_launch_dependents();
+  pdl_wait();
+  __shared__ float sv[256];
+  __shared__ int si[256];
+  const int64_t m = blockIdx.x;
+  float bv = -INFINITY;
+  int bi = 0x7fffffff;
+  for (int t = threadIdx.x; t < n_tiles; t += blockDim.x) {
+    const float v = val[m * n_tiles + t];
+    const int i = idx[m * n_tiles + t];
+    if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; }
+  }
+  sv[threadIdx.x] = bv;
+  si[threadIdx.x] = bi;
+  __syncthreads();
+  for (int s = 128; s > 0; s >>= 1) {
+    if ((int)threadIdx.x < s) {
+      const float v = sv[threadIdx.x + s];
+      const int i = si[threadIdx.x + s];
+      if (v > sv[threadIdx.x] || (v == sv[threadIdx.x] && i < si[threadIdx.x])) { sv[threadIdx.x] = v; si[threadIdx.x] = i; }
+    }
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) out[m] = si[0] == 0x7fffffff ? 0 : si[0];
+}
+
+// Argmax over stored logits y [M, N] (the route for heads the fused epilogue does not serve).
+template <typename T>
+__global__ void argmax_rows_kernel(const T* __restrict__ y, int64_t N, int64_t* __restrict__ out) {
+  pdl_launch_dependents();
+  pdl_wait();
+  __shared__ float sv[256];
+  __shared__ int si[256];
+  const int64_t m = blockIdx.x;
+  float bv = -INFINITY;
+  int bi = 0x7fffffff;
+  for (int64_t n = threadIdx.x; n < N; n += blockDim.x) {
+    const float v = to_f32<T>(y[m * N + n]);
+    if (v > bv) { bv = v; bi = (int)n; }               // ascending per thread: the first maximum is kept
+  }
+  sv[threadIdx.x] = bv;
+  si[threadIdx.x] = bi;
+  __syncthreads();
+  for (int s = 128; s > 0; s >>= 1) {
+    if ((int)threadIdx.x < s) {
+      const float v = sv[threadIdx.x + s];
+      const int i = si[threadIdx.x + s];
+      if (v > sv[threadIdx.x] || (v == sv[threadIdx.x] && i < si[threadIdx.x])) { sv[threadIdx.x] = v; si[threadIdx.x] = i; }
+    }
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) out[m] = si[0] == 0x7fffffff ? 0 : si[0];
+}
+
 // fp32 split-K buffer -> bf16 output.
 __global__ void splitk_finalize_kernel(float* __restrict__ partial, __nv_bfloat16* __restrict__ y, int64_t n) {
   for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
@@ -164,7 +263,7 @@ __global__ void splitk_finalize_kernel(float* __restrict__ partial, __nv_bfloat1
 }
 
 // ---------------------------------------------------------------- host side --------
-template <int TN>
+template <int TN, bool ARGMAX>
 int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, const TcParams& p, dim3 grid, cudaStream_t s) {
   using L = SmemLayout<TN>;
   static bool configured[64] = {false};
@@ -172,16 +271,17 @@ int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, const TcParams& p, d
   TSB_CUDA(cudaGetDevice(&dev));
   if (dev < 0 || dev >= 64) return TSB200_ERR_DEVICE;
   if (!configured[dev]) {
-    TSB_CUDA(cudaFuncSetAttribute(linear_tc_kernel<TN>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kBytes));
+    TSB_CUDA(cudaFuncSetAttribute(linear_tc_kernel<TN, ARGMAX>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kBytes));
     configured[dev] = true;
   }
-  TSB_CUDA(launch_kernel(linear_tc_kernel<TN>, grid, dim3(kThreads), (size_t)L::kBytes, s, mw, mx, p));
+  TSB_CUDA(launch_kernel(linear_tc_kernel<TN, ARGMAX>, grid, dim3(kThreads), (size_t)L::kBytes, s, mw, mx, p));
   return TSB200_OK;
 }
 
-// One dense GEMM: y[M, N] = x[M, K] . W[N, K]^T + bias (bf16 in/out; bits must be 16).
+// One dense GEMM: y[M, N] = x[M, K] . W[N, K]^T + bias (bf16 in/out; bits must be 16).  tokens != null: the greedy
+// head instead - no y; amax scratch (float [M][n_tiles], then int [M][n_tiles]) -> tokens [M] (M <= 128).
 int gemm_tc(const void* W, int bits, const float* scale, const void* bias, const void* x, void* y, int64_t M, int64_t K,
-            int64_t N, float* partial, int* status, cudaStream_t s) {
+            int64_t N, float* partial, int* status, cudaStream_t s, int64_t* tokens = nullptr, void* amax = nullptr) {
   const int tn = M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : 128));
   if (bits != 16) return TSB200_ERR_UNSUPPORTED;
   CUtensorMap mw, mx;
@@ -195,21 +295,38 @@ int gemm_tc(const void* W, int bits, const float* scale, const void* bias, const
   const int64_t n_tiles = (N + BM - 1) / BM, m_tiles = (M + tn - 1) / tn;
   // split K until the grid covers the 148 SMs (each split keeps >= 4 k-blocks)
   int splits = 1;
-  while (n_tiles * m_tiles * splits < 148 && splits * 2 <= 16 && kb_total / (splits * 2) >= 4) splits *= 2;
+  while (!tokens && n_tiles * m_tiles * splits < 148 && splits * 2 <= 16 && kb_total / (splits * 2) >= 4) splits *= 2;
   const int kb_per_split = (kb_total + splits - 1) / splits;
   splits = (kb_total + kb_per_split - 1) / kb_per_split;
   if (n_tiles > 0x7fffffffLL || m_tiles > 65535) return TSB200_ERR_UNSUPPORTED;
   TcParams p;
   p.M = M; p.N = N; p.K = K; p.kb_total = kb_total; p.kb_per_split = kb_per_split;
   p.scale = scale; p.bias = (const __nv_bfloat16*)bias; p.y = (__nv_bfloat16*)y; p.partial = partial; p.status = status;
+  p.amax_val = (float*)amax;
+  p.amax_idx = (int*)((float*)amax + (tokens ? M * n_tiles : 0));
+  if (tokens) {
+    if (m_tiles != 1) return TSB200_ERR_UNSUPPORTED;
+    dim3 g((unsigned)n_tiles, 1, 1);
+    int st2;
+    switch (tn) {
+      case 16: st2 = launch_tc<16, true>(mw, mx, p, g, s); break;
+      case 32: st2 = launch_tc<32, true>(mw, mx, p, g, s); break;
+      case 64: st2 = launch_tc<64, true>(mw, mx, p, g, s); break;
+      default: st2 = launch_tc<128, true>(mw, mx, p, g, s); break;
+    }
+    if (st2 != TSB200_OK) return st2;
+    TSB_CUDA(launch_kernel(argmax_finalize_kernel, dim3((unsigned)M), dim3(256), 0, s, (const float*)p.amax_val, (const int*)p.amax_idx,
+                           (int)n_tiles, tokens));
+    return TSB200_OK;
+  }
   if (splits > 1) TSB_CUDA(cudaMemsetAsync(partial, 0, (size_t)M * N * sizeof(float), s));
   dim3 grid((unsigned)n_tiles, (unsigned)m_tiles, (unsigned)splits);
   int st;
   switch (tn) {
-    case 16: st = launch_tc<16>(mw, mx, p, grid, s); break;
-    case 32: st = launch_tc<32>(mw, mx, p, grid, s); break;
-    case 64: st = launch_tc<64>(mw, mx, p, grid, s); break;
-    default: st = launch_tc<128>(mw, mx, p, grid, s); break;
+    case 16: st = launch_tc<16, false>(mw, mx, p, grid, s); break;
+    case 32: st = launch_tc<32, false>(mw, mx, p, grid, s); break;
+    case 64: st = launch_tc<64, false>(mw, mx, p, grid, s); break;
+    default: st = launch_tc<128, false>(mw, mx, p, grid, s); break;
   }
   if (st != TSB200_OK) return st;
   if (splits > 1) {
@@ -233,6 +350,19 @@ bool tc_supported_factor(int bits, int64_t K) {
 // Persistent kernel for packed factors (linear_tcq.cu).
 int gemm_tcq(const void* W, int bits, const float* scale, const void* bias, const void* x, void* y, int64_t M, int64_t K,
              int64_t N, float* partial, int* counters, int* status, cudaStream_t s);
+
+// Greedy head.  Fused route (dense bf16, full rank, M <= 128): no logits in memory.  Returns TSB200_ERR_UNSUPPORTED
+// for every other layer (the caller then computes the logits and reduces them).
+int linear_argmax_tc(const tsb200_linear_desc* d, const void* x, int64_t* tokens, int64_t M, void* amax, int* status, cudaStream_t s) {
+  if (d->act_dtype != TSB200_BF16 || d->rank > 0 || d->u_bits != 16 || M > 128 || (d->in_features % 8)) return TSB200_ERR_UNSUPPORTED;
+  if (!aligned(x, 16)) return TSB200_ERR_ARG;
+  return gemm_tc(d->u, 16, nullptr, d->bias, x, nullptr, M, d->in_features, d->out_features, nullptr, status, s, tokens, amax);
+}
+int argmax_rows(const void* y, int dtype, int64_t M, int64_t N, int64_t* tokens, cudaStream_t s) {
+  if (dtype == TSB200_F32) TSB_CUDA(launch_kernel(argmax_rows_kernel<float>, dim3((unsigned)M), dim3(256), 0, s, (const float*)y, N, tokens));
+  else TSB_CUDA(launch_kernel(argmax_rows_kernel<__nv_bfloat16>, dim3((unsigned)M), dim3(256), 0, s, (const __nv_bfloat16*)y, N, tokens));
+  return TSB200_OK;
+}
 
 int linear_tc(const tsb200_linear_desc* d, const void* x, void* y, int64_t M, void* workspace, size_t workspace_bytes,
               cudaStream_t s) {

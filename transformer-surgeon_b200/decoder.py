@@ -122,6 +122,10 @@ class CompressedDecoder:
         self.graph = None
         self.kernel_launches_per_step = 0
         self.peer = None                    # tensor_parallel.PeerBuffers once enable_peer_allreduce() ran
+        # greedy_head: the step ends in tsb200_linear_argmax (no logits in memory; `step` then returns None and only
+        # `next_tokens` is updated) instead of lm_head -> logits -> argmax.  Set before capture().
+        self.greedy_head = False
+        self.head_ws = None
 
     def enable_peer_allreduce(self):
         """Tensor parallel: sum the row-parallel partial outputs with the library's own kernel over NVLink
@@ -201,6 +205,12 @@ class CompressedDecoder:
             peer.allreduce_add_rmsnorm(1, self.resid, self.final_norm, c.rms_eps, out=self.xn); n += 1
         else:
             ops.add_rmsnorm(self.resid, delta, self.final_norm, c.rms_eps, c.norm_variant, out=self.xn); n += 1
+        if self.greedy_head:
+            if self.head_ws is None:
+                self.head_ws = torch.zeros(self.lm_head.argmax_workspace_bytes(B), dtype=torch.uint8, device=self.device)
+            self.lm_head.argmax(self.xn, out=self.next_tokens, ws=self.head_ws); n += 2
+            self.kernel_launches_per_step = n
+            return None
         self.lm_head(self.xn, out=self.logits, ws=self.lin_ws); n += 1
         torch.argmax(self.logits, dim=-1, out=self.next_tokens)
         self.kernel_launches_per_step = n
@@ -238,7 +248,7 @@ class CompressedDecoder:
             self.tokens.copy_(tokens, non_blocking=True)
         if self.graph is not None:
             self.graph.replay()
-            return self.logits
+            return None if self.greedy_head else self.logits
         return self._step_kernels()
 
     def reset(self):
@@ -267,6 +277,8 @@ class CompressedDecoder:
         (the kernels then return early and the results of that step are not to be trusted).  Synchronises;
         generate() calls it once at the end, long-running callers every so many steps."""
         words = {"linear": self.lin_ws[:4], "mlp": self.mlp_ws[:4], "attention": self.attn_ws[ops.ATTN_STATUS_OFFSET:ops.ATTN_STATUS_OFFSET + 4]}
+        if self.head_ws is not None:
+            words["head"] = self.head_ws[:4]
         bad = {k: int(v.view(torch.int32).item()) for k, v in words.items()}
         if self.peer is not None:
             bad["peer all-reduce"] = int(self.peer.status())

@@ -271,6 +271,24 @@ class PackedLinear:
         check(fn(C.byref(self.desc), _p(x2), _p(out), M, _p(ws), ws.numel(), _stream()), "tsb200_linear")
         return out.reshape(*lead, self.out_features)
 
+    def argmax_workspace_bytes(self, M):
+        return int(_lib.load().tsb200_linear_argmax_workspace_bytes(C.byref(self.desc), M))
+
+    def argmax(self, x, out=None, ws=None):
+        """Greedy head: argmax over the layer's outputs per row of x [M, in] -> int64 [M]; equals
+        torch.argmax(self(x), -1) (first maximum on ties).  A dense bf16 head reduces inside the GEMM's epilogue
+        and never writes the logits."""
+        lib = _lib.load()
+        x = _cuda(x, "x")
+        x2 = x.reshape(-1, x.shape[-1])
+        M = x2.shape[0]
+        if out is None:
+            out = torch.empty(M, dtype=torch.int64, device=x.device)
+        if ws is None:
+            ws = workspace(x.device, self.argmax_workspace_bytes(M), "head")
+        check(lib.tsb200_linear_argmax(C.byref(self.desc), _p(x2), _p(out), M, _p(ws), ws.numel(), _stream()), "tsb200_linear_argmax")
+        return out
+
     @staticmethod
     def device_status(ws=None, device=None):
         """Status word of a workspace (synchronises): 0, or the code of a bounded wait that ran out."""
