@@ -65,7 +65,7 @@ def parse():
                          "or tensor-parallel linears with an NCCL all-reduce (one batch shared by all ranks)")
     ap.add_argument("--tp-allreduce", default="peer", choices=["peer", "nccl"],
                     help="tensor parallel: the library's fused all-reduce + add + RMSNorm over NVLink peer memory, or NCCL")
-    ap.add_argument("--sweep", default=None, choices=["linear", "attention"],
+    ap.add_argument("--sweep", default=None, choices=["linear", "attention", "prefill"],
                     help="op-level sweeps (BASELINE.json configs[1] / configs[2]) instead of the decode step; "
                          "prints one JSON line per case")
     ap.add_argument("--sweep-m", default="1,16,128,2048", help="token counts of the linear sweep")
@@ -467,7 +467,8 @@ def run_ours(a):
         if not a.no_sweeps:
             try:
                 line["sweeps"] = {"linear": sweep_linear(a, ranks=(1024,), precisions=(4,), ms=(1, 128, 2048), copies=4),
-                                  "attention": sweep_attention(a, contexts=(4096,))}
+                                  "attention": sweep_attention(a, contexts=(4096,)),
+                                  "prefill": sweep_prefill(a, cases=[(8, 2048)])}
             except Exception as ex:          # a sweep must not hide the headline
                 line["sweeps"] = {"error": repr(ex)}
         try:
@@ -694,12 +695,47 @@ def sweep_attention(a, contexts=None, formats=("int8", "fp8", "nvfp4")):
     return out
 
 
+def sweep_prefill(a, cases=None):
+    """Prompt attention (tsb200_kv_gather_heads + tsb200_prefill_attn) at the Llama-3-8B layout: 32 query / 8 KV heads,
+    d 128, FP8 pages, whole prompts of T tokens; causal flops 4 B H d T^2 / 2 against the measured bf16 peak."""
+    import torch
+    from transformer_surgeon_b200 import ops
+    dev = torch.device("cuda", torch.cuda.current_device())
+    g = torch.Generator(device=dev).manual_seed(4)
+    H, Hkv, d = 32, 8, 128
+    out = []
+    for B, T in cases or [(a.sweep_batch if a.sweep_batch != 64 else 8, 2048)]:
+        pages = T // 16
+        bt = torch.randperm(B * pages, generator=g, device=dev).to(torch.int32).reshape(B, pages)
+        seq = torch.full((B,), T, dtype=torch.int32, device=dev)
+        kv = ops.PagedKV("fp8", B * pages, Hkv, d, bt, seq, dev)
+        kv.fill_fp8_scales(0.02, 0.02)
+        kv.k_pool.random_(0, 120)
+        kv.v_pool.random_(0, 120)
+        q = torch.randn((B, T, H, d), generator=g, device=dev).bfloat16()
+        o = torch.empty_like(q)
+        ops.prefill_attention(kv, q, T, out=o)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(5):
+            ops.prefill_attention(kv, q, T, out=o)
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / 5
+        flops = 4.0 * B * H * d * T * T / 2
+        out.append({"sweep": "prefill_attention", "batch": B, "tokens": T, "ms": ms, "prompt_tokens_per_s": B * T / (ms * 1e-3),
+                    "tflops": flops / ms / 1e9, "frac_tensor_burst": flops / ms / 1e9 / 1671.9,
+                    "includes": "dequantizing head-major gather + causal attention on tcgen05"})
+    return out
+
+
 if __name__ == "__main__":
     args = parse()
     if args.sweep:
         import torch
         torch.cuda.set_device(0)
-        for rec in (sweep_linear if args.sweep == "linear" else sweep_attention)(args):
+        for rec in {"linear": sweep_linear, "attention": sweep_attention, "prefill": sweep_prefill}[args.sweep](args):
             print(json.dumps(rec))
     elif args.impl == "reference":
         run_reference(args)
