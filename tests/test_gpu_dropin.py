@@ -244,3 +244,81 @@ def test_config5_style_qwen25vl_text_tower_mixed_precision(cuda, reference):
     dec4 = surgeon.decoder_from_model(model, batch=2, options={"max_cache_len": 64, "cache_impl": "paged_nvfp4"})
     _, logits4 = dec4.generate(ids, max_new_tokens=1)
     assert rel(logits4.cpu(), ref_logits) < 2.5e-1
+
+
+def test_gptq_codes_through_capture(cuda, reference):
+    """The reference's GPTQ method (compression/quantization_methods/gptq.py:7-104) yields codes and scales in the
+    same format as `vanilla`; its calibration runs through the manager's own flow (set_calibration_data -> apply).
+    The codes are taken at apply time, packed bit for bit, and logits and 32 greedy tokens equal the reference's."""
+    T = reference
+    from torch.utils.data import DataLoader
+    from transformer_surgeon_b200 import surgeon
+    model, mgr = make(T, "llama", 35)
+    ids = torch.randint(0, 256, (2, 12), generator=torch.Generator().manual_seed(36))
+    mgr.set("lrd", "rank", 16, criteria=["mlp"])
+    mgr.set("quantization", "precision", 4, criteria=["self_attn", "mlp"])
+    mgr.set("quantization", "method", "gptq", criteria=["self_attn", "mlp"])
+    mgr.set("quantization", "granularity", "per_channel", criteria=["self_attn", "mlp"])
+    g = torch.Generator().manual_seed(37)
+    mgr.set_calibration_data(DataLoader([{"input_ids": torch.randint(0, 256, (4, 24), generator=g)} for _ in range(4)], batch_size=None))
+    with surgeon.capture_quantization(model) as cap:
+        mgr.apply(hard=False)
+    assert len(cap.codes) == 2 * (4 + 3 * 2)
+    with torch.no_grad():
+        ref_logits = model(input_ids=ids).logits
+        ref_tokens = greedy(model, ids, 32)
+    model.cuda()
+    surgeon.pack_model(model, cuda)
+    for path, m in linears(T, model):
+        rec = cap.codes.get(path + ".weight")
+        if rec is not None:
+            assert m._tsb200.u.bits == 4
+            assert torch.equal(m._tsb200.u.codes().cpu(), rec[0]) and torch.equal(m._tsb200.u.scales.cpu(), rec[1])
+    with torch.no_grad():
+        out = model(input_ids=ids.cuda()).logits
+    assert rel(out.cpu(), ref_logits) < 1e-4
+    surgeon.unpack_model(model)
+    dec = surgeon.decoder_from_model(model.cpu(), batch=2, options={"max_cache_len": 64, "cache_impl": "paged_fp32"})
+    assert dec.layers[0].o.u.bits == 4 and dec.layers[0].down.v.bits == 4
+    toks, _ = dec.generate(ids, max_new_tokens=32)
+    assert torch.equal(toks.cpu(), ref_tokens)
+
+
+def test_packed_codes_in_the_checkpoint(cuda, reference, tmp_path):
+    """Packed codes as state_dict buffers: they survive manager.prepare_for_save() and save_pretrained, a model
+    built by from_pretrained ignores them, and load_packed_checkpoint attaches the kernels from the file alone -
+    the same containers bit for bit, the same logits bit for bit as the model that was saved."""
+    T = reference
+    from safetensors.torch import load_file
+    from transformer_surgeon_b200 import surgeon
+    model, mgr = make(T, "llama", 38)
+    ids = torch.randint(0, 256, (2, 12), generator=torch.Generator().manual_seed(39))
+    mgr.set("lrd", "rank", 16, criteria=["mlp"])
+    mgr.set("quantization", "precision", 4, criteria=["self_attn"])
+    mgr.set("quantization", "precision", 2, criteria=["mlp"])
+    mgr.set("quantization", "granularity", "per_channel", criteria=["self_attn", "mlp"])
+    with surgeon.capture_quantization(model):
+        mgr.apply(hard=False)
+    model.cuda()
+    n = surgeon.pack_model(model, cuda)
+    with torch.no_grad():
+        out = model(input_ids=ids.cuda()).logits
+    assert surgeon.register_packed_buffers(model) == n
+    mgr.prepare_for_save()                                            # utils/manager.py:843-894
+    keys = [k for k in model.state_dict() if "._tsb200_" in k]
+    assert len(keys) >= 4 * n
+    model.save_pretrained(tmp_path)
+    stored = load_file(str(tmp_path / "model.safetensors"))
+    assert all(k in stored for k in keys)
+    fresh = T.LlamaForCausalLMCompress.from_pretrained(tmp_path).eval().cuda()   # rebuilt from config.compression_config
+    assert not any("._tsb200_" in k for k in fresh.state_dict())
+    assert surgeon.load_packed_checkpoint(fresh, tmp_path, cuda) == n
+    for (pa, a), (pb, b) in zip(linears(T, model), linears(T, fresh)):
+        assert pa == pb and a._tsb200.u.bits == b._tsb200.u.bits
+        assert torch.equal(a._tsb200.u.data, b._tsb200.u.data) and torch.equal(a._tsb200.u.scales, b._tsb200.u.scales)
+        assert (a._tsb200.v is None) == (b._tsb200.v is None)
+    with torch.no_grad():
+        out2 = fresh(input_ids=ids.cuda()).logits
+    assert torch.equal(out2, out)
+    surgeon.unpack_model(model)
+    assert not any("._tsb200_" in k for k in model.state_dict())

@@ -292,7 +292,62 @@ def load_packed_state_dict(model, sd, device="cuda"):
     return n
 
 
+BUFFER_PREFIX = "_tsb200_"
+
+
+def register_packed_buffers(model):
+    """Make the packed codes part of the checkpoint: every tensor of a packed LinearCompressed's state
+    (`PackedLinear.state`) becomes a persistent buffer `_tsb200_<field>` of that module, so it is in
+    `model.state_dict()`, is left alone by `manager.prepare_for_save()` (utils/manager.py:843-894 strips only
+    the Quantizer's own attributes, compression/quantization.py:198-230) and is written by `save_pretrained` /
+    `export_to_hf` (hf/hf_export.py:42-51).  Loading the checkpoint into a freshly built model reports the
+    entries as unexpected keys and ignores them; `load_packed_checkpoint` attaches them.  Returns the number
+    of modules."""
+    n = 0
+    for _, m in model.named_modules():
+        if hasattr(m, "_tsb200"):
+            for k, t in m._tsb200.state("").items():
+                m.register_buffer(BUFFER_PREFIX + k.replace(".", "_"), t.detach().clone(), persistent=True)
+            n += 1
+    return n
+
+
+def remove_packed_buffers(model):
+    for _, m in model.named_modules():
+        for name in [b for b in m._buffers if b.startswith(BUFFER_PREFIX)]:
+            del m._buffers[name]
+
+
+def packed_buffers_to_state(sd):
+    """`<path>._tsb200_u_data`-style keys of a state dict -> the `<path>._tsb200.u.data` keys that
+    `load_packed_state_dict` reads."""
+    out = {}
+    for k, t in sd.items():
+        path, _, name = k.rpartition(".")
+        if not name.startswith(BUFFER_PREFIX):
+            continue
+        field = name[len(BUFFER_PREFIX):]
+        for head in ("u_", "v_"):
+            if field.startswith(head):
+                field = head[0] + "." + field[2:]
+        out[path + PACKED_KEY + field] = t
+    return out
+
+
+def load_packed_checkpoint(model, directory, device="cuda"):
+    """Attach kernels to `model` (built by `from_pretrained(directory)`) from the packed buffers stored in the
+    checkpoint's safetensors files: no pack step, no re-quantization.  Returns the number of modules attached."""
+    import glob
+    import os
+    from safetensors.torch import load_file
+    sd = {}
+    for f in sorted(glob.glob(os.path.join(directory, "*.safetensors"))):
+        sd.update({k: t for k, t in load_file(f).items() if ("." + BUFFER_PREFIX) in k})
+    return load_packed_state_dict(model, packed_buffers_to_state(sd), device)
+
+
 def unpack_model(model):
+    remove_packed_buffers(model)
     for _, m in model.named_modules():
         if hasattr(m, "_tsb200"):
             del m._tsb200
