@@ -25,8 +25,10 @@
 //     scale, bias, store;
 //   * split-K: every item stores its fp32 partial tile in a private slice of the workspace (plain
 //     stores, no zero-fill needed).  When each CTA holds one item of the phase, the CTAs of a tile
-//     meet at the tile's counter and each sums its share of the token columns; otherwise the last
-//     CTA to finish a tile sums all of it.  Slices are added in split order: a deterministic result;
+//     meet at the tile's counter (one device-scope fence by the signalling thread, acquire polling)
+//     and each sums its share of the token columns with all its slice loads in flight at once;
+//     otherwise the last CTA to finish a tile sums all of it.  Slices are added in split order: a
+//     deterministic result;
 //   * a launch executes a PROGRAM of up to 4 phases separated by grid-wide barriers (all CTAs are
 //     co-resident: grid <= #SMs, one CTA per SM, cooperative launch): the V and U factors of a
 //     low-rank layer, or the whole gated MLP (gate|up V, gate|up U with SiLU(g)*u in the epilogue,
@@ -34,6 +36,7 @@
 //     dequant warps already fill both A buffers of the next phase while the barrier is pending.
 // Every mbarrier / grid-barrier wait is bounded (see tc_common.cuh); on expiry the CTA records a
 // code in the status word, drains, frees its TMEM and returns.
+#include <type_traits>
 #include "tc_common.cuh"
 
 namespace tsb {
@@ -264,20 +267,6 @@ linear_tcq_kernel(const __grid_constant__ Program prog) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   pdl_launch_dependents();
 
-  if (threadIdx.x == 0) {
-    for (int i = 0; i < NR; ++i) { mbar_init(&w_full[i], 1); mbar_init(&x_full[i], 1 + kDqWarps); mbar_init(&stage_done[i], L::kSplitStage ? 2 : 1); }
-    mbar_init(acc_full, 2);                                 // both issuers commit, with or without MMAs of their own
-    mbar_init(ep_bar, kDqWarps);
-    *abort_flag = 0;
-    *last_flag = 0;
-    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
-  }
-  if (warp == 1) tmem_alloc(tmem_slot, kTmemCols);
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const unsigned tmem_base = *tmem_slot;
-
   // Work enumeration, identical in every role.  Phase -> items (round-robin over CTAs) -> passes
   // (one per matrix the item touches: 2 for a gated item) -> stages of KBS k-blocks.
   struct Item { int sub, nt, mt, kb0, nkb, ns; };        // ns = stages of the item's K range
@@ -295,6 +284,33 @@ linear_tcq_kernel(const __grid_constant__ Program prog) {
     it.ns = (it.nkb + KBS - 1) / KBS;
     return it;
   };
+
+  int pre_w = 0;                                            // weight boxes issued during the set-up (thread 0)
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < NR; ++i) { mbar_init(&w_full[i], 1); mbar_init(&x_full[i], 1 + kDqWarps); mbar_init(&stage_done[i], L::kSplitStage ? 2 : 1); }
+    mbar_init(acc_full, 2);                                 // both issuers commit, with or without MMAs of their own
+    mbar_init(ep_bar, kDqWarps);
+    *abort_flag = 0;
+    *last_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    // The first weight boxes of this CTA (first item of phase 0, first pass) leave NOW, before the tensor-memory
+    // allocation and the CTA-wide barrier: their latency (cold translation, tensor-map fetch, DRAM: about 2 us) is the
+    // head of every launch's critical path.  This thread is the weight producer: its loop below skips them.
+    const Phase& ph0 = prog.ph[0];
+    if ((int)blockIdx.x < ph0.items) {
+      const Item it = decode(ph0, blockIdx.x);
+      const SubGemm& sg = ph0.sub[ph0.gated ? 0 : it.sub];
+      for (; pre_w < it.ns && pre_w < NR; ++pre_w) {
+        mbar_expect_tx(&w_full[pre_w], (unsigned)L::kRaw);
+        tma_load_2d(r_ring + pre_w * L::kStage + L::kX, &sg.map_w, (it.kb0 + pre_w * KBS) * (BK * BITS / 8), it.nt * BM, &w_full[pre_w]);
+      }
+    }
+  }
+  if (warp == 1) tmem_alloc(tmem_slot, kTmemCols);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const unsigned tmem_base = *tmem_slot;
 
   if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer: packed weights
@@ -318,6 +334,7 @@ linear_tcq_kernel(const __grid_constant__ Program prog) {
 #pragma unroll 1
             for (int jj = 0; jj < it.ns; ++jj, ++gs) {
               const int s = gs % NR, kb = it.kb0 + jj * KBS;
+              if (gs < pre_w) continue;                        // issued during the set-up
               // the stage is free once its previous user's MMAs are complete
               if (gs >= NR && !mbar_wait(&stage_done[s], ((gs / NR) - 1) & 1, abort_flag, 1)) { ok = false; break; }
               mbar_expect_tx(&w_full[s], (unsigned)L::kRaw);
@@ -440,13 +457,24 @@ linear_tcq_kernel(const __grid_constant__ Program prog) {
             const int i = jj * KBS;
             const int s = gs % NR, buf = gs % L::NBUF;
             ok = mbar_wait_relaxed(&w_full[s], (gs / NR) & 1, abort_flag, 4);
+#ifdef TSB_ALT
+            const bool whole = it.ns >= 2;
+            if (whole && (gs & 1) != grp) {                    // the other group's stage: only keep the arrival count
+              if (!ok) break;
+              __syncwarp();
+              if (lane == 0) mbar_arrive(&x_full[s]);
+              continue;
+            }
+#else
+            const bool whole = false;
+#endif
             // the A buffer is free once the MMAs of the stage NBUF back are complete
             if (ok && gs >= L::NBUF) ok = mbar_wait_relaxed(&stage_done[(gs - L::NBUF) % NR], ((gs - L::NBUF) / NR) & 1, abort_flag, 5);
             if (!ok) break;
             tc_fence_after();
             const unsigned raw = smem_u32(r_ring + s * L::kStage + L::kX);
             const int nsub = min(KBS, it.nkb - i);
-            for (int j = grp; j < nsub; j += 2) {              // both groups work on the stage: half the latency
+            for (int j = whole ? 0 : grp; j < nsub; j += whole ? 1 : 2) {
               unsigned regs[32];
               dequant_row_regs<BITS, L::kRawStageRow>(raw, row, j, regs);
               tmem_st32(lane_addr + L::kACol0 + buf * 128 + j * 32, regs);
@@ -531,39 +559,59 @@ linear_tcq_kernel(const __grid_constant__ Program prog) {
         if (split && ph.scatter) {
           // The CTAs of this (matrix, n tile, m tile) meet at the tile's counter; CTA `sp` then sums token
           // columns sp, sp + splits, ... over all slices in split order (the order the single-finalizer
-          // path uses), with every load of a column in flight at once.  The counter counts arrivals, then
-          // departures; the last CTA to leave resets it.
+          // path uses), with every load of a column in flight at once.
           int* ctr = &ph.counters[(it.sub * ph.m_tiles + it.mt) * ph.n_tiles + it.nt];
-          __threadfence();
-          if (!(ok = warps_rendezvous(ep_bar, ep_uses, lane, abort_flag))) break;
           if (threadIdx.x == 64) {
+            // one device-scope fence by the signalling thread: the slice stores of the other epilogue threads are
+            // ordered before it by the rendezvous above, and the fence is cumulative
+            __threadfence();
             atomicAdd(ctr, 1);
-            grid_wait(ctr, ph.splits, abort_flag);             // failure raises the abort flag
+            grid_wait(ctr, ph.splits, abort_flag);             // acquire loads; failure raises the abort flag
+            // departure: the counter counts `splits` arrivals, then `splits` departures, and the last departure wraps
+            // it to 0 for the next launch (a CTA departs only after it has seen every arrival; nothing waits for the
+            // departures, and the increment returns nothing, so neither does this thread)
+            atomicInc(reinterpret_cast<unsigned*>(ctr), 2u * (unsigned)ph.splits - 1u);
           }
           if (!(ok = warps_rendezvous(ep_bar, ep_uses, lane, abort_flag))) break;
           if (*abort_flag) { ok = false; break; }
-          __threadfence();
+          // the slices are read with L2 loads (ld.global.cg) after that acquire and the rendezvous: no further fence
           const int sp = item % ph.splits;
           if (n < ph.N) {
             const float* tile0 = ph.partial + (size_t)(item - sp) * (TN * BM) + row;
-            for (int c = sp + grp * ph.splits; c < TN; c += 2 * ph.splits) {
-              const int64_t m = m0 + c;
-              if (m >= prog.M) break;
-              float v = 0.f;
-              for (int s0 = 0; s0 < ph.splits; s0 += 8) {
-                float a[8];
+            // all of this thread's columns and slices in flight at once (up to 8 x 4 or 4 x 8 loads): one round trip
+            // to the L2 instead of one per column.  A column's slices are added in split order.
+            const int cstep = 2 * ph.splits;
+            auto batch = [&](auto cb_c, auto sb_c) {
+              constexpr int CB = decltype(cb_c)::value, SB = decltype(sb_c)::value;
+              for (int cb = sp + grp * ph.splits; cb < TN; cb += CB * cstep) {
+                float v[CB];
 #pragma unroll
-                for (int u = 0; u < 8; ++u)
-                  if (s0 + u < ph.splits) a[u] = __ldcg(tile0 + (size_t)(s0 + u) * (TN * BM) + c * BM);
+                for (int u = 0; u < CB; ++u) v[u] = 0.f;
+                for (int s0 = 0; s0 < ph.splits; s0 += SB) {
+                  float a[CB][SB];
 #pragma unroll
-                for (int u = 0; u < 8; ++u)
-                  if (s0 + u < ph.splits) v += a[u];
+                  for (int u = 0; u < CB; ++u)
+#pragma unroll
+                    for (int t = 0; t < SB; ++t)
+                      a[u][t] = (cb + u * cstep < TN && s0 + t < ph.splits)
+                                    ? __ldcg(tile0 + (size_t)(s0 + t) * (TN * BM) + (cb + u * cstep) * BM) : 0.f;
+#pragma unroll
+                  for (int u = 0; u < CB; ++u)
+#pragma unroll
+                    for (int t = 0; t < SB; ++t)
+                      if (s0 + t < ph.splits) v[u] += a[u][t];
+                }
+#pragma unroll
+                for (int u = 0; u < CB; ++u) {
+                  const int c = cb + u * cstep;
+                  const int64_t m = m0 + c;
+                  if (c < TN && m < prog.M) y[m * ph.N + n] = __float2bfloat16_rn(v[u] * sc0 + bv0);
+                }
               }
-              y[m * ph.N + n] = __float2bfloat16_rn(v * sc0 + bv0);
-            }
+            };
+            if (ph.splits <= 4) batch(std::integral_constant<int, 8>{}, std::integral_constant<int, 4>{});
+            else batch(std::integral_constant<int, 4>{}, std::integral_constant<int, 8>{});
           }
-          if (!(ok = warps_rendezvous(ep_bar, ep_uses, lane, abort_flag))) break;   // this CTA's slice reads are done
-          if (threadIdx.x == 64 && atomicAdd(ctr, 1) == 2 * ph.splits - 1) *ctr = 0;
         } else if (split) {
           // last CTA of this (matrix, n tile, m tile) finalizes: sum of the slices -> y, then resets the counter
           int* ctr = &ph.counters[(it.sub * ph.m_tiles + it.mt) * ph.n_tiles + it.nt];
