@@ -457,24 +457,13 @@ linear_tcq_kernel(const __grid_constant__ Program prog) {
             const int i = jj * KBS;
             const int s = gs % NR, buf = gs % L::NBUF;
             ok = mbar_wait_relaxed(&w_full[s], (gs / NR) & 1, abort_flag, 4);
-#ifdef TSB_ALT
-            const bool whole = it.ns >= 2;
-            if (whole && (gs & 1) != grp) {                    // the other group's stage: only keep the arrival count
-              if (!ok) break;
-              __syncwarp();
-              if (lane == 0) mbar_arrive(&x_full[s]);
-              continue;
-            }
-#else
-            const bool whole = false;
-#endif
             // the A buffer is free once the MMAs of the stage NBUF back are complete
             if (ok && gs >= L::NBUF) ok = mbar_wait_relaxed(&stage_done[(gs - L::NBUF) % NR], ((gs - L::NBUF) / NR) & 1, abort_flag, 5);
             if (!ok) break;
             tc_fence_after();
             const unsigned raw = smem_u32(r_ring + s * L::kStage + L::kX);
             const int nsub = min(KBS, it.nkb - i);
-            for (int j = whole ? 0 : grp; j < nsub; j += whole ? 1 : 2) {
+            for (int j = grp; j < nsub; j += 2) {              // both groups work on the stage: half the latency
               unsigned regs[32];
               dequant_row_regs<BITS, L::kRawStageRow>(raw, row, j, regs);
               tmem_st32(lane_addr + L::kACol0 + buf * 128 + j * 32, regs);
