@@ -176,6 +176,10 @@ __device__ __forceinline__ void tmem_ld8(unsigned taddr, unsigned (&r)[8]) {
                : "r"(taddr)
                : "memory");
 }
+template <int W> __device__ __forceinline__ void tmem_ldw(unsigned taddr, unsigned (&r)[W]) {
+  if constexpr (W == 16) tmem_ld16(taddr, r);
+  else tmem_ld8(taddr, r);
+}
 // D[tmem] (+)= A[tmem] . B[smem descriptor]; kind::f16, A K-major in tensor memory.
 __device__ __forceinline__ void umma_bf16_ts(unsigned d_tmem, unsigned a_tmem, unsigned long long bdesc, unsigned idesc,
                                              unsigned accumulate) {
@@ -243,7 +247,10 @@ __device__ __forceinline__ bool grid_wait(const int* ctr, int target, volatile i
 }
 
 template <int TN, int BITS>
-__global__ void __launch_bounds__(kThreadsQ, 1)
+// 128 registers (not the 168 a 384-thread CTA could have): the CTA of a launch then fits beside the CTAs of the small
+// kernel before it, so its set-up and first weight copies run under programmatic dependent launch while that kernel
+// still executes.  With 168 registers the decode step was 4 % slower although this kernel alone was faster.
+__global__ void __maxnreg__(128)
 linear_tcq_kernel(const __grid_constant__ Program prog) {
   using L = QLayout<TN, BITS>;
   constexpr int NR = L::NR;
@@ -493,52 +500,53 @@ linear_tcq_kernel(const __grid_constant__ Program prog) {
         const unsigned acc1 = (unsigned)((ph.gated ? 2 : 1) * TN);   // column offset of chain 1
         float* slice = ph.partial + (size_t)item * (TN * BM);
         __nv_bfloat16* y = sg0.y;
+        // W columns per step, the tensor-memory loads of both chains issued before one wait (a tcgen05.ld costs its
+        // warp ~115 cycles to issue whatever its width, so few wide loads, not many narrow ones); a gated item first
+        // turns the gate columns into SiLU(g), then fetches the up columns into the freed registers
+        constexpr int W = CH >= 16 ? 16 : 8;
 #pragma unroll 1
-        for (int c0 = grp * CH; c0 < (grp + 1) * CH; c0 += 8) {
-          unsigned r[8];
-          tmem_ld8(lane_addr + (v0 ? 0u : acc1) + (unsigned)c0, r);
+        for (int c0 = grp * CH; c0 < (grp + 1) * CH; c0 += W) {
+          unsigned r[W], t[W];
+          tmem_ldw<W>(lane_addr + (v0 ? 0u : acc1) + (unsigned)c0, r);
+          if (v0 && v1) tmem_ldw<W>(lane_addr + acc1 + (unsigned)c0, t);
+          tmem_ld_wait();
           if (v0 && v1) {
-            unsigned t[8];
-            tmem_ld8(lane_addr + acc1 + (unsigned)c0, t);
-            tmem_ld_wait();
 #pragma unroll
-            for (int j = 0; j < 8; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) + __uint_as_float(t[j]));
+            for (int j = 0; j < W; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) + __uint_as_float(t[j]));
           }
           if (ph.gated) {
-            unsigned r2[8];
-            tmem_ld8(lane_addr + (u0 ? 0u : acc1) + (unsigned)(TN + c0), r2);
-            if (u0 && u1) {
-              unsigned t[8];
-              tmem_ld8(lane_addr + acc1 + (unsigned)(TN + c0), t);
-              tmem_ld_wait();
+            // same rounding points as separate gate / up / SiLU*up kernels (blocks/mlp.py:181-183)
 #pragma unroll
-              for (int j = 0; j < 8; ++j) r2[j] = __float_as_uint(__uint_as_float(r2[j]) + __uint_as_float(t[j]));
+            for (int j = 0; j < W; ++j) {
+              const float g = __bfloat162float(__float2bfloat16_rn(__uint_as_float(r[j]) * sc0 + bv0));
+              r[j] = __float_as_uint(__bfloat162float(__float2bfloat16_rn(__fdividef(g, 1.0f + __expf(-g)))));
             }
+            tmem_ldw<W>(lane_addr + (u0 ? 0u : acc1) + (unsigned)(TN + c0), t);
+            unsigned t2[W];
+            if (u0 && u1) tmem_ldw<W>(lane_addr + acc1 + (unsigned)(TN + c0), t2);
             tmem_ld_wait();
+            if (u0 && u1) {
+#pragma unroll
+              for (int j = 0; j < W; ++j) t[j] = __float_as_uint(__uint_as_float(t[j]) + __uint_as_float(t2[j]));
+            }
             if (n < ph.N) {
 #pragma unroll
-              for (int j = 0; j < 8; ++j) {
+              for (int j = 0; j < W; ++j) {
                 const int64_t m = m0 + c0 + j;
                 if (m < prog.M) {
-                  // same rounding points as separate gate / up / SiLU*up kernels (blocks/mlp.py:181-183)
-                  const float g = __bfloat162float(__float2bfloat16_rn(__uint_as_float(r[j]) * sc0 + bv0));
-                  const float u = __bfloat162float(__float2bfloat16_rn(__uint_as_float(r2[j]) * sc1 + bv1));
-                  const float a = __bfloat162float(__float2bfloat16_rn(__fdividef(g, 1.0f + __expf(-g))));
-                  y[m * ph.N + n] = __float2bfloat16_rn(__fmul_rn(a, u));
+                  const float u = __bfloat162float(__float2bfloat16_rn(__uint_as_float(t[j]) * sc1 + bv1));
+                  y[m * ph.N + n] = __float2bfloat16_rn(__fmul_rn(__uint_as_float(r[j]), u));
                 }
               }
             }
-          } else {
-            tmem_ld_wait();
-            if (split) {
+          } else if (split) {
 #pragma unroll
-              for (int j = 0; j < 8; ++j) __stcg(&slice[(c0 + j) * BM + row], __uint_as_float(r[j]));
-            } else if (n < ph.N) {
+            for (int j = 0; j < W; ++j) __stcg(&slice[(c0 + j) * BM + row], __uint_as_float(r[j]));
+          } else if (n < ph.N) {
 #pragma unroll
-              for (int j = 0; j < 8; ++j) {
-                const int64_t m = m0 + c0 + j;
-                if (m < prog.M) y[m * ph.N + n] = __float2bfloat16_rn(__uint_as_float(r[j]) * sc0 + bv0);
-              }
+            for (int j = 0; j < W; ++j) {
+              const int64_t m = m0 + c0 + j;
+              if (m < prog.M) y[m * ph.N + n] = __float2bfloat16_rn(__uint_as_float(r[j]) * sc0 + bv0);
             }
           }
         }
@@ -567,7 +575,7 @@ linear_tcq_kernel(const __grid_constant__ Program prog) {
           const int sp = item % ph.splits;
           if (n < ph.N) {
             const float* tile0 = ph.partial + (size_t)(item - sp) * (TN * BM) + row;
-            // all of this thread's columns and slices in flight at once (up to 8 x 4 or 4 x 8 loads): one round trip
+            // all of this thread's columns and slices in flight at once (up to 8 x 4, 4 x 8 or 2 x 16 loads): one round trip
             // to the L2 instead of one per column.  A column's slices are added in split order.
             const int cstep = 2 * ph.splits;
             auto batch = [&](auto cb_c, auto sb_c) {
@@ -599,7 +607,8 @@ linear_tcq_kernel(const __grid_constant__ Program prog) {
               }
             };
             if (ph.splits <= 4) batch(std::integral_constant<int, 8>{}, std::integral_constant<int, 4>{});
-            else batch(std::integral_constant<int, 4>{}, std::integral_constant<int, 8>{});
+            else if (ph.splits <= 8) batch(std::integral_constant<int, 4>{}, std::integral_constant<int, 8>{});
+            else batch(std::integral_constant<int, 2>{}, std::integral_constant<int, 16>{});
           }
         } else if (split) {
           // last CTA of this (matrix, n tile, m tile) finalizes: sum of the slices -> y, then resets the counter
