@@ -74,7 +74,7 @@ def test_static_scratch_rejects_oversized_problem(cuda):
     ops, kv, q, L = _setup(cuda, "fp8", 3)
     cap = lib.tsb200_paged_decode_attn_static_capacity()
     assert cap == 8 << 20
-    B, H, d = 64, 32, 128
+    B, H, d = 128, 32, 128                   # 5 splits x 128 x 32 heads x 130 floats = 10.6 MB of partials
     assert lib.tsb200_paged_decode_attn_workspace_bytes(B, H, d, 32768) > cap
     qbig = torch.zeros((B, H, d), dtype=torch.bfloat16, device=cuda)
     desc = kv.desc()

@@ -20,6 +20,9 @@ inline int choose_splits(int64_t B, int hkv, int64_t max_seq_len) {
   const int64_t base = B * hkv;
   const int64_t pages = (max_seq_len + 15) / 16;
   int64_t s = (148 * 8 + base - 1) / (base > 0 ? base : 1);
+  // few (sequence, kv head) pairs, long contexts: about 768 CTAs measured fastest (8 sequences x 4 kv heads x 32k
+  // tokens, NVFP4 pages: 24 splits 99 us, 37 splits 115 us, 13 splits 128 us)
+  if (base > 0 && base < 148) s = (768 + base - 1) / base;
   const int64_t cap = pages / 4 > 0 ? pages / 4 : 1;   // at least 4 pages per split
   if (s > cap) s = cap;
   if (s < 1) s = 1;
