@@ -1,6 +1,6 @@
 """Install the UNMODIFIED reference (CESOIA/transformer-surgeon) under oracle/_ref/ (TEST INFRASTRUCTURE).
 
-    python oracle/make_ref.py [<reference checkout>]        default: $TSB200_REFERENCE or /root/reference
+    python oracle/make_ref.py [<reference checkout>]        default: $TSB200_REFERENCE, else a `reference` directory beside this repository
 
 oracle/_ref/ is git-ignored (no reference source enters the history) but ships with the working tree to
 the GPU machine, like the built shared library.  The reference is pure Python, so "installing" it means
@@ -41,7 +41,7 @@ def import_reference():
 
 
 def make(src=None, force=False):
-    src = src or os.environ.get("TSB200_REFERENCE", "/root/reference")
+    src = src or os.environ.get("TSB200_REFERENCE") or os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
     if not os.path.isfile(os.path.join(src, PKG, "__init__.py")):
         raise FileNotFoundError(f"{src} holds no `{PKG}` package")
     if ref_path() and not force:
