@@ -269,7 +269,11 @@ int tsb200_prefill_attn(const void* q, int64_t q_token_stride, const void* k, co
  * status word: zero-fill them ONCE before the first use; every completed call leaves the counters zero.
  * The status word becomes non-zero when a kernel gave up on a bounded wait for its own copies (the output
  * of that call is then not to be trusted); the caller reads and clears it.  One workspace must not serve
- * overlapping calls. */
+ * overlapping calls.
+ * Arithmetic: scores and outputs accumulate in fp32.  The tensor-core kernels feed q and the softmax weights to the
+ * MMA as f16 (int8 / NVFP4 pages) or as the sum of three e4m3 terms (FP8 pages, d = 128, <= 4 query heads per kv
+ * head): about 11-12 significant bits either way, also when q and out are fp32.  Unquantized pages are attended in
+ * fp32 throughout (tsb200_paged_decode_attn_simt, which accepts every format). */
 size_t tsb200_paged_decode_attn_workspace_bytes(int64_t B, int H, int head_dim, int64_t max_seq_len);
 int tsb200_paged_decode_attn(const tsb200_kv_desc* kv, const void* q, void* out, int dtype,
                              int64_t q_batch_stride, int64_t B, int H, float sm_scale, int64_t max_seq_len,
