@@ -47,13 +47,13 @@ constexpr int kDqWarps = 8;                 // two groups of four
 constexpr int kThreadsQ = 64 + kDqWarps * 32 + 64;   // weight producer, MMA issuer 0, 8 dequant warps, MMA issuer 1, activation producer
 constexpr int kIssuer1Warp = 2 + kDqWarps;
 constexpr int kXWarp = 3 + kDqWarps;
-constexpr int kSmemBudget = 208 * 1024;
+constexpr int kSmemBudget = 216 * 1024;     // three 72 KB stages of the 256-token tile (int4), six 32 KB stages of the decode tiles
 constexpr unsigned kTmemCols = 512;
 
 template <int TN, int BITS> struct QLayout {
   static constexpr int kKbsFull = 1024 / BITS / BK;        // k-blocks in a 128-byte row of codes
-  // A buffer = KBS * 32 TMEM columns <= 128; the 256-token tile keeps one k-block (32 KB of activations) per stage
-  static constexpr int kKbsCap = (TN <= 32 || TN == 128) ? 4 : (TN <= 128 ? 2 : 1);
+  // A buffer = KBS * 32 TMEM columns <= 128; 64- and 256-token tiles keep two k-blocks per stage (16 / 64 KB of activations)
+  static constexpr int kKbsCap = (TN <= 32 || TN == 128) ? 4 : 2;
   // A buffers of 128 TMEM columns above the accumulators.  Token tiles up to 32 need at most 4 x 32 accumulator
   // columns (two chains, gate and up), which leaves room for THREE buffers: the dequant warps may then run two
   // stages ahead of the MMAs instead of one, and the chain "dequantize -> MMAs -> buffer free" no longer sets the
@@ -410,7 +410,13 @@ linear_tcq_kernel(const __grid_constant__ Program prog) {
             const unsigned d_tmem = tmem_base + (unsigned)((ph.gated ? 2 * (two ? me : 0) + ps : (two ? me : 0)) * TN);
             bool first = true;                                // the chain's first MMA of the pass overwrites
             for (int jj = 0; jj < it.ns; ++jj, ++gs) {
-              if (!L::kSplitStage && (two ? (gs & 1) != me : me != 0)) continue;     // the other lane's stage
+              if (!L::kSplitStage && (two ? (gs & 1) != me : me != 0)) {            // the other lane's stage
+                // a lane without any stage in this pass (single chain) still commits the item below: it follows the
+                // stages one by one (a parity wait is only meaningful in order), so that its arrival cannot fall into
+                // the previous item's phase of the accumulator barrier
+                if (!two) ok = mbar_wait(&x_full[gs % NR], (gs / NR) & 1, abort_flag, 2);
+                continue;
+              }
               const int i = jj * KBS;
               const int s = gs % NR, buf = gs % L::NBUF;
               ok = mbar_wait(&x_full[s], (gs / NR) & 1, abort_flag, 2);
@@ -756,7 +762,7 @@ int launch_q_bits(int bits, const Program& prog, int grid, bool coresident, cuda
 // Inner extent (bytes) of the weight box: must equal QLayout<TN, BITS>::kRawStageRow.
 int raw_box_bytes(int tn, int bits) {
   const int full = 1024 / bits / BK;
-  const int cap = (tn <= 32 || tn == 128) ? 4 : (tn <= 128 ? 2 : 1);
+  const int cap = (tn <= 32 || tn == 128) ? 4 : 2;
   const int kbs = full < cap ? full : cap;
   return kbs * BK * bits / 8;
 }
@@ -854,6 +860,7 @@ int run_program_tcq(const PhaseSpec* specs, int n_phases, int bits, int64_t M, u
     case 16: return launch_q_bits<16>(bits, prog, grid, coresident, s);
     case 32: return launch_q_bits<32>(bits, prog, grid, coresident, s);
     case 64: return launch_q_bits<64>(bits, prog, grid, coresident, s);
+    case 256: return launch_q_bits<256>(bits, prog, grid, coresident, s);
     default: return launch_q_bits<128>(bits, prog, grid, coresident, s);
   }
 }

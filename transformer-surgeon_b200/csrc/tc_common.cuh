@@ -32,9 +32,10 @@ struct GemmPlan {
 // of a weight box stays a multiple of 16); a larger alignment never needs more slices than kb_align = 1.
 inline GemmPlan plan_gemm(int64_t M, int64_t N, int64_t K, int nsub = 1, bool no_split = false, int kb_align = 1) {
   GemmPlan g;
-  // a 256-token tile (one k-block per stage) measured slower than 128 at M = 2048 (408 vs 460 TFLOP/s): both
-  // are bound by the activation tiles every 128-row weight tile re-reads from L2, not by the MMA shape
-  g.tn = M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : 128));
+  // above 128 tokens a 256-token tile with two k-blocks per stage: every widened weight tile then meets twice as many
+  // tokens, and one M128 x N256 x K16 MMA (128 cycles of the tensor pipe) outlasts the ~115 cycles its lane needs to
+  // issue it (M = 2048, rank 1024, int4: 524 -> 566 TFLOP/s; with one k-block per stage it was slower than 128)
+  g.tn = M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : (M <= 128 ? 128 : 256)));
   g.kb_total = (int)((K + BK - 1) / BK);
   const int64_t n_tiles = (N + BM - 1) / BM, m_tiles = (M + g.tn - 1) / g.tn;
   const int64_t base = n_tiles * m_tiles * nsub;
