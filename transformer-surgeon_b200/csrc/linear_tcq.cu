@@ -66,11 +66,18 @@ template <int TN, int BITS> struct QLayout {
   static constexpr int kRaw = BM * kRawStageRow;
   static constexpr int kXTile = TN * 128;
   static constexpr int kX = KBS * kXTile;
+  static constexpr int kXRows = TN >= 128 ? 128 : TN;      // tokens per activation box
+  static constexpr int kXPieces = TN / kXRows;             // boxes per k-block
+  static constexpr int kXLanes = KBS * kXPieces;           // lanes that issue a stage's activation boxes together
   static constexpr int kStage = kX + kRaw;                 // multiple of 1024
   static constexpr int kNRraw = kSmemBudget / kStage;
   static constexpr int NR = kNRraw > 12 ? 12 : kNRraw;
   static constexpr int kBarBytes = 1024;
-  static constexpr int kBytes = NR * kStage + kBarBytes + 1024;
+  // Token tiles of 128 and more transpose their outputs through shared memory (16 tokens x 128 rows of bf16 per dequant
+  // group), so that a token's 128 outputs leave as 16-byte stores of whole 256-byte runs instead of 2-byte stores
+  static constexpr int kOutStage = TN >= 128 ? 2 * 16 * BM * 2 : 0;
+  static constexpr int kBytes = NR * kStage + kBarBytes + kOutStage + 1024;
+  static_assert(kBytes <= 227 * 1024, "shared memory of one CTA");
   // The tensor pipe needs ~55 + N/2 cycles per tcgen05.mma (the A operand is read from tensor memory), and
   // the lane that issues them spends another ~300-400 cycles per stage between its last MMA and the next
   // stage's first (commit, wait, descriptors) during which the pipe would idle.  Two lanes of different warps
@@ -200,6 +207,27 @@ __device__ __forceinline__ bool warps_rendezvous(unsigned long long* bar, int& u
   return ok;
 }
 
+// CNT token columns of a dequant group (4 warps, 128 weight rows) -> y, transposed through the group's staging tile
+// [CNT][128] bf16: thread `row` deposits its CNT values, the group meets, then every thread moves 16-byte pieces (8
+// consecutive rows of one token).  Slot j holds token column c_first + j * c_stride of the tile; columns beyond the tile
+// or beyond M and row pieces beyond N (a multiple of 8) are skipped.  The group meets again before the tile is reused.
+template <int CNT, int TN>
+__device__ __forceinline__ bool store_transposed(const float (&v)[CNT], __nv_bfloat16* sb, int row, __nv_bfloat16* y, int64_t N, int64_t M,
+                                                 int64_t n_tile0, int64_t m0, int c_first, int c_stride, unsigned long long* bar,
+                                                 int& uses, int lane, volatile int* abort_flag) {
+#pragma unroll
+  for (int j = 0; j < CNT; ++j) sb[j * BM + row] = __float2bfloat16_rn(v[j]);
+  if (!warps_rendezvous(bar, uses, lane, abort_flag)) return false;
+#pragma unroll
+  for (int p = row; p < CNT * 16; p += BM) {
+    const int slot = p >> 4, part = p & 15;
+    const int c = c_first + slot * c_stride;
+    const int64_t m = m0 + c, nn = n_tile0 + part * 8;
+    if (c < TN && m < M && nn < N) *reinterpret_cast<uint4*>(y + m * N + nn) = *reinterpret_cast<const uint4*>(sb + slot * BM + part * 8);
+  }
+  return warps_rendezvous(bar, uses, lane, abort_flag);
+}
+
 
 constexpr int kMaxPhases = 4;
 
@@ -267,7 +295,8 @@ linear_tcq_kernel(const __grid_constant__ Program prog) {
                                                             //      weight box, activation tiles and A buffer are free
   unsigned long long* acc_full = bars + 3 * NR;             // [1]  MMA commit: accumulator(s) of the item complete
   unsigned long long* ep_bar = acc_full + 1;                // [1]  rendezvous of the 8 warps
-  unsigned* tmem_slot = reinterpret_cast<unsigned*>(ep_bar + 1);
+  unsigned long long* grp_bar = ep_bar + 1;                 // [2]  rendezvous of one dequant group's 4 warps
+  unsigned* tmem_slot = reinterpret_cast<unsigned*>(grp_bar + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   volatile int* last_flag = abort_flag + 1;
 
@@ -297,6 +326,8 @@ linear_tcq_kernel(const __grid_constant__ Program prog) {
     for (int i = 0; i < NR; ++i) { mbar_init(&w_full[i], 1); mbar_init(&x_full[i], 1 + kDqWarps); mbar_init(&stage_done[i], L::kSplitStage ? 2 : 1); }
     mbar_init(acc_full, 2);                                 // both issuers commit, with or without MMAs of their own
     mbar_init(ep_bar, kDqWarps);
+    mbar_init(&grp_bar[0], kDqWarps / 2);
+    mbar_init(&grp_bar[1], kDqWarps / 2);
     *abort_flag = 0;
     *last_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
@@ -355,38 +386,94 @@ linear_tcq_kernel(const __grid_constant__ Program prog) {
     // ---------------------------------------------------------------- TMA producer: activations
     // Same stage sequence; a phase's activations exist once the preceding kernel (phase 0) or the previous phase
     // (grid barrier) has produced them.
-    if (lane == 0) {
-      bool ok = true;
-      int gs = 0;
-#pragma unroll 1
-      for (int p = 0; p < prog.n_phases && ok; ++p) {
-        const Phase& ph = prog.ph[p];
-        for (int j = 0; j < ph.nsub; ++j) asm volatile("prefetch.tensormap [%0];\n" ::"l"(&ph.sub[j].map_x) : "memory");
-        if (p == 0) {
-          pdl_wait();
-        } else {
-          ok = grid_wait(&prog.grid_bar[p - 1], (int)gridDim.x, abort_flag);
-          asm volatile("fence.proxy.async;\n" ::: "memory");  // other CTAs' stores -> visible to the copy engine
+    // One lane issues ~23 bytes per cycle whatever the box (measured, data resident in L2), lanes of one warp that
+    // execute the copy instruction together issue side by side (4 lanes: 71 bytes per cycle).  Token tiles of 128 and
+    // more therefore fetch a stage as kXLanes boxes of 128 tokens x one k-block from as many lanes; the waits stay
+    // with lane 0 and their outcome is broadcast, so the warp runs the loop convergently.
+    if constexpr (TN >= 128) {
+        bool ok = true;
+        int gs = 0;
+  #pragma unroll 1
+        for (int p = 0; p < prog.n_phases && ok; ++p) {
+          const Phase& ph = prog.ph[p];
+          if (lane == 0)
+            for (int j = 0; j < ph.nsub; ++j) asm volatile("prefetch.tensormap [%0];\n" ::"l"(&ph.sub[j].map_x) : "memory");
+          if (p == 0) {
+            pdl_wait();
+          } else {
+            if (lane == 0) ok = grid_wait(&prog.grid_bar[p - 1], (int)gridDim.x, abort_flag);
+            ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
+            asm volatile("fence.proxy.async;\n" ::: "memory");  // other CTAs' stores -> visible to the copy engine
+          }
+          const int passes = ph.gated ? 2 : 1;
+  #pragma unroll 1
+          for (int item = blockIdx.x; item < ph.items && ok; item += gridDim.x) {
+            const Item it = decode(ph, item);
+  #pragma unroll 1
+            for (int ps = 0; ps < passes && ok; ++ps) {
+              const SubGemm& sg = ph.sub[ph.gated ? ps : it.sub];
+  #pragma unroll 1
+              for (int jj = 0; jj < it.ns; ++jj, ++gs) {
+                const int s = gs % NR, kb = it.kb0 + jj * KBS;
+                if (lane == 0) {
+                  if (gs >= NR) ok = mbar_wait(&stage_done[s], ((gs / NR) - 1) & 1, abort_flag, 1);
+                  if (ok) mbar_expect_tx(&x_full[s], (unsigned)L::kX);
+                }
+                ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;   // also orders the expected byte count before the copies
+                if (!ok) break;
+                uint8_t* st = r_ring + s * L::kStage;
+                if constexpr (TN >= 128) {                      // rows beyond M and columns beyond K are zero-filled
+                  if (lane < L::kXLanes) {
+                    const int j = lane / L::kXPieces, q = lane % L::kXPieces;
+                    tma_load_2d(st + j * L::kXTile + q * (L::kXRows * 128), &sg.map_x, (kb + j) * BK, it.mt * TN + q * L::kXRows, &x_full[s]);
+                  }
+                } else if (lane == 0) {
+                  if (ph.x3d) {                                 // k-blocks beyond K are zero-filled by the copy engine
+                    tma_load_3d(st, &sg.map_x, 0, it.mt * TN, kb, &x_full[s]);
+                  } else {
+  #pragma unroll 1
+                    for (int j = 0; j < KBS; ++j)               // columns beyond K are zero-filled by the copy engine
+                      tma_load_2d(st + j * L::kXTile, &sg.map_x, (kb + j) * BK, it.mt * TN, &x_full[s]);
+                  }
+                }
+              }
+            }
+          }
         }
-        const int passes = ph.gated ? 2 : 1;
-#pragma unroll 1
-        for (int item = blockIdx.x; item < ph.items && ok; item += gridDim.x) {
-          const Item it = decode(ph, item);
-#pragma unroll 1
-          for (int ps = 0; ps < passes && ok; ++ps) {
-            const SubGemm& sg = ph.sub[ph.gated ? ps : it.sub];
-#pragma unroll 1
-            for (int jj = 0; jj < it.ns; ++jj, ++gs) {
-              const int s = gs % NR, kb = it.kb0 + jj * KBS;
-              if (gs >= NR && !mbar_wait(&stage_done[s], ((gs / NR) - 1) & 1, abort_flag, 1)) { ok = false; break; }
-              uint8_t* st = r_ring + s * L::kStage;
-              mbar_expect_tx(&x_full[s], (unsigned)L::kX);
-              if (ph.x3d) {                                   // k-blocks beyond K are zero-filled by the copy engine
-                tma_load_3d(st, &sg.map_x, 0, it.mt * TN, kb, &x_full[s]);
-              } else {
-#pragma unroll 1
-                for (int j = 0; j < KBS; ++j)                 // columns beyond K are zero-filled by the copy engine
-                  tma_load_2d(st + j * L::kXTile, &sg.map_x, (kb + j) * BK, it.mt * TN, &x_full[s]);
+    } else {
+      if (lane == 0) {
+        bool ok = true;
+        int gs = 0;
+  #pragma unroll 1
+        for (int p = 0; p < prog.n_phases && ok; ++p) {
+          const Phase& ph = prog.ph[p];
+          for (int j = 0; j < ph.nsub; ++j) asm volatile("prefetch.tensormap [%0];\n" ::"l"(&ph.sub[j].map_x) : "memory");
+          if (p == 0) {
+            pdl_wait();
+          } else {
+            ok = grid_wait(&prog.grid_bar[p - 1], (int)gridDim.x, abort_flag);
+            asm volatile("fence.proxy.async;\n" ::: "memory");  // other CTAs' stores -> visible to the copy engine
+          }
+          const int passes = ph.gated ? 2 : 1;
+  #pragma unroll 1
+          for (int item = blockIdx.x; item < ph.items && ok; item += gridDim.x) {
+            const Item it = decode(ph, item);
+  #pragma unroll 1
+            for (int ps = 0; ps < passes && ok; ++ps) {
+              const SubGemm& sg = ph.sub[ph.gated ? ps : it.sub];
+  #pragma unroll 1
+              for (int jj = 0; jj < it.ns; ++jj, ++gs) {
+                const int s = gs % NR, kb = it.kb0 + jj * KBS;
+                if (gs >= NR && !mbar_wait(&stage_done[s], ((gs / NR) - 1) & 1, abort_flag, 1)) { ok = false; break; }
+                uint8_t* st = r_ring + s * L::kStage;
+                mbar_expect_tx(&x_full[s], (unsigned)L::kX);
+                if (ph.x3d) {                                   // k-blocks beyond K are zero-filled by the copy engine
+                  tma_load_3d(st, &sg.map_x, 0, it.mt * TN, kb, &x_full[s]);
+                } else {
+  #pragma unroll 1
+                  for (int j = 0; j < KBS; ++j)                 // columns beyond K are zero-filled by the copy engine
+                    tma_load_2d(st + j * L::kXTile, &sg.map_x, (kb + j) * BK, it.mt * TN, &x_full[s]);
+                }
               }
             }
           }
@@ -447,7 +534,8 @@ linear_tcq_kernel(const __grid_constant__ Program prog) {
     const int q = warp & 3;                                  // TMEM lane quarter this warp may access
     const int row = q * 32 + lane;                           // weight row within the tile = TMEM lane
     const unsigned lane_addr = tmem_base + ((unsigned)(q * 32) << 16);
-    int gs = 0, it_count = 0, ep_uses = 0;
+    int gs = 0, it_count = 0, ep_uses = 0, grp_uses = 0;
+    __nv_bfloat16* out_stage = reinterpret_cast<__nv_bfloat16*>(r_ring + NR * L::kStage + L::kBarBytes) + grp * (16 * BM);
     bool ok = true;
     bool waited = false;
     for (int p = 0; p < prog.n_phases && ok; ++p) {
@@ -506,6 +594,8 @@ linear_tcq_kernel(const __grid_constant__ Program prog) {
         const unsigned acc1 = (unsigned)((ph.gated ? 2 : 1) * TN);   // column offset of chain 1
         float* slice = ph.partial + (size_t)item * (TN * BM);
         __nv_bfloat16* y = sg0.y;
+        // outputs through the staging tile: token tiles of 128 and more, rows of y 16-byte aligned
+        const bool vec = TN >= 128 && ph.N % 8 == 0 && (reinterpret_cast<uintptr_t>(y) & 15) == 0;
         // W columns per step, the tensor-memory loads of both chains issued before one wait (a tcgen05.ld costs its
         // warp ~115 cycles to issue whatever its width, so few wide loads, not many narrow ones); a gated item first
         // turns the gate columns into SiLU(g), then fetches the up columns into the freed registers
@@ -548,13 +638,29 @@ linear_tcq_kernel(const __grid_constant__ Program prog) {
           } else if (split) {
 #pragma unroll
             for (int j = 0; j < W; ++j) __stcg(&slice[(c0 + j) * BM + row], __uint_as_float(r[j]));
-          } else if (n < ph.N) {
+          } else {
+            if constexpr (TN >= 128) {
+              if (vec) {
+                float v[W];
 #pragma unroll
-            for (int j = 0; j < W; ++j) {
-              const int64_t m = m0 + c0 + j;
-              if (m < prog.M) y[m * ph.N + n] = __float2bfloat16_rn(__uint_as_float(r[j]) * sc0 + bv0);
+                for (int j = 0; j < W; ++j) v[j] = __uint_as_float(r[j]) * sc0 + bv0;
+                if (!(ok = store_transposed<W, TN>(v, out_stage, row, y, ph.N, prog.M, (int64_t)it.nt * BM, m0, c0, 1, &grp_bar[grp],
+                                                   grp_uses, lane, abort_flag)))
+                  break;
+                continue;
+              }
+            }
+            if (n < ph.N) {
+#pragma unroll
+              for (int j = 0; j < W; ++j) {
+                const int64_t m = m0 + c0 + j;
+                if (m < prog.M) y[m * ph.N + n] = __float2bfloat16_rn(__uint_as_float(r[j]) * sc0 + bv0);
+              }
             }
           }
+        }
+        if constexpr (TN >= 128) {
+          if (!ok) break;
         }
         tc_fence_before();
         // every warp is done reading the accumulator before any warp stores the next item's A operand
@@ -579,42 +685,98 @@ linear_tcq_kernel(const __grid_constant__ Program prog) {
           if (*abort_flag) { ok = false; break; }
           // the slices are read with L2 loads (ld.global.cg) after that acquire and the rendezvous: no further fence
           const int sp = item % ph.splits;
-          if (n < ph.N) {
-            const float* tile0 = ph.partial + (size_t)(item - sp) * (TN * BM) + row;
-            // all of this thread's columns and slices in flight at once (up to 8 x 4, 4 x 8 or 2 x 16 loads): one round trip
-            // to the L2 instead of one per column.  A column's slices are added in split order.
-            const int cstep = 2 * ph.splits;
-            auto batch = [&](auto cb_c, auto sb_c) {
-              constexpr int CB = decltype(cb_c)::value, SB = decltype(sb_c)::value;
-              for (int cb = sp + grp * ph.splits; cb < TN; cb += CB * cstep) {
-                float v[CB];
-#pragma unroll
-                for (int u = 0; u < CB; ++u) v[u] = 0.f;
-                for (int s0 = 0; s0 < ph.splits; s0 += SB) {
-                  float a[CB][SB];
-#pragma unroll
-                  for (int u = 0; u < CB; ++u)
-#pragma unroll
-                    for (int t = 0; t < SB; ++t)
-                      a[u][t] = (cb + u * cstep < TN && s0 + t < ph.splits)
-                                    ? __ldcg(tile0 + (size_t)(s0 + t) * (TN * BM) + (cb + u * cstep) * BM) : 0.f;
-#pragma unroll
-                  for (int u = 0; u < CB; ++u)
-#pragma unroll
-                    for (int t = 0; t < SB; ++t)
-                      if (s0 + t < ph.splits) v[u] += a[u][t];
+          if constexpr (TN >= 128) {
+            {
+              const float* tile0 = ph.partial + (size_t)(item - sp) * (TN * BM) + row;
+              // all of this thread's columns and slices in flight at once (up to 16 x 2, 8 x 4, 4 x 8 or 2 x 16 loads): one round
+              // trip to the L2 instead of one per column.  A column's slices are added in split order.  (Rows beyond N exist in
+              // the slices and are summed like the others; they are never stored.)
+              const int cstep = 2 * ph.splits;
+              auto batch = [&](auto cb_c, auto sb_c) -> bool {
+                constexpr int CB = decltype(cb_c)::value, SB = decltype(sb_c)::value;
+                for (int cb = sp + grp * ph.splits; cb < TN; cb += CB * cstep) {
+                  float v[CB];
+  #pragma unroll
+                  for (int u = 0; u < CB; ++u) v[u] = 0.f;
+                  for (int s0 = 0; s0 < ph.splits; s0 += SB) {
+                    float a[CB][SB];
+  #pragma unroll
+                    for (int u = 0; u < CB; ++u)
+  #pragma unroll
+                      for (int t = 0; t < SB; ++t)
+                        a[u][t] = (cb + u * cstep < TN && s0 + t < ph.splits)
+                                      ? __ldcg(tile0 + (size_t)(s0 + t) * (TN * BM) + (cb + u * cstep) * BM) : 0.f;
+  #pragma unroll
+                    for (int u = 0; u < CB; ++u)
+  #pragma unroll
+                      for (int t = 0; t < SB; ++t)
+                        if (s0 + t < ph.splits) v[u] += a[u][t];
+                  }
+                  if constexpr (CB >= 8) {
+                    if (vec) {
+  #pragma unroll
+                      for (int u = 0; u < CB; ++u) v[u] = v[u] * sc0 + bv0;
+                      if (!store_transposed<CB, TN>(v, out_stage, row, y, ph.N, prog.M, (int64_t)it.nt * BM, m0, cb, cstep, &grp_bar[grp],
+                                                    grp_uses, lane, abort_flag))
+                        return false;
+                      continue;
+                    }
+                  }
+                  if (n < ph.N) {
+  #pragma unroll
+                    for (int u = 0; u < CB; ++u) {
+                      const int c = cb + u * cstep;
+                      const int64_t m = m0 + c;
+                      if (c < TN && m < prog.M) y[m * ph.N + n] = __float2bfloat16_rn(v[u] * sc0 + bv0);
+                    }
+                  }
                 }
-#pragma unroll
-                for (int u = 0; u < CB; ++u) {
-                  const int c = cb + u * cstep;
-                  const int64_t m = m0 + c;
-                  if (c < TN && m < prog.M) y[m * ph.N + n] = __float2bfloat16_rn(v[u] * sc0 + bv0);
+                return true;
+              };
+              if (ph.splits <= 2) ok = batch(std::integral_constant<int, 16>{}, std::integral_constant<int, 2>{});
+              else if (ph.splits <= 4) ok = batch(std::integral_constant<int, 8>{}, std::integral_constant<int, 4>{});
+              else if (ph.splits <= 8) ok = batch(std::integral_constant<int, 4>{}, std::integral_constant<int, 8>{});
+              else ok = batch(std::integral_constant<int, 2>{}, std::integral_constant<int, 16>{});
+              if (!ok) break;
+            }
+          } else {
+            if (n < ph.N) {
+              const float* tile0 = ph.partial + (size_t)(item - sp) * (TN * BM) + row;
+              // all of this thread's columns and slices in flight at once (up to 8 x 4, 4 x 8 or 2 x 16 loads): one round trip
+              // to the L2 instead of one per column.  A column's slices are added in split order.
+              const int cstep = 2 * ph.splits;
+              auto batch = [&](auto cb_c, auto sb_c) {
+                constexpr int CB = decltype(cb_c)::value, SB = decltype(sb_c)::value;
+                for (int cb = sp + grp * ph.splits; cb < TN; cb += CB * cstep) {
+                  float v[CB];
+  #pragma unroll
+                  for (int u = 0; u < CB; ++u) v[u] = 0.f;
+                  for (int s0 = 0; s0 < ph.splits; s0 += SB) {
+                    float a[CB][SB];
+  #pragma unroll
+                    for (int u = 0; u < CB; ++u)
+  #pragma unroll
+                      for (int t = 0; t < SB; ++t)
+                        a[u][t] = (cb + u * cstep < TN && s0 + t < ph.splits)
+                                      ? __ldcg(tile0 + (size_t)(s0 + t) * (TN * BM) + (cb + u * cstep) * BM) : 0.f;
+  #pragma unroll
+                    for (int u = 0; u < CB; ++u)
+  #pragma unroll
+                      for (int t = 0; t < SB; ++t)
+                        if (s0 + t < ph.splits) v[u] += a[u][t];
+                  }
+  #pragma unroll
+                  for (int u = 0; u < CB; ++u) {
+                    const int c = cb + u * cstep;
+                    const int64_t m = m0 + c;
+                    if (c < TN && m < prog.M) y[m * ph.N + n] = __float2bfloat16_rn(v[u] * sc0 + bv0);
+                  }
                 }
-              }
-            };
-            if (ph.splits <= 4) batch(std::integral_constant<int, 8>{}, std::integral_constant<int, 4>{});
-            else if (ph.splits <= 8) batch(std::integral_constant<int, 4>{}, std::integral_constant<int, 8>{});
-            else batch(std::integral_constant<int, 2>{}, std::integral_constant<int, 16>{});
+              };
+              if (ph.splits <= 4) batch(std::integral_constant<int, 8>{}, std::integral_constant<int, 4>{});
+              else if (ph.splits <= 8) batch(std::integral_constant<int, 4>{}, std::integral_constant<int, 8>{});
+              else batch(std::integral_constant<int, 2>{}, std::integral_constant<int, 16>{});
+            }
           }
         } else if (split) {
           // last CTA of this (matrix, n tile, m tile) finalizes: sum of the slices -> y, then resets the counter
@@ -788,7 +950,11 @@ bool fill_sub(SubGemm& sg, const GemmSpec& g, int64_t M, int tn, int bits, bool 
   const CUtensorMapSwizzle sw = box == 128 ? CU_TENSOR_MAP_SWIZZLE_128B
                                 : (box == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : (box == 32 ? CU_TENSOR_MAP_SWIZZLE_32B : CU_TENSOR_MAP_SWIZZLE_NONE));
   if (!make_map(&sg.map_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, g.W, rb, (uint64_t)g.N, rb, (uint32_t)box, BM, sw)) return false;
-  if (x3d) {
+  if (tn >= 128) {                                                     // boxes of 128 tokens x one k-block, one per lane
+    if (!make_map(&sg.map_x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, g.x, (uint64_t)g.K, (uint64_t)M, (uint64_t)g.K * 2, BK, 128,
+                  CU_TENSOR_MAP_SWIZZLE_128B))
+      return false;
+  } else if (x3d) {
     if (!make_map_x3d(&sg.map_x, g.x, (uint64_t)g.K, (uint64_t)M, (uint32_t)tn, (uint32_t)stage_kbs(tn, bits))) return false;
   } else if (!make_map(&sg.map_x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, g.x, (uint64_t)g.K, (uint64_t)M, (uint64_t)g.K * 2, BK,
                        (uint32_t)tn, CU_TENSOR_MAP_SWIZZLE_128B)) {
