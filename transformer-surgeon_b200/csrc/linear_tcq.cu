@@ -54,12 +54,12 @@ template <int TN, int BITS> struct QLayout {
   static constexpr int kKbsFull = 1024 / BITS / BK;        // k-blocks in a 128-byte row of codes
   // A buffer = KBS * 32 TMEM columns <= 128; 64- and 256-token tiles keep two k-blocks per stage (16 / 64 KB of activations)
   static constexpr int kKbsCap = (TN <= 32 || TN == 128) ? 4 : 2;
-  // A buffers of 128 TMEM columns above the accumulators.  Token tiles up to 32 need at most 4 x 32 accumulator
-  // columns (two chains, gate and up), which leaves room for THREE buffers: the dequant warps may then run two
-  // stages ahead of the MMAs instead of one, and the chain "dequantize -> MMAs -> buffer free" no longer sets the
-  // pace of the main loop.
-  static constexpr int NBUF = TN <= 32 ? 3 : 2;
-  static constexpr unsigned kACol0 = TN <= 32 ? 128 : 256;  // TMEM column of A buffer 0; buffer b at + 128 b
+  // A buffers (KBS x 32 TMEM columns each) above the accumulators.  Token tiles up to 32 need at most 4 x 32 accumulator
+  // columns (two chains, gate and up), the others 256.  As many buffers as fit (up to 4, and no more than ring stages):
+  // the dequant warps then run NBUF - 1 stages ahead of the MMAs, and the chain "dequantize -> MMAs issued -> MMAs
+  // complete -> buffer free" (traced at 256 tokens: 920 + 310 + 970 + 520 cycles per TWO stages with two buffers, i.e.
+  // 685 cycles per k-block against 512 of the tensor pipe) no longer sets the pace of the main loop.
+  static constexpr unsigned kACol0 = TN <= 32 ? 128 : 256;  // TMEM column of A buffer 0; buffer b at + kABufCols b
   static constexpr int KBS = kKbsFull < kKbsCap ? kKbsFull : kKbsCap;
   static constexpr int kRawRow = BK * BITS / 8;            // bytes of one weight row per k-block
   static constexpr int kRawStageRow = KBS * kRawRow;       // bytes of one weight row per stage (32/64/128)
@@ -72,10 +72,14 @@ template <int TN, int BITS> struct QLayout {
   static constexpr int kStage = kX + kRaw;                 // multiple of 1024
   static constexpr int kNRraw = kSmemBudget / kStage;
   static constexpr int NR = kNRraw > 12 ? 12 : kNRraw;
+  static constexpr int kABufCols = KBS * 32;
+  static constexpr int kNBufFit = (512 - (int)kACol0) / kABufCols;
+  static constexpr int NBUF = kNBufFit < NR ? (kNBufFit < 4 ? kNBufFit : 4) : (NR < 4 ? NR : 4);
+  static_assert(NBUF >= 2 && kACol0 + NBUF * kABufCols <= 512, "tensor memory columns");
   static constexpr int kBarBytes = 1024;
-  // Token tiles of 128 and more transpose their outputs through shared memory (16 tokens x 128 rows of bf16 per dequant
-  // group), so that a token's 128 outputs leave as 16-byte stores of whole 256-byte runs instead of 2-byte stores
-  static constexpr int kOutStage = TN >= 128 ? 2 * 16 * BM * 2 : 0;
+  // Token tiles of 128 and more transpose their outputs through shared memory (16 tokens x 32 rows of bf16 per warp),
+  // so that they leave as 16-byte stores instead of 2-byte stores
+  static constexpr int kOutStage = TN >= 128 ? kDqWarps * 16 * 32 * 2 : 0;
   static constexpr int kBytes = NR * kStage + kBarBytes + kOutStage + 1024;
   static_assert(kBytes <= 227 * 1024, "shared memory of one CTA");
   // The tensor pipe needs ~55 + N/2 cycles per tcgen05.mma (the A operand is read from tensor memory), and
@@ -90,6 +94,10 @@ template <int TN, int BITS> struct QLayout {
   static constexpr bool kTwoChains = 2 * TN <= 256;
   static constexpr bool kTwoChainsGated = 4 * TN <= 256;
   static constexpr bool kSplitStage = TN <= 32 && KBS >= 2;
+  // The 256-token tile has one accumulator of 256 columns; its two halves are independent accumulators, so each lane
+  // issues every stage's MMAs for ITS 128 tokens (N = 128: the lane's ~114 cycles per MMA cover 64 cycles of the pipe,
+  // two lanes keep it busy; one lane issuing N = 256 needs 141-171 cycles per 128 cycles of the pipe)
+  static constexpr bool kSplitTokens = TN == 256;
 };
 
 __device__ __forceinline__ uint4 lds128(unsigned addr) {
@@ -207,27 +215,26 @@ __device__ __forceinline__ bool warps_rendezvous(unsigned long long* bar, int& u
   return ok;
 }
 
-// CNT token columns of a dequant group (4 warps, 128 weight rows) -> y, transposed through the group's staging tile
-// [CNT][128] bf16: thread `row` deposits its CNT values, the group meets, then every thread moves 16-byte pieces (8
-// consecutive rows of one token).  Slot j holds token column c_first + j * c_stride of the tile; columns beyond the tile
-// or beyond M and row pieces beyond N (a multiple of 8) are skipped.  The group meets again before the tile is reused.
+// CNT token columns of one warp (32 weight rows) -> y, transposed through the warp's staging tile [CNT][32] bf16: lane
+// `lane` deposits its CNT values, then every lane moves 16-byte pieces (8 consecutive rows of one token), so a token's
+// 32 outputs leave as four 16-byte stores of one 64-byte run instead of 32 2-byte stores.  Slot j holds token column
+// c_first + j * c_stride of the tile; columns beyond the tile or beyond M and row pieces beyond N (a multiple of 8) are
+// skipped.  Warp-local: no other warp is waited for.
 template <int CNT, int TN>
-__device__ __forceinline__ bool store_transposed(const float (&v)[CNT], __nv_bfloat16* sb, int row, __nv_bfloat16* y, int64_t N, int64_t M,
-                                                 int64_t n_tile0, int64_t m0, int c_first, int c_stride, unsigned long long* bar,
-                                                 int& uses, int lane, volatile int* abort_flag) {
+__device__ __forceinline__ void store_transposed(const float (&v)[CNT], __nv_bfloat16* sb, int lane, __nv_bfloat16* y, int64_t N, int64_t M,
+                                                 int64_t n_warp0, int64_t m0, int c_first, int c_stride) {
 #pragma unroll
-  for (int j = 0; j < CNT; ++j) sb[j * BM + row] = __float2bfloat16_rn(v[j]);
-  if (!warps_rendezvous(bar, uses, lane, abort_flag)) return false;
+  for (int j = 0; j < CNT; ++j) sb[j * 32 + lane] = __float2bfloat16_rn(v[j]);
+  __syncwarp();
 #pragma unroll
-  for (int p = row; p < CNT * 16; p += BM) {
-    const int slot = p >> 4, part = p & 15;
+  for (int p = lane; p < CNT * 4; p += 32) {
+    const int slot = p >> 2, part = p & 3;
     const int c = c_first + slot * c_stride;
-    const int64_t m = m0 + c, nn = n_tile0 + part * 8;
-    if (c < TN && m < M && nn < N) *reinterpret_cast<uint4*>(y + m * N + nn) = *reinterpret_cast<const uint4*>(sb + slot * BM + part * 8);
+    const int64_t m = m0 + c, nn = n_warp0 + part * 8;
+    if (c < TN && m < M && nn < N) *reinterpret_cast<uint4*>(y + m * N + nn) = *reinterpret_cast<const uint4*>(sb + slot * 32 + part * 8);
   }
-  return warps_rendezvous(bar, uses, lane, abort_flag);
+  __syncwarp();
 }
-
 
 constexpr int kMaxPhases = 4;
 
@@ -295,8 +302,7 @@ linear_tcq_kernel(const __grid_constant__ Program prog) {
                                                             //      weight box, activation tiles and A buffer are free
   unsigned long long* acc_full = bars + 3 * NR;             // [1]  MMA commit: accumulator(s) of the item complete
   unsigned long long* ep_bar = acc_full + 1;                // [1]  rendezvous of the 8 warps
-  unsigned long long* grp_bar = ep_bar + 1;                 // [2]  rendezvous of one dequant group's 4 warps
-  unsigned* tmem_slot = reinterpret_cast<unsigned*>(grp_bar + 2);
+  unsigned* tmem_slot = reinterpret_cast<unsigned*>(ep_bar + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   volatile int* last_flag = abort_flag + 1;
 
@@ -323,11 +329,9 @@ linear_tcq_kernel(const __grid_constant__ Program prog) {
 
   int pre_w = 0;                                            // weight boxes issued during the set-up (thread 0)
   if (threadIdx.x == 0) {
-    for (int i = 0; i < NR; ++i) { mbar_init(&w_full[i], 1); mbar_init(&x_full[i], 1 + kDqWarps); mbar_init(&stage_done[i], L::kSplitStage ? 2 : 1); }
+    for (int i = 0; i < NR; ++i) { mbar_init(&w_full[i], 1); mbar_init(&x_full[i], 1 + kDqWarps); mbar_init(&stage_done[i], (L::kSplitStage || L::kSplitTokens) ? 2 : 1); }
     mbar_init(acc_full, 2);                                 // both issuers commit, with or without MMAs of their own
     mbar_init(ep_bar, kDqWarps);
-    mbar_init(&grp_bar[0], kDqWarps / 2);
-    mbar_init(&grp_bar[1], kDqWarps / 2);
     *abort_flag = 0;
     *last_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
@@ -484,7 +488,7 @@ linear_tcq_kernel(const __grid_constant__ Program prog) {
     // ---------------------------------------------------------------- MMA issuers
     if (lane == 0) {
       const int me = warp == 1 ? 0 : 1;                       // issuer 0: even stages / chain 0; issuer 1: odd stages / chain 1
-      constexpr unsigned idesc = idesc_bf16(TN);
+      constexpr unsigned idesc = idesc_bf16(L::kSplitTokens ? TN / 2 : TN);
       int gs = 0;
       bool ok = true;
       for (int p = 0; p < prog.n_phases && ok; ++p) {
@@ -494,10 +498,11 @@ linear_tcq_kernel(const __grid_constant__ Program prog) {
           const Item it = decode(ph, item);
           const int passes = ph.gated ? 2 : 1;
           for (int ps = 0; ps < passes && ok; ++ps) {
-            const unsigned d_tmem = tmem_base + (unsigned)((ph.gated ? 2 * (two ? me : 0) + ps : (two ? me : 0)) * TN);
+            const unsigned d_tmem = L::kSplitTokens ? tmem_base + (unsigned)(me * (TN / 2))
+                                                    : tmem_base + (unsigned)((ph.gated ? 2 * (two ? me : 0) + ps : (two ? me : 0)) * TN);
             bool first = true;                                // the chain's first MMA of the pass overwrites
             for (int jj = 0; jj < it.ns; ++jj, ++gs) {
-              if (!L::kSplitStage && (two ? (gs & 1) != me : me != 0)) {            // the other lane's stage
+              if (!L::kSplitStage && !L::kSplitTokens && (two ? (gs & 1) != me : me != 0)) {   // the other lane's stage
                 // a lane without any stage in this pass (single chain) still commits the item below: it follows the
                 // stages one by one (a parity wait is only meaningful in order), so that its arrival cannot fall into
                 // the previous item's phase of the accumulator barrier
@@ -509,8 +514,8 @@ linear_tcq_kernel(const __grid_constant__ Program prog) {
               ok = mbar_wait(&x_full[s], (gs / NR) & 1, abort_flag, 2);
               if (!ok) break;
               tc_fence_after();
-              const unsigned a_tmem = tmem_base + L::kACol0 + buf * 128;
-              const unsigned x_base = smem_u32(r_ring + s * L::kStage);
+              const unsigned a_tmem = tmem_base + L::kACol0 + buf * L::kABufCols;
+              const unsigned x_base = smem_u32(r_ring + s * L::kStage) + (L::kSplitTokens ? me * (TN / 2) * 128 : 0);   // this lane's tokens
               const int nsub = min(KBS, it.nkb - i);
               const bool halves = L::kSplitStage && two;      // this lane takes the k-blocks of its parity
               for (int j = halves ? me : 0; j < nsub && (!L::kSplitStage || two || me == 0); j += halves ? 2 : 1) {
@@ -534,8 +539,8 @@ linear_tcq_kernel(const __grid_constant__ Program prog) {
     const int q = warp & 3;                                  // TMEM lane quarter this warp may access
     const int row = q * 32 + lane;                           // weight row within the tile = TMEM lane
     const unsigned lane_addr = tmem_base + ((unsigned)(q * 32) << 16);
-    int gs = 0, it_count = 0, ep_uses = 0, grp_uses = 0;
-    __nv_bfloat16* out_stage = reinterpret_cast<__nv_bfloat16*>(r_ring + NR * L::kStage + L::kBarBytes) + grp * (16 * BM);
+    int gs = 0, it_count = 0, ep_uses = 0;
+    __nv_bfloat16* out_stage = reinterpret_cast<__nv_bfloat16*>(r_ring + NR * L::kStage + L::kBarBytes) + (warp - 2) * (16 * 32);   // this warp's
     bool ok = true;
     bool waited = false;
     for (int p = 0; p < prog.n_phases && ok; ++p) {
@@ -567,7 +572,7 @@ linear_tcq_kernel(const __grid_constant__ Program prog) {
             for (int j = grp; j < nsub; j += 2) {              // both groups work on the stage: half the latency
               unsigned regs[32];
               dequant_row_regs<BITS, L::kRawStageRow>(raw, row, j, regs);
-              tmem_st32(lane_addr + L::kACol0 + buf * 128 + j * 32, regs);
+              tmem_st32(lane_addr + L::kACol0 + buf * L::kABufCols + j * 32, regs);
             }
             tmem_st_wait();
             tc_fence_before();
@@ -644,9 +649,7 @@ linear_tcq_kernel(const __grid_constant__ Program prog) {
                 float v[W];
 #pragma unroll
                 for (int j = 0; j < W; ++j) v[j] = __uint_as_float(r[j]) * sc0 + bv0;
-                if (!(ok = store_transposed<W, TN>(v, out_stage, row, y, ph.N, prog.M, (int64_t)it.nt * BM, m0, c0, 1, &grp_bar[grp],
-                                                   grp_uses, lane, abort_flag)))
-                  break;
+                store_transposed<W, TN>(v, out_stage, lane, y, ph.N, prog.M, (int64_t)it.nt * BM + q * 32, m0, c0, 1);
                 continue;
               }
             }
@@ -658,9 +661,6 @@ linear_tcq_kernel(const __grid_constant__ Program prog) {
               }
             }
           }
-        }
-        if constexpr (TN >= 128) {
-          if (!ok) break;
         }
         tc_fence_before();
         // every warp is done reading the accumulator before any warp stores the next item's A operand
@@ -716,9 +716,7 @@ linear_tcq_kernel(const __grid_constant__ Program prog) {
                     if (vec) {
   #pragma unroll
                       for (int u = 0; u < CB; ++u) v[u] = v[u] * sc0 + bv0;
-                      if (!store_transposed<CB, TN>(v, out_stage, row, y, ph.N, prog.M, (int64_t)it.nt * BM, m0, cb, cstep, &grp_bar[grp],
-                                                    grp_uses, lane, abort_flag))
-                        return false;
+                      store_transposed<CB, TN>(v, out_stage, lane, y, ph.N, prog.M, (int64_t)it.nt * BM + q * 32, m0, cb, cstep);
                       continue;
                     }
                   }

@@ -36,6 +36,9 @@ inline GemmPlan plan_gemm(int64_t M, int64_t N, int64_t K, int nsub = 1, bool no
   // tokens, and one M128 x N256 x K16 MMA (128 cycles of the tensor pipe) outlasts the ~115 cycles its lane needs to
   // issue it (M = 2048, rank 1024, int4: 524 -> 566 TFLOP/s; with one k-block per stage it was slower than 128)
   g.tn = M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : (M <= 128 ? 128 : 256)));
+#ifdef TSB_FORCE_TN128
+  if (g.tn == 256) g.tn = 128;
+#endif
   g.kb_total = (int)((K + BK - 1) / BK);
   const int64_t n_tiles = (N + BM - 1) / BM, m_tiles = (M + g.tn - 1) / g.tn;
   const int64_t base = n_tiles * m_tiles * nsub;
