@@ -397,7 +397,7 @@ linear_tcq_kernel(const __grid_constant__ Program prog) {
     if constexpr (TN >= 128) {
         bool ok = true;
         int gs = 0;
-  #pragma unroll 1
+#pragma unroll 1
         for (int p = 0; p < prog.n_phases && ok; ++p) {
           const Phase& ph = prog.ph[p];
           if (lane == 0)
@@ -410,13 +410,13 @@ linear_tcq_kernel(const __grid_constant__ Program prog) {
             asm volatile("fence.proxy.async;\n" ::: "memory");  // other CTAs' stores -> visible to the copy engine
           }
           const int passes = ph.gated ? 2 : 1;
-  #pragma unroll 1
+#pragma unroll 1
           for (int item = blockIdx.x; item < ph.items && ok; item += gridDim.x) {
             const Item it = decode(ph, item);
-  #pragma unroll 1
+#pragma unroll 1
             for (int ps = 0; ps < passes && ok; ++ps) {
               const SubGemm& sg = ph.sub[ph.gated ? ps : it.sub];
-  #pragma unroll 1
+#pragma unroll 1
               for (int jj = 0; jj < it.ns; ++jj, ++gs) {
                 const int s = gs % NR, kb = it.kb0 + jj * KBS;
                 if (lane == 0) {
@@ -435,7 +435,7 @@ linear_tcq_kernel(const __grid_constant__ Program prog) {
                   if (ph.x3d) {                                 // k-blocks beyond K are zero-filled by the copy engine
                     tma_load_3d(st, &sg.map_x, 0, it.mt * TN, kb, &x_full[s]);
                   } else {
-  #pragma unroll 1
+#pragma unroll 1
                     for (int j = 0; j < KBS; ++j)               // columns beyond K are zero-filled by the copy engine
                       tma_load_2d(st + j * L::kXTile, &sg.map_x, (kb + j) * BK, it.mt * TN, &x_full[s]);
                   }
@@ -448,7 +448,7 @@ linear_tcq_kernel(const __grid_constant__ Program prog) {
       if (lane == 0) {
         bool ok = true;
         int gs = 0;
-  #pragma unroll 1
+#pragma unroll 1
         for (int p = 0; p < prog.n_phases && ok; ++p) {
           const Phase& ph = prog.ph[p];
           for (int j = 0; j < ph.nsub; ++j) asm volatile("prefetch.tensormap [%0];\n" ::"l"(&ph.sub[j].map_x) : "memory");
@@ -459,13 +459,13 @@ linear_tcq_kernel(const __grid_constant__ Program prog) {
             asm volatile("fence.proxy.async;\n" ::: "memory");  // other CTAs' stores -> visible to the copy engine
           }
           const int passes = ph.gated ? 2 : 1;
-  #pragma unroll 1
+#pragma unroll 1
           for (int item = blockIdx.x; item < ph.items && ok; item += gridDim.x) {
             const Item it = decode(ph, item);
-  #pragma unroll 1
+#pragma unroll 1
             for (int ps = 0; ps < passes && ok; ++ps) {
               const SubGemm& sg = ph.sub[ph.gated ? ps : it.sub];
-  #pragma unroll 1
+#pragma unroll 1
               for (int jj = 0; jj < it.ns; ++jj, ++gs) {
                 const int s = gs % NR, kb = it.kb0 + jj * KBS;
                 if (gs >= NR && !mbar_wait(&stage_done[s], ((gs / NR) - 1) & 1, abort_flag, 1)) { ok = false; break; }
@@ -474,7 +474,7 @@ linear_tcq_kernel(const __grid_constant__ Program prog) {
                 if (ph.x3d) {                                   // k-blocks beyond K are zero-filled by the copy engine
                   tma_load_3d(st, &sg.map_x, 0, it.mt * TN, kb, &x_full[s]);
                 } else {
-  #pragma unroll 1
+#pragma unroll 1
                   for (int j = 0; j < KBS; ++j)                 // columns beyond K are zero-filled by the copy engine
                     tma_load_2d(st + j * L::kXTile, &sg.map_x, (kb + j) * BK, it.mt * TN, &x_full[s]);
                 }
@@ -688,7 +688,8 @@ linear_tcq_kernel(const __grid_constant__ Program prog) {
           if constexpr (TN >= 128) {
             {
               const float* tile0 = ph.partial + (size_t)(item - sp) * (TN * BM) + row;
-              // all of this thread's columns and slices in flight at once (up to 16 x 2, 8 x 4, 4 x 8 or 2 x 16 loads): one round
+              // all of this thread's columns and slices in flight at once (up to 16 x 2, 8 x 4, 4 x 8 or 2 x 16 loads; a round trip to freshly written slices costs ~2200 cycles, and 64 loads
+              // per thread spill under the 128-register cap): one round
               // trip to the L2 instead of one per column.  A column's slices are added in split order.  (Rows beyond N exist in
               // the slices and are summed like the others; they are never stored.)
               const int cstep = 2 * ph.splits;
@@ -696,32 +697,36 @@ linear_tcq_kernel(const __grid_constant__ Program prog) {
                 constexpr int CB = decltype(cb_c)::value, SB = decltype(sb_c)::value;
                 for (int cb = sp + grp * ph.splits; cb < TN; cb += CB * cstep) {
                   float v[CB];
-  #pragma unroll
+#pragma unroll
                   for (int u = 0; u < CB; ++u) v[u] = 0.f;
                   for (int s0 = 0; s0 < ph.splits; s0 += SB) {
                     float a[CB][SB];
-  #pragma unroll
+#pragma unroll
                     for (int u = 0; u < CB; ++u)
-  #pragma unroll
+#pragma unroll
                       for (int t = 0; t < SB; ++t)
                         a[u][t] = (cb + u * cstep < TN && s0 + t < ph.splits)
                                       ? __ldcg(tile0 + (size_t)(s0 + t) * (TN * BM) + (cb + u * cstep) * BM) : 0.f;
-  #pragma unroll
+#pragma unroll
                     for (int u = 0; u < CB; ++u)
-  #pragma unroll
+#pragma unroll
                       for (int t = 0; t < SB; ++t)
                         if (s0 + t < ph.splits) v[u] += a[u][t];
                   }
                   if constexpr (CB >= 8) {
                     if (vec) {
-  #pragma unroll
+#pragma unroll
                       for (int u = 0; u < CB; ++u) v[u] = v[u] * sc0 + bv0;
-                      store_transposed<CB, TN>(v, out_stage, lane, y, ph.N, prog.M, (int64_t)it.nt * BM + q * 32, m0, cb, cstep);
+                      constexpr int CS = CB < 16 ? CB : 16;      // the staging tile holds 16 token columns
+#pragma unroll
+                      for (int h = 0; h < CB / CS; ++h)
+                        store_transposed<CS, TN>(*reinterpret_cast<const float(*)[CS]>(&v[h * CS]), out_stage, lane, y, ph.N, prog.M,
+                                                 (int64_t)it.nt * BM + q * 32, m0, cb + h * CS * cstep, cstep);
                       continue;
                     }
                   }
                   if (n < ph.N) {
-  #pragma unroll
+#pragma unroll
                     for (int u = 0; u < CB; ++u) {
                       const int c = cb + u * cstep;
                       const int64_t m = m0 + c;
@@ -747,23 +752,23 @@ linear_tcq_kernel(const __grid_constant__ Program prog) {
                 constexpr int CB = decltype(cb_c)::value, SB = decltype(sb_c)::value;
                 for (int cb = sp + grp * ph.splits; cb < TN; cb += CB * cstep) {
                   float v[CB];
-  #pragma unroll
+#pragma unroll
                   for (int u = 0; u < CB; ++u) v[u] = 0.f;
                   for (int s0 = 0; s0 < ph.splits; s0 += SB) {
                     float a[CB][SB];
-  #pragma unroll
+#pragma unroll
                     for (int u = 0; u < CB; ++u)
-  #pragma unroll
+#pragma unroll
                       for (int t = 0; t < SB; ++t)
                         a[u][t] = (cb + u * cstep < TN && s0 + t < ph.splits)
                                       ? __ldcg(tile0 + (size_t)(s0 + t) * (TN * BM) + (cb + u * cstep) * BM) : 0.f;
-  #pragma unroll
+#pragma unroll
                     for (int u = 0; u < CB; ++u)
-  #pragma unroll
+#pragma unroll
                       for (int t = 0; t < SB; ++t)
                         if (s0 + t < ph.splits) v[u] += a[u][t];
                   }
-  #pragma unroll
+#pragma unroll
                   for (int u = 0; u < CB; ++u) {
                     const int c = cb + u * cstep;
                     const int64_t m = m0 + c;
