@@ -82,6 +82,32 @@ def test_against_oracle(cuda, name, p, M, K, N, r):
         assert rel_err(y, ref32) < TOL[name], (simt, rel_err(y, ref32))
 
 
+@pytest.mark.parametrize("p", [4, 8, "binary"])
+@pytest.mark.parametrize("M,K,N,r", [(300, 2048, 1000, 0),      # two 256-token tiles (one ragged), 8-way split-K, ragged row tile
+                                     (700, 1024, 2052, 256),    # N not a multiple of 8: outputs leave as single elements
+                                     (257, 4096, 136, 1024),    # one token past a tile, 18-way split-K then 4-way
+                                     (1024, 512, 4096, 0),      # no split-K, several items per CTA
+                                     (129, 832, 264, 0)])       # K not a multiple of the k-block pair
+def test_prompt_sized_token_counts(cuda, p, M, K, N, r):
+    """More than 128 tokens: the 256-token tile with its transposed 16-byte output stores, every split-K batch
+    shape, ragged tiles in both directions; bf16, max-rel-err <= 1e-2 against the fp32 result on the dequantized
+    factors, and a second identical call returns the same bits."""
+    from transformer_surgeon_b200 import ops
+    x, U, V, b = _case(M, K, N, r, p, "bf16", seed=5)
+    fu = ops.Factor.quantize(U.to(cuda), p)
+    fv = ops.Factor.quantize(V.to(cuda), p) if r else None
+    Ud = fu.reconstruct(torch.bfloat16).cpu()
+    Vd = fv.reconstruct(torch.bfloat16).cpu() if r else None
+    ref32 = olin.linear_compressed_fp32(x, Ud, b, Vd)
+    lin = ops.PackedLinear(fu, fv, b.to(cuda), torch.bfloat16)
+    y = lin(x.to(cuda))
+    assert rel_err(y.cpu(), ref32) < TOL["bf16"], rel_err(y.cpu(), ref32)
+    # element-wise: no output may be missing or misplaced (a max-error bound alone would let a zero row through)
+    err = (y.cpu().float() - ref32.float()).abs()
+    assert (err <= 2e-2 * ref32.float().abs() + 1e-2 * ref32.float().abs().max()).all()
+    assert torch.equal(lin(x.to(cuda)), y)
+
+
 def test_config2_shape_sweep(cuda):
     """x [M, 4096], W 4096x4096 factored at r in {256, 1024}, 8/4-bit + binary factors, bf16:
     compared with the dequantized fp32 result (max-rel-err <= 1e-2)."""
