@@ -48,6 +48,24 @@ HBM_NOMINAL_GBS = 8000.0
 METRIC = "decode tokens/s (Llama-3-8B LRD+W4+FP8-KV)"
 
 
+_RESULT_OUT = None
+
+
+def divert_stdout():
+    """Whatever a library writes to stdout during the run (NCCL prints its version there) goes to stderr; the result
+    line alone reaches the real stdout through emit()."""
+    global _RESULT_OUT
+    sys.stdout.flush()
+    _RESULT_OUT = os.fdopen(os.dup(1), "w")
+    os.dup2(2, 1)
+
+
+def emit(text):
+    out = _RESULT_OUT or sys.stdout
+    out.write(text + "\n")
+    out.flush()
+
+
 def parse():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -281,7 +299,7 @@ def run_reference(a):
                                    % (a.layers, a.rank, a.wbits, a.batch, a.context)},
             "cpu_baseline": {"value": tps, "unit": "tokens/s", "cores": os.cpu_count(), "kind": dec.kind, "sample": sample},
             "e2e": {"value": tps, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
-    print(json.dumps(line))
+    emit(json.dumps(line))
 
 
 # ------------------------------------------------------------------------------ GPU arm
@@ -394,9 +412,9 @@ def run_ours(a):
     if a.parallel == "tp" and world > 1:                     # tensor parallel only (development runs)
         rec = tp_leg(a, device, world, rank, barrier)
         if rank == 0:
-            print(json.dumps({"metric": METRIC, "value": rec["tokens_per_s"], "unit": "tokens/s", "n_gpus": world, "steps": a.steps,
-                              "warmup": a.warmup, "ms_per_step": rec["ms_per_step"], "higher_is_better": True, "scaling": "strong",
-                              "tp": rec}))
+            emit(json.dumps({"metric": METRIC, "value": rec["tokens_per_s"], "unit": "tokens/s", "n_gpus": world, "steps": a.steps,
+                             "warmup": a.warmup, "ms_per_step": rec["ms_per_step"], "higher_is_better": True, "scaling": "strong",
+                             "tp": rec}))
         barrier()
         dist.destroy_process_group()
         return
@@ -485,7 +503,7 @@ def run_ours(a):
             if not done.wait(240.0):
                 if rank == 0:
                     line["tp"] = {"error": "tensor-parallel leg did not finish within 240 s"}
-                    print(json.dumps(line), flush=True)
+                    emit(json.dumps(line))
                 os._exit(0)
         threading.Thread(target=watchdog, daemon=True).start()
         try:
@@ -495,7 +513,7 @@ def run_ours(a):
         if rank == 0:
             line["tp"] = rec
     if rank == 0:
-        print(json.dumps(line), flush=True)
+        emit(json.dumps(line))
     if world > 1:
         if rec is not None and "error" in rec:
             os._exit(0)                      # a failed leg may have left collectives unmatched: leave without a teardown
@@ -596,7 +614,7 @@ def run_c5(a):
                          "ms_per_launch": t_attn * 1e-3, "share_of_step": nl * t_attn / step_us,
                          "parity": "KV formats are this project's definitions: parity unpinned",
                          "step_achieved": step_bytes / (step_us * 1e-6) / 1e9, "step_frac": step_bytes / (step_us * 1e-6) / 1e9 / peak}}
-    print(json.dumps(line), flush=True)
+    emit(json.dumps(line))
 
 
 def sweep_linear(a, ranks=(256, 1024), precisions=(8, 4, "binary"), ms=None, copies=8):
@@ -732,11 +750,12 @@ def sweep_prefill(a, cases=None):
 
 if __name__ == "__main__":
     args = parse()
+    divert_stdout()
     if args.sweep:
         import torch
         torch.cuda.set_device(0)
         for rec in {"linear": sweep_linear, "attention": sweep_attention, "prefill": sweep_prefill}[args.sweep](args):
-            print(json.dumps(rec))
+            emit(json.dumps(rec))
     elif args.impl == "reference":
         run_reference(args)
     elif args.config == "c5":
