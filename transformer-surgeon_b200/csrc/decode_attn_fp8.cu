@@ -104,6 +104,40 @@ decode_attn_fp8_kernel(tsb200_kv_desc kv, const T* __restrict__ q, int64_t qs, i
   }
   __syncwarp();
 
+  // this warp's pages: pb + w, pb + w + kWarps, ...; consecutive two form a pair (one ring stage)
+  const int n_pages = (pe - pb - w + kWarps - 1) / kWarps > 0 ? (pe - pb - w + kWarps - 1) / kWarps : 0;
+  const int n_pairs = (n_pages + 1) / 2;
+  const int64_t rec_stride = (int64_t)kv.hkv * REC;
+  auto page_ptrs = [&](int idx, const uint8_t*& kr, const uint8_t*& vr) {
+    const int pg = pb + w + idx * kWarps;
+    int64_t page = kv.block_table[(int64_t)b * kv.bt_stride + pg];
+    page = page < 0 ? 0 : (page >= kv.num_pages ? kv.num_pages - 1 : page);
+    kr = kv.k_pool + page * rec_stride + (int64_t)hk * REC;
+    vr = kv.v_pool + page * rec_stride + (int64_t)hk * REC;
+  };
+  auto issue = [&](int pair) {
+    if (pair < n_pairs && lane == 0) {
+      uint8_t* st = ring + (pair % kStages) * STAGE;
+      unsigned long long* bar = &bars[pair % kStages];
+      const bool two = 2 * pair + 1 < n_pages;
+      mbar_expect_tx(bar, two ? 4u * REC : 2u * REC);
+      const uint8_t *kr, *vr;
+      page_ptrs(2 * pair, kr, vr);
+      bulk_g2s(st, kr, REC, bar);
+      bulk_g2s(st + REC, vr, REC, bar);
+      if (two) {
+        page_ptrs(2 * pair + 1, kr, vr);
+        bulk_g2s(st + 2 * REC, kr, REC, bar);
+        bulk_g2s(st + 3 * REC, vr, REC, bar);
+      }
+    }
+  };
+  // the first copies leave before the query is expanded: their latency (block-table entry, then the copy: ~2 us) runs
+  // under that work instead of after it
+#pragma unroll
+  for (int i = 0; i < kStages - 1; ++i) issue(i);
+
+
   // ---- expanded query operand -------------------------------------------------------------------
   // column n of n-tile nt: head 2*nt + (n >> 2), term n & 3 (hi, mid, lo, zero); this lane supplies
   // column n = gid.  k-slots of QK step c (c = 0..3): lane `tid` covers dims 16*(tid + 4*(c>>1)) +
@@ -159,37 +193,6 @@ decode_attn_fp8_kernel(tsb200_kv_desc kv, const T* __restrict__ q, int64_t qs, i
 #pragma unroll
     for (int j = 0; j < 2; ++j) oacc[i][j][0] = oacc[i][j][1] = oacc[i][j][2] = oacc[i][j][3] = 0.f;
   float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
-
-  // this warp's pages: pb + w, pb + w + kWarps, ...; consecutive two form a pair (one ring stage)
-  const int n_pages = (pe - pb - w + kWarps - 1) / kWarps > 0 ? (pe - pb - w + kWarps - 1) / kWarps : 0;
-  const int n_pairs = (n_pages + 1) / 2;
-  const int64_t rec_stride = (int64_t)kv.hkv * REC;
-  auto page_ptrs = [&](int idx, const uint8_t*& kr, const uint8_t*& vr) {
-    const int pg = pb + w + idx * kWarps;
-    int64_t page = kv.block_table[(int64_t)b * kv.bt_stride + pg];
-    page = page < 0 ? 0 : (page >= kv.num_pages ? kv.num_pages - 1 : page);
-    kr = kv.k_pool + page * rec_stride + (int64_t)hk * REC;
-    vr = kv.v_pool + page * rec_stride + (int64_t)hk * REC;
-  };
-  auto issue = [&](int pair) {
-    if (pair < n_pairs && lane == 0) {
-      uint8_t* st = ring + (pair % kStages) * STAGE;
-      unsigned long long* bar = &bars[pair % kStages];
-      const bool two = 2 * pair + 1 < n_pages;
-      mbar_expect_tx(bar, two ? 4u * REC : 2u * REC);
-      const uint8_t *kr, *vr;
-      page_ptrs(2 * pair, kr, vr);
-      bulk_g2s(st, kr, REC, bar);
-      bulk_g2s(st + REC, vr, REC, bar);
-      if (two) {
-        page_ptrs(2 * pair + 1, kr, vr);
-        bulk_g2s(st + 2 * REC, kr, REC, bar);
-        bulk_g2s(st + 3 * REC, vr, REC, bar);
-      }
-    }
-  };
-#pragma unroll
-  for (int i = 0; i < kStages - 1; ++i) issue(i);
 
   bool ok = true;
   for (int pair = 0; pair < n_pairs && ok; ++pair) {
