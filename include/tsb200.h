@@ -60,7 +60,12 @@ int tsb200_check_device(void);
 /* Programmatic dependent launch for the decode-step kernels (linear, rope_append, decode
  * attention, add_rmsnorm, swiglu): when enabled, each launch may start while its predecessor on
  * the stream drains; the kernels order their dependent memory accesses themselves.  Process-wide;
- * returns the previous setting.  Default 0. */
+ * returns the previous setting.  Default 0.
+ * What a kernel touches before that ordering point is constant data (weights, weight scales) and, in the FP8 decode
+ * attention with one split, pages of the cache STRICTLY OLDER than the one that holds a sequence's newest token together
+ * with their block-table entries: with this setting on, the launches that directly precede a decode attention on its
+ * stream must not rewrite those (an append never does; a cache compaction or page remap must be followed by one launch
+ * of anything else, or run with the setting off). */
 int tsb200_set_pdl(int enabled);
 
 /* ------------------------------------------------------------------------------------

@@ -301,3 +301,44 @@ def test_rope_append_fused_equals_separate_calls(cuda, name):
     g2.rope_append(q4, k4, v4, rope)
     assert torch.equal(q4, q_ref)
     assert torch.equal(g1.k_pool, g2.k_pool) and torch.equal(g1.v_pool, g2.v_pool)
+
+
+def test_fp8_attention_after_append_under_dependent_launch(cuda):
+    """One decode step's append -> attention pair with programmatic dependent launch on: the attention may fetch pages
+    older than the newest token before the append has finished.  Lengths sit on, before and after page boundaries and
+    around the page count at which that early fetch starts; the result equals, bit for bit, the one with the setting
+    off, and the oracle's within the attention tolerance."""
+    from transformer_surgeon_b200 import ops
+    rng = np.random.default_rng(29)
+    B, H, Hkv, d = 32, 16, 4, 128                            # 128 (sequence, kv head) pairs: one split
+    lens = np.array([0, 1, 15, 16, 17, 31, 32, 33, 95, 96, 97, 111, 112, 113, 127, 128, 129, 191, 192, 193, 207, 208, 209,
+                     223, 224, 225, 239, 240, 241, 300, 400, 430], dtype=np.int32)
+    o, g = make_pair("fp8", B, 28, Hkv, d, cuda, rng)
+    T = int(lens.max())
+    k, v = outlier_kv(rng, B, T + 1, Hkv, d, torch.bfloat16)
+    sync_scales(o, g, k, v)
+    nl = torch.from_numpy(lens).to(cuda)
+    g.append(k[:, :T].to(cuda), v[:, :T].to(cuda), new_lens=nl)
+    o.append(k[:, :T].float().numpy(), v[:, :T].float().numpy(), new_lens=lens)
+    k_new = torch.stack([k[b, lens[b]] for b in range(B)]).unsqueeze(1).to(cuda)      # token at position lens[b]
+    v_new = torch.stack([v[b, lens[b]] for b in range(B)]).unsqueeze(1).to(cuda)
+    q = torch.from_numpy(rng.standard_normal((B, H, d)).astype(np.float32)).bfloat16().to(cuda)
+    write_pos, after = nl.clone(), nl + 1
+    outs = []
+    for pdl in (False, True):
+        old = ops.set_pdl(pdl)
+        try:
+            for _ in range(3):                               # the same token into the same slot every time
+                g.append(k_new, v_new, seq_lens=write_pos)
+                out = ops.paged_decode_attention(g, q, max_seq_len=448, seq_lens=after)
+            torch.cuda.synchronize()
+        finally:
+            ops.set_pdl(old)
+        outs.append(out.clone())
+    assert torch.equal(outs[0], outs[1])
+    o.seq_lens[:] = lens
+    o.append(k_new.float().cpu().numpy(), v_new.float().cpu().numpy())
+    o.seq_lens[:] = lens + 1
+    ref, ref_abs = oatt.paged_decode_attention(o, q.float().cpu().numpy(), with_abs=True)
+    tol = attn_tol(ref, ref_abs, "bf16", False)
+    assert np.all(np.abs(outs[1].float().cpu().numpy() - ref) <= tol)

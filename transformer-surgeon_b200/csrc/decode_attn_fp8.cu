@@ -35,6 +35,7 @@ using tc::smem_u32;
 #endif
 constexpr int kWarps = TSB_FP8_WARPS;
 constexpr int kStages = 2;
+constexpr int kEarlyStages = 1;            // ring stages that may be filled before the dependency wait (2 measured no faster)
 constexpr int D = 128;
 constexpr int REC = 16 * D;                 // bytes of one K or V record
 constexpr int STAGE = 4 * REC;              // K_A, V_A, K_B, V_B
@@ -85,15 +86,10 @@ decode_attn_fp8_kernel(tsb200_kv_desc kv, const T* __restrict__ q, int64_t qs, i
                        float* __restrict__ ws, int* __restrict__ counters, T* __restrict__ out, int* __restrict__ status) {
   extern __shared__ __align__(128) uint8_t smem[];
   pdl_launch_dependents();
-  pdl_wait();     // q, the page just appended and seq_lens come from the preceding kernels
   const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
   const int gid = lane >> 2, tid = lane & 3;
   const int b = blockIdx.x / kv.hkv, hk = blockIdx.x % kv.hkv, s = blockIdx.y;
   const int g = H / kv.hkv;                                  // <= 4
-  int len = kv.seq_lens[b];
-  len = len < 0 ? 0 : (len > max_seq_len ? (int)max_seq_len : len);
-  int pb, pe;
-  split_range(len, s, S, pb, pe);
 
   uint8_t* ring = smem + (size_t)w * WARP_SMEM;
   unsigned* pbuf = reinterpret_cast<unsigned*>(ring + kStages * STAGE);
@@ -103,11 +99,51 @@ decode_attn_fp8_kernel(tsb200_kv_desc kv, const T* __restrict__ q, int64_t qs, i
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
   __syncwarp();
+  const int64_t rec_stride = (int64_t)kv.hkv * REC;
+  auto page_of = [&](int pg, const uint8_t*& kr, const uint8_t*& vr) {
+    int64_t page = kv.block_table[(int64_t)b * kv.bt_stride + pg];
+    page = page < 0 ? 0 : (page >= kv.num_pages ? kv.num_pages - 1 : page);
+    kr = kv.k_pool + page * rec_stride + (int64_t)hk * REC;
+    vr = kv.v_pool + page * rec_stride + (int64_t)hk * REC;
+  };
+
+  // Before the preceding kernels are known to be complete (programmatic dependent launch): with one split the warp's
+  // pairs are pages w, w + kWarps, w + 2 kWarps ... whatever the length, and pages strictly older than the one that holds the
+  // newest token are not written by an append that precedes this launch - neither by one that has already counted its
+  // token into seq_lens nor by one that has not.  Their copies leave now and land while those kernels finish.  (A length
+  // that shrank in between only makes the copied pages unused; such stages are drained before shared memory is reused.)
+  int early_pairs = 0;                                       // ring stages filled ahead of the wait
+  if (S == 1) {
+    int len0 = kv.seq_lens[b];                                // may be one append behind
+    len0 = len0 > max_seq_len ? (int)max_seq_len : len0;
+    const int old_pages = (len0 - 1) >> 4;
+#pragma unroll
+    for (int i = 0; i < kEarlyStages; ++i) {
+      if (early_pairs == i && w + (2 * i + 1) * kWarps < old_pages) {
+        early_pairs = i + 1;
+        if (lane == 0) {
+          uint8_t* st = ring + i * STAGE;
+          mbar_expect_tx(&bars[i], 4u * REC);
+          const uint8_t *kr, *vr;
+          page_of(w + 2 * i * kWarps, kr, vr);
+          bulk_g2s(st, kr, REC, &bars[i]);
+          bulk_g2s(st + REC, vr, REC, &bars[i]);
+          page_of(w + (2 * i + 1) * kWarps, kr, vr);
+          bulk_g2s(st + 2 * REC, kr, REC, &bars[i]);
+          bulk_g2s(st + 3 * REC, vr, REC, &bars[i]);
+        }
+      }
+    }
+  }
+  pdl_wait();     // q, the page just appended and seq_lens come from the preceding kernels
+  int len = kv.seq_lens[b];
+  len = len < 0 ? 0 : (len > max_seq_len ? (int)max_seq_len : len);
+  int pb, pe;
+  split_range(len, s, S, pb, pe);
 
   // this warp's pages: pb + w, pb + w + kWarps, ...; consecutive two form a pair (one ring stage)
   const int n_pages = (pe - pb - w + kWarps - 1) / kWarps > 0 ? (pe - pb - w + kWarps - 1) / kWarps : 0;
   const int n_pairs = (n_pages + 1) / 2;
-  const int64_t rec_stride = (int64_t)kv.hkv * REC;
   auto page_ptrs = [&](int idx, const uint8_t*& kr, const uint8_t*& vr) {
     const int pg = pb + w + idx * kWarps;
     int64_t page = kv.block_table[(int64_t)b * kv.bt_stride + pg];
@@ -135,7 +171,8 @@ decode_attn_fp8_kernel(tsb200_kv_desc kv, const T* __restrict__ q, int64_t qs, i
   // the first copies leave before the query is expanded: their latency (block-table entry, then the copy: ~2 us) runs
   // under that work instead of after it
 #pragma unroll
-  for (int i = 0; i < kStages - 1; ++i) issue(i);
+  for (int i = 0; i < kStages - 1; ++i)
+    if (i >= early_pairs) issue(i);                          // the first pairs may already be on their way
 
 
   // ---- expanded query operand -------------------------------------------------------------------
@@ -196,7 +233,7 @@ decode_attn_fp8_kernel(tsb200_kv_desc kv, const T* __restrict__ q, int64_t qs, i
 
   bool ok = true;
   for (int pair = 0; pair < n_pairs && ok; ++pair) {
-    issue(pair + kStages - 1);
+    if (pair + kStages - 1 >= early_pairs) issue(pair + kStages - 1);
     {
       unsigned long long* bar = &bars[pair % kStages];
       const unsigned parity = (pair / kStages) & 1;
@@ -306,6 +343,12 @@ decode_attn_fp8_kernel(tsb200_kv_desc kv, const T* __restrict__ q, int64_t qs, i
       }
     }
     __syncwarp();     // all lanes are done with this stage and with pbuf before they are refilled
+  }
+  for (int i = n_pairs; i < early_pairs && ok; ++i) {        // copies issued for a length that no longer holds: let them land
+    unsigned spins = 0;
+    while (!mbar_try_wait(&bars[i], 0)) {
+      if (++spins > kWaitLimit) { ok = false; break; }
+    }
   }
   if (!ok) {
     // error path only: a wait ran out.  Give the copies still in flight a bounded time to land before
