@@ -61,11 +61,12 @@ int tsb200_check_device(void);
  * attention, add_rmsnorm, swiglu): when enabled, each launch may start while its predecessor on
  * the stream drains; the kernels order their dependent memory accesses themselves.  Process-wide;
  * returns the previous setting.  Default 0.
- * What a kernel touches before that ordering point is constant data (weights, weight scales) and, in the FP8 decode
- * attention with one split, pages of the cache STRICTLY OLDER than the one that holds a sequence's newest token together
- * with their block-table entries: with this setting on, the launches that directly precede a decode attention on its
- * stream must not rewrite those (an append never does; a cache compaction or page remap must be followed by one launch
- * of anything else, or run with the setting off). */
+ * What a kernel touches before that ordering point is constant data (weights, weight and cache scales, RoPE tables),
+ * the lengths and the block table (seq_lens, new_lens, block_table: read by the append and by the decode attention) and,
+ * in the FP8 decode attention with one split, pages of the cache STRICTLY OLDER than the one that holds a sequence's
+ * newest token.  With this setting on, a launch OF THIS LIBRARY that directly precedes an append or a decode attention on
+ * its stream must therefore not be the one that writes those (none does: lengths are advanced and pages remapped by the
+ * caller's own kernels or copies, which complete before a dependent launch starts). */
 int tsb200_set_pdl(int enabled);
 
 /* ------------------------------------------------------------------------------------

@@ -150,8 +150,10 @@ __global__ void kv_append_kernel(tsb200_kv_desc kv, T* __restrict__ q, int64_t q
                                  int64_t vs_, int64_t B,
                                  int64_t Tn, const int32_t* __restrict__ new_lens, const float* __restrict__ rope_cos,
                                  const float* __restrict__ rope_sin, int64_t rope_rows, int64_t rec_bytes) {
+  // Programmatic dependent launch: the write position, the page and the scales (inputs that the launch directly before
+  // this one does not produce) are looked up while that launch drains; the wait stands in front of the first access to
+  // q, k and v and of every store.
   pdl_launch_dependents();
-  pdl_wait();
   const int lane = threadIdx.x & 31;
   const int64_t warp = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5;
   const int64_t total = B * Tn * kv.hkv;
@@ -167,6 +169,7 @@ __global__ void kv_append_kernel(tsb200_kv_desc kv, T* __restrict__ q, int64_t q
     qp = qp < 0 ? 0 : (qp >= rope_rows ? rope_rows - 1 : qp);
     float xq[D / 32];
     T* dst = q + qbt * qs + (int64_t)qh * D;
+    pdl_wait();
     load_vec<T, D>(dst, lane, xq, true, rope_cos + qp * (D / 2), rope_sin + qp * (D / 2));
 #pragma unroll
     for (int i = 0; i < D / 32; ++i) dst[lane * (D / 32) + i] = from_f32<T>(xq[i]);
@@ -190,6 +193,7 @@ __global__ void kv_append_kernel(tsb200_kv_desc kv, T* __restrict__ q, int64_t q
     kscale = kv.k_scale[b * kv.hkv + h];
     vscale = kv.v_scale[b * kv.hkv + h];
   }
+  pdl_wait();
   load_vec<T, D>(k + bt * ks + (int64_t)h * D, lane, x, rope, rope ? rope_cos + rp * (D / 2) : nullptr, rope ? rope_sin + rp * (D / 2) : nullptr);
   if (FMT >= TSB200_KV_F32) dense_store<T, D>(x, lane, kv.k_pool + rec, slot);
   else quant_store<D, FMT, false>(x, lane, kv.k_pool + rec, slot, kscale);
