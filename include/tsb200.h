@@ -64,9 +64,9 @@ int tsb200_check_device(void);
  * What a kernel touches before that ordering point is constant data (weights, weight and cache scales, RoPE tables),
  * the lengths and the block table (seq_lens, new_lens, block_table: read by the append and by the decode attention) and,
  * in the FP8 decode attention with one split, pages of the cache STRICTLY OLDER than the one that holds a sequence's
- * newest token.  With this setting on, a launch OF THIS LIBRARY that directly precedes an append or a decode attention on
- * its stream must therefore not be the one that writes those (none does: lengths are advanced and pages remapped by the
- * caller's own kernels or copies, which complete before a dependent launch starts). */
+ * newest token.  With this setting on, the launch that directly precedes an append or a decode attention on its stream
+ * must therefore not be the one that writes those: advance lengths, remap pages and refresh scales at least two launches
+ * ahead (the engine of this package does so at the start of a step), or turn the setting off around such a pair. */
 int tsb200_set_pdl(int enabled);
 
 /* ------------------------------------------------------------------------------------
