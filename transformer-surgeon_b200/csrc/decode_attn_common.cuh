@@ -46,7 +46,9 @@ inline int choose_splits_fp8(int64_t B, int hkv, int64_t max_seq_len) {
   const int64_t base = B * hkv;
   const int64_t pages = (max_seq_len + 15) / 16;
   int64_t s = base > 0 ? 296 / base : 1;
-  if (s < 3) s = 1;              // two splits measured no faster than one (128 pairs, context 2k)
+  // two splits pay from about 1.5k tokens on (128 pairs: 1k tokens 18.8 us against 17.2 us for one split, 2k 25.9 / 28.5,
+  // 4k 38.9 / 50.9, 8k 64.0 / 94.2 - one split leaves every SM with a single CTA)
+  if (s == 2 && pages < 96) s = 1;
   const int64_t cap = pages / 24 > 0 ? pages / 24 : 1;
   if (s > cap) s = cap;
   if (s < 1) s = 1;
