@@ -111,12 +111,12 @@ class ClockSampler:
          "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self, index):
-        self.index, self.rows, self.proc = index, [], None
+        self.index, self.rows, self.proc, self.t_begin = index, [], None, None
 
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}",
-                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                          "--format=csv,noheader,nounits", "-lms", "20"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._read, daemon=True).start()
         except Exception:
@@ -124,16 +124,28 @@ class ClockSampler:
 
     def _read(self):
         for line in self.proc.stdout:
-            self.rows.append([c.strip() for c in line.split(",")])
+            self.rows.append([c.strip() for c in line.split(",")] + [time.monotonic()])
+
+    def wait_first(self, limit_s=3.0):
+        """Blocks until the first sample has arrived (the tool needs a moment to start), at most limit_s."""
+        t0 = time.monotonic()
+        while self.proc is not None and not self.rows and time.monotonic() - t0 < limit_s:
+            time.sleep(0.01)
+
+    def mark_begin(self):
+        """Start of the timed region: only samples that arrive from here on are reported (the sampler itself is
+        started ahead of the warm-up steps, so that it is already streaming by then)."""
+        self.t_begin = time.monotonic()
 
     def stop(self):
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
         self.proc.terminate()
-        mhz = sorted(int(r[0]) for r in self.rows if r and r[0].isdigit())
-        mx = [int(r[1]) for r in self.rows if len(r) > 1 and r[1].isdigit()]
+        rows = [r for r in self.rows if self.t_begin is None or r[-1] >= self.t_begin]
+        mhz = sorted(int(r[0]) for r in rows if r and r[0].isdigit())
+        mx = [int(r[1]) for r in rows if len(r) > 2 and r[1].isdigit()]
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        reasons = [n for i, n in enumerate(names) if any(len(r) > 2 + i and r[2 + i] == "Active" for r in self.rows)]
+        reasons = [n for i, n in enumerate(names) if any(len(r) > 3 + i and r[2 + i] == "Active" for r in rows)]
         return {"sm_mhz": mhz[len(mhz) // 2] if mhz else None, "sm_max_mhz": max(mx) if mx else None,
                 "reasons": reasons, "samples": len(mhz)}
 
@@ -319,11 +331,14 @@ def timed_steps(dec, a, tok_host, out_host, barrier, sampler=None):
     """(ms of K device-resident steps, ms of K end-to-end steps, context at the start)."""
     import torch
     dec.tokens.copy_(tok_host)
+    if sampler is not None:
+        sampler.start()
+        sampler.wait_first()
     for _ in range(a.warmup):
         dec.step()
     barrier()
     if sampler is not None:
-        sampler.start()
+        sampler.mark_begin()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     ctx0 = int(dec.seq_lens[0].item())
     e0.record()
