@@ -87,6 +87,8 @@ def parse():
                     help="op-level sweeps (BASELINE.json configs[1] / configs[2]) instead of the decode step; "
                          "prints one JSON line per case")
     ap.add_argument("--sweep-m", default="1,16,128,2048", help="token counts of the linear sweep")
+    ap.add_argument("--sweep-ranks", default="256,1024", help="ranks of the linear sweep")
+    ap.add_argument("--sweep-precisions", default="8,4,binary", help="factor precisions of the linear sweep")
     ap.add_argument("--sweep-ctx", default="4096,16384,32768", help="contexts of the attention sweep")
     ap.add_argument("--sweep-batch", type=int, default=64)
     ap.add_argument("--no-sweeps", action="store_true", help="N = 1: leave the op-level `sweeps` records out of the line")
@@ -641,6 +643,10 @@ def sweep_linear(a, ranks=(256, 1024), precisions=(8, 4, "binary"), ms=None, cop
     g = torch.Generator(device=dev).manual_seed(2)
     peak_bw, _ = peaks()
     ms = ms or [int(v) for v in a.sweep_m.split(",")]
+    if ranks == (256, 1024) and getattr(a, "sweep_ranks", None):
+        ranks = tuple(int(v) for v in a.sweep_ranks.split(","))
+    if precisions == (8, 4, "binary") and getattr(a, "sweep_precisions", None):
+        precisions = tuple(v if v == "binary" else int(v) for v in a.sweep_precisions.split(","))
     out = []
     for r in ranks:
         for p in precisions:
