@@ -1,5 +1,5 @@
 // Tensor-parallel epilogue in one kernel: all-reduce of the row-parallel partial outputs over PEER
-// MEMORY (plain NVLink loads, no multicast) fused with the residual add and RMSNorm that follow it.
+// MEMORY (plain NVLink loads only) fused with the residual add and RMSNorm that follow it.
 //
 //   delta = sum over ranks s of partial_s            (fp32, ranks in index order: every rank gets the
 //                                                     same bits, so the replicated residual never drifts)
