@@ -50,3 +50,19 @@ def test_swiglu(cuda, name):
     ref = oatt.swiglu(gu[:, :160], gu[:, 160:])
     tol = dict(rtol=1e-2, atol=1e-2) if name == "bf16" else dict(rtol=1e-5, atol=1e-6)
     torch.testing.assert_close(y.cpu(), ref, **tol)
+
+
+def test_swiglu_prompt_sized_equals_elementwise_form(cuda):
+    """Prompt-sized bf16 calls take the 16-byte form of the kernel: the same bits as the element-wise form (reached
+    through rows that are not 16-byte aligned), column slices of one [M, 2n] buffer included."""
+    from transformer_surgeon_b200 import ops
+    gen = torch.Generator().manual_seed(5)
+    M, n = 300, 2048
+    gu = (torch.randn(M, 2 * n, generator=gen) * 3).bfloat16().to(cuda)
+    y = ops.swiglu(gu[:, :n], gu[:, n:])                                  # aligned rows: 16-byte form
+    wide = torch.zeros((M, 2 * n + 2), dtype=torch.bfloat16, device=cuda)  # row starts 4 bytes off: element-wise form
+    wide[:, 1:2 * n + 1] = gu
+    y_ref = ops.swiglu(wide[:, 1:n + 1], wide[:, n + 1:2 * n + 1])
+    assert torch.equal(y, y_ref)
+    ref = oatt.swiglu(gu[:, :n].cpu(), gu[:, n:].cpu())
+    torch.testing.assert_close(y.cpu(), ref, rtol=1e-2, atol=1e-2)

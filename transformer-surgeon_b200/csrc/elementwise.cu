@@ -176,6 +176,31 @@ __global__ void swiglu_kernel(const T* __restrict__ gate, const T* __restrict__ 
   }
 }
 
+// Same arithmetic, eight bf16 elements (16 bytes) per thread and step: rows of n % 8 == 0 elements whose starts are
+// 16-byte aligned (a prompt-sized [65536, 14336] call moves 5.6 GB: the element-wise form ran at half the copy rate).
+__global__ void swiglu_bf16x8_kernel(const __nv_bfloat16* __restrict__ gate, const __nv_bfloat16* __restrict__ up,
+                                     __nv_bfloat16* __restrict__ y, int64_t M, int64_t n8, int64_t gs, int64_t us, int64_t ys) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int64_t total = M * n8;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t m = i / n8, c = (i - m * n8) * 8;
+    const uint4 gv = *reinterpret_cast<const uint4*>(gate + m * gs + c);
+    const uint4 uv = *reinterpret_cast<const uint4*>(up + m * us + c);
+    const __nv_bfloat162* gp = reinterpret_cast<const __nv_bfloat162*>(&gv);
+    const __nv_bfloat162* upp = reinterpret_cast<const __nv_bfloat162*>(&uv);
+    uint4 o;
+    __nv_bfloat162* op = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 g = __bfloat1622float2(gp[j]), u = __bfloat1622float2(upp[j]);
+      const float a0 = rnd<__nv_bfloat16>(g.x / (1.0f + expf(-g.x))), a1 = rnd<__nv_bfloat16>(g.y / (1.0f + expf(-g.y)));
+      op[j] = __halves2bfloat162(from_f32<__nv_bfloat16>(__fmul_rn(a0, u.x)), from_f32<__nv_bfloat16>(__fmul_rn(a1, u.y)));
+    }
+    *reinterpret_cast<uint4*>(y + m * ys + c) = o;
+  }
+}
+
 inline int egrid(int64_t n) {
   int64_t g = (n + 255) / 256;
   return (int)(g < 1 ? 1 : (g > 148 * 8 ? 148 * 8 : g));
@@ -238,9 +263,16 @@ int tsb200_swiglu(const void* gate, const void* up, void* y, int dtype, int64_t 
   if (!gate || !up || !y || gate_stride < n || up_stride < n || y_stride < n) return TSB200_ERR_ARG;
   if (dtype == TSB200_F32)
     swiglu_kernel<float><<<egrid(M * n), 256, 0, as_stream(stream)>>>((const float*)gate, (const float*)up, (float*)y, M, n, gate_stride, up_stride, y_stride);
-  else if (dtype == TSB200_BF16)
-    TSB_CUDA(launch_kernel(swiglu_kernel<__nv_bfloat16>, dim3(egrid(M * n)), dim3(256), 0, as_stream(stream),
-                           (const __nv_bfloat16*)gate, (const __nv_bfloat16*)up, (__nv_bfloat16*)y, M, n, gate_stride, up_stride, y_stride));
+  else if (dtype == TSB200_BF16) {
+    const bool vec = n % 8 == 0 && gate_stride % 8 == 0 && up_stride % 8 == 0 && y_stride % 8 == 0 && aligned(gate, 16) &&
+                     aligned(up, 16) && aligned(y, 16) && M * n >= 8 * 256 * 148;
+    if (vec)
+      TSB_CUDA(launch_kernel(swiglu_bf16x8_kernel, dim3(egrid(M * n / 8)), dim3(256), 0, as_stream(stream), (const __nv_bfloat16*)gate,
+                             (const __nv_bfloat16*)up, (__nv_bfloat16*)y, M, n / 8, gate_stride, up_stride, y_stride));
+    else
+      TSB_CUDA(launch_kernel(swiglu_kernel<__nv_bfloat16>, dim3(egrid(M * n)), dim3(256), 0, as_stream(stream),
+                             (const __nv_bfloat16*)gate, (const __nv_bfloat16*)up, (__nv_bfloat16*)y, M, n, gate_stride, up_stride, y_stride));
+  }
   else
     return TSB200_ERR_UNSUPPORTED;
   TSB_LAUNCH_CHECK();
