@@ -332,6 +332,7 @@ __global__ void kv_fp8_scales_kernel(const T* __restrict__ k, const T* __restric
   const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = blockDim.x >> 5;
   const bool rope = rope_cos != nullptr;
   float mk = 0.f, mv = 0.f;
+#pragma unroll 4                         // several tokens' vectors in flight per warp: the loop is latency-bound otherwise
   for (int64_t t = w; t < Tn; t += nw) {
     const int64_t vec = (b * Tn + t) * hkv + h;
     int64_t p = (pos0 ? (int64_t)pos0[b] : 0) + t;
